@@ -1,0 +1,344 @@
+// C API: NCCL-compatible entry points plus the AMem pause/resume calls, on top of amem::Comm.
+//
+// Reference for the five added calls: nccl_patch/nccl_2.27.5-1.diff:63-112 (they ignore the
+// communicator argument and always return ncclSuccess there).  Here the argument selects the
+// scope and failures are reported.
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "../comm/comm.h"
+#include "../core/log.h"
+#include "../include/nccl.h"
+#include "../ipc/uds.h"
+
+using namespace amem;
+
+namespace {
+
+static_assert(sizeof(ncclUniqueId) == sizeof(UniqueId), "unique id size");
+static_assert(sizeof(amemMemStats_t) == sizeof(MemStats), "amemMemStats_t must mirror MemStats");
+static_assert(sizeof(amemPauseResumeStats_t) == sizeof(PauseResumeStats), "amemPauseResumeStats_t must mirror PauseResumeStats");
+
+inline ncclResult_t R(Status s) {
+  if (s != kSuccess && log_level_ref().load() >= kWarn) LOGW("%s: %s", status_name(s), last_error_slot().c_str());
+  return (ncclResult_t)s;
+}
+inline Comm* C(ncclComm_t c) { return reinterpret_cast<Comm*>(c); }
+
+// AMEM_ENABLE=0 turns pause/resume into no-ops (the reference defaults to disabled and needs
+// AMEM_ENABLE=1, amem_nccl.cpp:711; this library exists to pause, so it defaults to on).
+bool amem_enabled() {
+  static int v = (int)env_long("AMEM_ENABLE", 1);
+  return v != 0;
+}
+
+PauseResumeStats g_process_stats;
+
+CommConfig config_from(const ncclConfig_t* cfg) {
+  CommConfig c;
+  if (cfg && cfg->maxCTAs != NCCL_CONFIG_UNDEF_INT && cfg->maxCTAs > 0) c.max_blocks = cfg->maxCTAs;
+  return c;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* amemLastError(void) { return last_error_slot().c_str(); }
+const char* ncclGetLastError(ncclComm_t) { return last_error_slot().c_str(); }
+const char* ncclGetErrorString(ncclResult_t r) { return status_name((int)r); }
+
+ncclResult_t ncclGetVersion(int* version) {
+  if (!version) return ncclInvalidArgument;
+  *version = NCCL_VERSION_CODE;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclGetUniqueId(ncclUniqueId* out) {
+  if (!out) return ncclInvalidArgument;
+  return R(make_unique_id(reinterpret_cast<UniqueId*>(out)));
+}
+
+ncclResult_t ncclCommInitRankConfig(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank, ncclConfig_t* config) {
+  if (!comm) return ncclInvalidArgument;
+  UniqueId uid;
+  memcpy(&uid, &id, sizeof(uid));
+  Comm* c = nullptr;
+  Status s = Comm::create(uid, nranks, rank, config_from(config), default_backend(), &c);
+  *comm = reinterpret_cast<ncclComm_t>(c);
+  return R(s);
+}
+
+ncclResult_t ncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId id, int rank) {
+  return ncclCommInitRankConfig(comm, nranks, id, rank, nullptr);
+}
+
+// One process drives ndev GPUs: the ranks bootstrap concurrently on helper threads.
+ncclResult_t ncclCommInitAll(ncclComm_t* comms, int ndev, const int* devlist) {
+  if (!comms || ndev < 1) return ncclInvalidArgument;
+  ncclUniqueId id;
+  ncclResult_t r = ncclGetUniqueId(&id);
+  if (r != ncclSuccess) return r;
+  std::vector<ncclResult_t> res(ndev, ncclSuccess);
+  std::vector<std::thread> th;
+  bool device = default_backend() && default_backend()->is_device();
+  for (int i = 0; i < ndev; ++i) {
+    th.emplace_back([&, i] {
+      if (device) cudaSetDevice(devlist ? devlist[i] : i);
+      res[i] = ncclCommInitRank(&comms[i], ndev, id, i);
+    });
+  }
+  for (auto& t : th) t.join();
+  for (auto x : res)
+    if (x != ncclSuccess) return x;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclCommFinalize(ncclComm_t comm) {
+  if (!comm) return ncclInvalidArgument;
+  Comm* c = C(comm);
+  if (c->backend()->is_device() && !c->paused()) c->backend()->device_sync(c->device());
+  return ncclSuccess;
+}
+
+ncclResult_t ncclCommDestroy(ncclComm_t comm) {
+  if (!comm) return ncclSuccess;
+  return R(C(comm)->destroy());
+}
+
+ncclResult_t ncclCommAbort(ncclComm_t comm) {
+  if (!comm) return ncclSuccess;
+  C(comm)->abort();
+  return R(C(comm)->destroy());
+}
+
+ncclResult_t ncclCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, ncclConfig_t* config) {
+  if (!comm || !newcomm) return ncclInvalidArgument;
+  Comm* c = nullptr;
+  Status s = C(comm)->split(color, key, config_from(config), &c);
+  *newcomm = reinterpret_cast<ncclComm_t>(c);
+  return R(s);
+}
+
+ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* asyncError) {
+  if (!comm || !asyncError) return ncclInvalidArgument;
+  *asyncError = (ncclResult_t)C(comm)->check_async();
+  return ncclSuccess;
+}
+ncclResult_t ncclCommCount(const ncclComm_t comm, int* count) {
+  if (!comm || !count) return ncclInvalidArgument;
+  *count = C(comm)->nranks();
+  return ncclSuccess;
+}
+ncclResult_t ncclCommCuDevice(const ncclComm_t comm, int* device) {
+  if (!comm || !device) return ncclInvalidArgument;
+  *device = C(comm)->device();
+  return ncclSuccess;
+}
+ncclResult_t ncclCommUserRank(const ncclComm_t comm, int* rank) {
+  if (!comm || !rank) return ncclInvalidArgument;
+  *rank = C(comm)->rank();
+  return ncclSuccess;
+}
+ncclResult_t ncclCommRegister(const ncclComm_t, void* buff, size_t, void** handle) {
+  if (handle) *handle = buff;
+  return ncclSuccess;
+}
+ncclResult_t ncclCommDeregister(const ncclComm_t, void*) { return ncclSuccess; }
+
+// ---- memory ---------------------------------------------------------------------------
+ncclResult_t ncclMemAlloc(void** ptr, size_t size) {
+  if (!ptr || size == 0) return ncclInvalidArgument;
+  VmmBackend* be = default_backend();
+  if (!be) return R(fail(kInvalidUsage, "no usable memory backend"));
+  int dev = 0;
+  if (be->is_device()) {
+    if (cudaGetDevice(&dev) != cudaSuccess) return ncclUnhandledCudaError;
+    cudaFree(0);
+  }
+  if (Registry::instance().is_paused(0)) return R(fail(kInvalidUsage, "ncclMemAlloc while paused"));
+  size_t gran = 0;
+  Status s = be->granularity(dev, &gran);
+  if (s != kSuccess) return R(s);
+  size_t sz = (size + gran - 1) / gran * gran;
+  uint64_t va = 0, h = 0;
+  if ((s = be->reserve(sz, gran, &va)) != kSuccess) return R(s);
+  if ((s = be->create(dev, sz, &h)) != kSuccess) {
+    be->free_va(va, sz);
+    return R(s);
+  }
+  if ((s = be->map(va, sz, h, dev)) != kSuccess) {
+    be->release(h);
+    be->free_va(va, sz);
+    return R(s);
+  }
+  Allocation rec;
+  rec.va = va;
+  rec.size = sz;
+  rec.handle = h;
+  rec.dev = dev;
+  rec.type = kLocalPosix;
+  rec.category = kStateful;
+  rec.tag = kTagPosix;
+  rec.owner = 0;
+  if ((s = Registry::instance().add(rec)) != kSuccess) {
+    be->unmap(va, sz);
+    be->release(h);
+    be->free_va(va, sz);
+    return R(s);
+  }
+  *ptr = (void*)va;
+  return ncclSuccess;
+}
+
+ncclResult_t ncclMemFree(void* ptr) {
+  if (!ptr) return ncclSuccess;
+  Allocation a;
+  if (!Registry::instance().find((uint64_t)ptr, &a) || a.owner != 0)
+    return R(fail(kInvalidArgument, "ncclMemFree: pointer was not returned by ncclMemAlloc"));
+  VmmBackend* be = default_backend();
+  if (a.state != kMemHole) {
+    if (be->is_device()) be->device_sync(a.dev);
+    be->unmap(a.va, a.size);
+    be->release(a.handle);
+  }
+  if (a.shadow) be->host_free(a.shadow, a.size);
+  be->free_va(a.va, a.size);
+  Registry::instance().remove(a.va);
+  return ncclSuccess;
+}
+
+// ---- collectives ----------------------------------------------------------------------
+#define NEED_COMM(c) if (!(c)) return R(fail(kInvalidArgument, "null communicator"))
+
+ncclResult_t ncclAllReduce(const void* s, void* r, size_t count, ncclDataType_t dt, ncclRedOp_t op, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollAllReduce, s, r, count, dt, dt, op, 0, 1.0f, false, kAlgoAuto, st));
+}
+ncclResult_t amemAllReduceAlgo(const void* s, void* r, size_t count, ncclDataType_t dt, ncclRedOp_t op, int algo, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollAllReduce, s, r, count, dt, dt, op, 0, 1.0f, false, algo, st));
+}
+ncclResult_t ncclReduce(const void* s, void* r, size_t count, ncclDataType_t dt, ncclRedOp_t op, int root, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollReduce, s, r, count, dt, dt, op, root, 1.0f, false, kAlgoAuto, st));
+}
+ncclResult_t ncclBroadcast(const void* s, void* r, size_t count, ncclDataType_t dt, int root, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollBroadcast, s, r, count, dt, dt, kSum, root, 1.0f, false, kAlgoAuto, st));
+}
+ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t dt, int root, ncclComm_t comm, cudaStream_t st) {
+  return ncclBroadcast(buff, buff, count, dt, root, comm, st);
+}
+ncclResult_t ncclReduceScatter(const void* s, void* r, size_t recvcount, ncclDataType_t dt, ncclRedOp_t op, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollReduceScatter, s, r, recvcount, dt, dt, op, 0, 1.0f, false, kAlgoAuto, st));
+}
+ncclResult_t amemReduceScatterScaleCast(const void* s, void* r, size_t recvcount, ncclDataType_t in_t, ncclDataType_t out_t, float scale,
+                                        ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollReduceScatter, s, r, recvcount, in_t, out_t, kSum, 0, scale, true, kAlgoAuto, st));
+}
+ncclResult_t ncclAllGather(const void* s, void* r, size_t sendcount, ncclDataType_t dt, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollAllGather, s, r, sendcount, dt, dt, kSum, 0, 1.0f, false, kAlgoAuto, st));
+}
+ncclResult_t ncclAlltoAll(const void* s, void* r, size_t count, ncclDataType_t dt, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->collective(kCollAllToAll, s, r, count, dt, dt, kSum, 0, 1.0f, false, kAlgoAuto, st));
+}
+ncclResult_t ncclSend(const void* s, size_t count, ncclDataType_t dt, int peer, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->p2p(true, s, nullptr, count * dtype_size(dt), peer, st));
+}
+ncclResult_t ncclRecv(void* r, size_t count, ncclDataType_t dt, int peer, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  return R(C(comm)->p2p(false, nullptr, r, count * dtype_size(dt), peer, st));
+}
+ncclResult_t ncclGroupStart(void) {
+  // A paused process may not batch work either (the reference guards group calls too,
+  // nccl_2.27.5-1.diff:205-229).
+  if (Registry::instance().process_paused()) return R(fail(kInvalidUsage, "ncclGroupStart while paused"));
+  return R(Comm::group_start());
+}
+ncclResult_t ncclGroupEnd(void) { return R(Comm::group_end()); }
+
+// ---- AMem -----------------------------------------------------------------------------
+ncclResult_t ncclPause(ncclComm_t* comm) {
+  if (!amem_enabled()) return ncclSuccess;
+  if (comm && *comm) return R(C(*comm)->pause(nullptr));
+  return R(Comm::pause_all(&g_process_stats));
+}
+ncclResult_t ncclResume(ncclComm_t* comm) {
+  if (!amem_enabled()) return ncclSuccess;
+  if (comm && *comm) return R(C(*comm)->resume(nullptr));
+  PauseResumeStats s;
+  Status st = Comm::resume_all(&s);
+  // keep the pause half recorded by the preceding ncclPause
+  g_process_stats.create_map_us = s.create_map_us;
+  g_process_stats.agree_us = s.agree_us;
+  g_process_stats.exchange_us = s.exchange_us;
+  g_process_stats.import_us = s.import_us;
+  g_process_stats.preload_us = s.preload_us;
+  g_process_stats.resume_barrier_us = s.resume_barrier_us;
+  g_process_stats.resume_total_us = s.resume_total_us;
+  g_process_stats.bytes_preloaded = s.bytes_preloaded;
+  g_process_stats.free_after_resume = s.free_after_resume;
+  return R(st);
+}
+ncclResult_t ncclMemStats(void) {
+  Registry::instance().dump_stats(log_level_ref().load() >= kDebug);
+  return ncclSuccess;
+}
+ncclResult_t ncclSetGroupID(int id) { return R(Registry::instance().set_group_id(id)); }
+ncclResult_t ncclGetGroupID(int* id) {
+  if (!id) return ncclInvalidArgument;
+  *id = Registry::instance().group_id();
+  return ncclSuccess;
+}
+
+ncclResult_t amemMemStatsGet(amemMemStats_t* out) {
+  if (!out) return ncclInvalidArgument;
+  Registry::instance().stats(reinterpret_cast<MemStats*>(out));
+  return ncclSuccess;
+}
+ncclResult_t amemPauseResumeStatsGet(ncclComm_t comm, amemPauseResumeStats_t* out) {
+  if (!out) return ncclInvalidArgument;
+  const PauseResumeStats& s = comm ? C(comm)->last_stats() : g_process_stats;
+  memcpy(out, &s, sizeof(s));
+  return ncclSuccess;
+}
+ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* stage_bytes) {
+  NEED_COMM(comm);
+  if (emulated) *emulated = C(comm)->emulated() ? 1 : 0;
+  if (nvls) *nvls = C(comm)->nvls() ? 1 : 0;
+  if (stage_bytes) *stage_bytes = C(comm)->stage_segment().size;
+  return ncclSuccess;
+}
+ncclResult_t amemInject(const char* what, int nth, int param) {
+  if (!what) return ncclInvalidArgument;
+  if (!strncmp(what, "uds:", 4)) {
+    uds_inject(what + 4, nth, param);
+    return ncclSuccess;
+  }
+  if (!strncmp(what, "vmm:", 4)) {
+    VmmBackend* be = default_backend();
+    if (!be) return ncclInvalidUsage;
+    be->inject_failure(what + 4, nth);
+    return ncclSuccess;
+  }
+  return ncclInvalidArgument;
+}
+ncclResult_t amemBackendUsage(size_t* physical_bytes, size_t* mappings, const char** backend_name) {
+  VmmBackend* be = default_backend();
+  if (!be) return ncclInvalidUsage;
+  if (physical_bytes) *physical_bytes = be->live_physical_bytes();
+  if (mappings) *mappings = be->live_mappings();
+  if (backend_name) *backend_name = be->name();
+  return ncclSuccess;
+}
+
+}  // extern "C"

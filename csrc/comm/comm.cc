@@ -1,0 +1,331 @@
+#include "comm.h"
+
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../core/log.h"
+#include "../kernels/launch.h"
+#include "emu.h"
+
+namespace amem {
+
+static std::mutex g_comms_mu;
+static std::vector<Comm*> g_comms;
+
+static size_t round_up(size_t x, size_t g) { return (x + g - 1) / g * g; }
+
+struct RankInfo {
+  int pid;
+  int dev;
+  int mc_ok;
+  int is_device;
+};
+
+std::vector<Comm*> Comm::all() {
+  std::lock_guard<std::mutex> g(g_comms_mu);
+  return g_comms;
+}
+
+Status Comm::create(const UniqueId& id, int nranks, int rank, const CommConfig& cfg, VmmBackend* be, Comm** out) {
+  if (!be) return fail(kInvalidUsage, "no usable memory backend (no CUDA device and AMEM_BACKEND != mock)");
+  if (nranks > kMaxRanks) return fail(kInvalidArgument, "communicators span one NVLink domain: at most %d ranks, got %d", kMaxRanks, nranks);
+  Comm* c = new Comm();
+  Status st = c->init(id, nranks, rank, cfg, be);
+  if (st != kSuccess) {
+    std::string keep = last_error_slot();
+    delete c;
+    last_error_slot() = keep;
+    return st;
+  }
+  {
+    std::lock_guard<std::mutex> g(g_comms_mu);
+    g_comms.push_back(c);
+  }
+  *out = c;
+  return kSuccess;
+}
+
+Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cfg, VmmBackend* be) {
+  be_ = be;
+  rank_ = rank;
+  nranks_ = nranks;
+  dev_ = 0;
+  if (be_->is_device()) {
+    if (cudaGetDevice(&dev_) != cudaSuccess) return fail(kCudaError, "cudaGetDevice failed");
+    cudaFree(0);  // make sure the primary context exists before driver VMM calls
+  }
+  AMEM_TRY(Mesh::connect(id, rank, nranks, &mesh_));
+  Registry::instance().set_owner_state(this->id(), kRunInit);
+
+  // Who is where: decides emulation (all ranks share one process and one device).
+  RankInfo mine{(int)getpid(), dev_, be_->mc_supported(dev_) ? 1 : 0, be_->is_device() ? 1 : 0};
+  std::vector<RankInfo> infos(nranks);
+  AMEM_TRY(mesh_->allgather(&mine, sizeof(mine), infos.data()));
+  bool same_proc_dev = nranks > 1, all_mc = true;
+  for (int r = 0; r < nranks; ++r) {
+    if (infos[r].is_device != mine.is_device) return fail(kInvalidUsage, "ranks use different memory backends");
+    if (infos[r].pid != mine.pid || infos[r].dev != mine.dev) same_proc_dev = false;
+    all_mc = all_mc && infos[r].mc_ok;
+  }
+  if (be_->is_device() && nranks > 1 && !same_proc_dev) {
+    for (int r = 0; r < nranks; ++r)
+      for (int q = r + 1; q < nranks; ++q)
+        if (infos[r].dev == infos[q].dev)
+          return fail(kInvalidUsage, "ranks %d and %d share GPU %d: ranks that wait on each other need a GPU each "
+                      "(or all ranks in one process on one GPU, which is emulated as a single grid)", r, q, infos[r].dev);
+  }
+  bool emulate = be_->is_device() && same_proc_dev;
+  if (emulate) emu_ = EmuGroup::get(this->id(), nranks);
+
+  // Sizes.
+  AMEM_TRY(be_->granularity(dev_, &gran_));
+  bool device = be_->is_device();
+  size_t stage = cfg.stage_bytes ? cfg.stage_bytes : (size_t)env_long("AMEM_STAGE_MB", device ? 288 : 12) << 20;
+  p2p_slot_bytes_ = cfg.p2p_slot_bytes ? cfg.p2p_slot_bytes : (size_t)env_long("AMEM_P2P_SLOT_KB", device ? 64 : 8) << 10;
+  if (stage < p2p_area_bytes(p2p_slot_bytes_) + (1u << 20))
+    return fail(kInvalidArgument, "staging of %zu bytes is too small for the point-to-point area", stage);
+  max_blocks_ = cfg.max_blocks ? cfg.max_blocks : (int)env_long("AMEM_MAX_BLOCKS", emulate ? 8 : 64);
+  if (!device) max_blocks_ = 1;
+  if (max_blocks_ > kMaxBlocks) max_blocks_ = kMaxBlocks;
+  timeout_ns_ = (unsigned long long)env_long("AMEM_DEVICE_TIMEOUT_MS", 20000) * 1000000ull;
+  opt_.barrier = env_long("AMEM_PAUSE_BARRIER", 1) != 0;
+  opt_.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
+
+  // Status words the kernels can reach without a copy.
+  if (device) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, kStatusWords * sizeof(uint32_t), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess)
+      return fail(kCudaError, "cudaHostAlloc(status) failed");
+    status_ = (uint32_t*)p;
+    status_pinned_ = true;
+  } else {
+    status_ = (uint32_t*)calloc(kStatusWords, sizeof(uint32_t));
+  }
+  memset(status_, 0, kStatusWords * sizeof(uint32_t));
+
+  // Control segment (stateful) and staging segment (scratch).
+  AMEM_TRY(sym_alloc(round_up(sizeof(CtrlBlock) + (1u << 16), gran_), kStateful, kTagP2P, &ctrl_));
+  AMEM_TRY(be_->memset_zero(ctrl_.va[rank_], ctrl_.size, dev_));
+  AMEM_TRY(be_->copies_sync(dev_));
+  AMEM_TRY(sym_alloc(round_up(stage, gran_), kScratch, kTagP2P, &stage_));
+  int want_nvls = cfg.nvls >= 0 ? cfg.nvls : (int)env_long("AMEM_NVLS", 1);
+  if (device && !emulate && nranks > 1 && all_mc && want_nvls) {
+    Status st = setup_multicast();
+    if (st != kSuccess) LOGW("rank %d: NVLS disabled: %s", rank_, last_error_slot().c_str());
+  }
+  AMEM_TRY(mesh_->barrier());  // everybody's control block is zeroed and mapped
+  LOGD("comm %#llx rank %d/%d dev %d backend %s emu %d nvls %d stage %zu MiB", (unsigned long long)this->id(), rank_,
+       nranks_, dev_, be_->name(), emulate ? 1 : 0, nvls() ? 1 : 0, stage_.size >> 20);
+  return kSuccess;
+}
+
+// Every rank creates `size` bytes, then maps everybody's memory side by side in one reserved
+// window: window + r * size is rank r's memory as seen from this process.
+Status Comm::sym_alloc(size_t size, int category, int tag, Segment* out) {
+  Segment s;
+  s.sym_id = next_sym_++;
+  s.size = round_up(size, gran_);
+  s.category = category;
+  s.tag = tag;
+  Registry& reg = Registry::instance();
+  if (reg.is_paused(id())) return fail(kInvalidUsage, "symmetric allocation while the communicator is paused");
+  AMEM_TRY(be_->reserve(s.size * nranks_, gran_, &s.window));
+  for (int r = 0; r < nranks_; ++r) s.va[r] = s.window + (uint64_t)r * s.size;
+  uint64_t h = 0;
+  AMEM_TRY(be_->create(dev_, s.size, &h));
+  Status st = be_->map(s.va[rank_], s.size, h, dev_);
+  if (st != kSuccess) {
+    be_->release(h);
+    return st;
+  }
+  Allocation rec;
+  rec.va = s.va[rank_];
+  rec.size = s.size;
+  rec.handle = h;
+  rec.dev = dev_;
+  rec.type = kLocalPosix;
+  rec.category = category;
+  rec.tag = tag;
+  rec.owner = id();
+  rec.sym_id = s.sym_id;
+  rec.exporter_rank = -1;
+  rec.importers = nranks_ > 1 ? (((1u << nranks_) - 1u) & ~(1u << rank_)) : 0;
+  AMEM_TRY(reg.add(rec));
+  if (nranks_ > 1) {
+    int fd = -1;
+    AMEM_TRY(be_->export_fd(h, &fd));
+    st = kSuccess;
+    for (int r = 0; r < nranks_ && st == kSuccess; ++r)
+      if (r != rank_) st = mesh_->send_fd(r, s.sym_id, s.size, fd);
+    close(fd);
+    AMEM_TRY(st);
+    for (int r = 0; r < nranks_; ++r) {
+      if (r == rank_) continue;
+      uint32_t sym = 0;
+      uint64_t sz = 0;
+      int pfd = -1;
+      AMEM_TRY(mesh_->recv_fd(r, &sym, &sz, &pfd));
+      if (sym != s.sym_id || sz != s.size) {
+        close(pfd);
+        return fail(kInternalError, "symmetric allocation out of step with rank %d (segment %u/%u, %llu/%zu bytes)", r, sym, s.sym_id,
+                    (unsigned long long)sz, s.size);
+      }
+      uint64_t ph = 0;
+      st = be_->import_fd(pfd, s.size, &ph);
+      close(pfd);
+      AMEM_TRY(st);
+      st = be_->map(s.va[r], s.size, ph, dev_);
+      if (st != kSuccess) {
+        be_->release(ph);
+        return st;
+      }
+      Allocation imp;
+      imp.va = s.va[r];
+      imp.size = s.size;
+      imp.handle = ph;
+      imp.dev = dev_;
+      imp.type = kPeerPosix;
+      imp.category = category;
+      imp.tag = kTagP2PPeer;
+      imp.owner = id();
+      imp.sym_id = s.sym_id;
+      imp.exporter_rank = r;
+      AMEM_TRY(reg.add(imp));
+    }
+  }
+  *out = s;
+  return kSuccess;
+}
+
+Status Comm::sym_free(Segment* seg) {
+  Registry& reg = Registry::instance();
+  for (int r = 0; r < nranks_; ++r) {
+    Allocation a;
+    if (!reg.find(seg->va[r], &a)) continue;
+    if (a.state != kMemHole) {
+      if (a.mc_handle && r == rank_) be_->mc_unbind(a.mc_handle, dev_, a.mc_offset, a.size);
+      be_->unmap(a.va, a.size);
+      be_->release(a.handle);
+    }
+    if (a.shadow) be_->host_free(a.shadow, a.size);
+    reg.remove(a.va);
+  }
+  if (seg->mc_va) {
+    be_->unmap(seg->mc_va, seg->size);
+    be_->free_va(seg->mc_va, seg->size);
+    be_->release(seg->mc_handle);
+  }
+  if (seg->window) be_->free_va(seg->window, seg->size * nranks_);
+  *seg = Segment();
+  return kSuccess;
+}
+
+// One multicast object per communicator: rank 0 creates it and passes the handle around, every
+// rank adds its device, binds its staging memory and maps the multicast address range.  The
+// object and its mapping survive pause; only the binding is undone and redone
+// (the reference does the same for NCCL's NVLS buffers, amem_nccl.cpp:536-538,614-616).
+Status Comm::setup_multicast() {
+  uint64_t mc = 0;
+  Status st = kSuccess;
+  size_t mc_gran = 0;
+  st = be_->mc_granularity(nranks_, stage_.size, &mc_gran);
+  bool ok = st == kSuccess && mc_gran && stage_.size % mc_gran == 0;
+  if (ok && rank_ == 0) {
+    st = be_->mc_create(nranks_, stage_.size, &mc);
+    ok = st == kSuccess;
+  }
+  bool all = false;
+  AMEM_TRY(mesh_->all_ok(ok, &all));
+  if (!all) {
+    if (mc) be_->release(mc);
+    return fail(kInvalidUsage, "multicast object could not be created (granularity %zu, staging %zu)", mc_gran, stage_.size);
+  }
+  if (rank_ == 0) {
+    int fd = -1;
+    AMEM_TRY(be_->export_fd(mc, &fd));
+    for (int r = 1; r < nranks_ && st == kSuccess; ++r) st = mesh_->send_fd(r, 0xffffffffu, stage_.size, fd);
+    close(fd);
+    AMEM_TRY(st);
+  } else {
+    uint32_t sym = 0;
+    uint64_t sz = 0;
+    int fd = -1;
+    AMEM_TRY(mesh_->recv_fd(0, &sym, &sz, &fd));
+    st = be_->import_fd(fd, 0, &mc);
+    close(fd);
+    AMEM_TRY(st);
+  }
+  ok = be_->mc_add_device(mc, dev_) == kSuccess;
+  AMEM_TRY(mesh_->all_ok(ok, &all));  // every device must be added before the first bind
+  Allocation rec;
+  uint64_t va = 0;
+  if (all) {
+    ok = Registry::instance().find(stage_.va[rank_], &rec) && be_->mc_bind(mc, 0, rec.handle, stage_.size) == kSuccess;
+    if (ok) {
+      ok = be_->reserve(stage_.size, mc_gran, &va) == kSuccess;
+      if (ok && be_->map(va, stage_.size, mc, dev_) != kSuccess) {
+        be_->free_va(va, stage_.size);
+        va = 0;
+        ok = false;
+      }
+      if (!ok) be_->mc_unbind(mc, dev_, 0, stage_.size);
+    }
+    bool bound = ok;
+    AMEM_TRY(mesh_->all_ok(ok, &all));
+    if (!all && bound) {
+      be_->unmap(va, stage_.size);
+      be_->free_va(va, stage_.size);
+      be_->mc_unbind(mc, dev_, 0, stage_.size);
+    }
+  }
+  if (!all) {
+    be_->release(mc);
+    return fail(kInvalidUsage, "multicast bind/map failed on some rank");
+  }
+  rec.mc_handle = mc;
+  rec.mc_offset = 0;
+  rec.type = kLocalSymm;
+  rec.tag = kTagNvls;
+  AMEM_TRY(Registry::instance().update(rec));
+  stage_.mc_handle = mc;
+  stage_.mc_va = va;
+  return kSuccess;
+}
+
+Comm::~Comm() {
+  if (status_) {
+    if (status_pinned_) cudaFreeHost(status_);
+    else free(status_);
+  }
+  if (order_event_) cudaEventDestroy((cudaEvent_t)order_event_);
+  delete mesh_;
+}
+
+Status Comm::destroy() {
+  {
+    std::lock_guard<std::mutex> g(g_comms_mu);
+    g_comms.erase(std::remove(g_comms.begin(), g_comms.end(), this), g_comms.end());
+  }
+  if (be_->is_device()) be_->device_sync(dev_);
+  // Peers must be done with my memory before I unmap it.
+  if (!aborted_ && mesh_ && nranks_ > 1) mesh_->barrier();
+  for (auto& s : extra_) sym_free(&s);
+  sym_free(&stage_);
+  sym_free(&ctrl_);
+  uint64_t cid = id();
+  Registry::instance().forget_owner(cid);
+  emu_.reset();
+  EmuGroup::drop(cid);
+  delete this;
+  return kSuccess;
+}
+
+void Comm::abort() {
+  aborted_ = true;
+  if (mesh_) mesh_->shutdown_all();
+}
+
+}  // namespace amem

@@ -1,0 +1,391 @@
+// Communicator operations: collectives, grouped point-to-point, split, pause / resume.
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../core/log.h"
+#include "../kernels/launch.h"
+#include "comm.h"
+#include "emu.h"
+
+namespace amem {
+
+static thread_local int t_group_depth = 0;
+static thread_local std::vector<Comm*> t_group_comms;
+
+void Comm::fill_args(CollArgs* a) const {
+  memset(a, 0, sizeof(*a));
+  a->rank = rank_;
+  a->nranks = nranks_;
+  for (int r = 0; r < nranks_; ++r) {
+    a->ctrl[r] = (CtrlBlock*)ctrl_.va[r];
+    a->stage[r] = (char*)stage_.va[r];
+  }
+  a->mc_stage = (char*)stage_.mc_va;
+  a->stage_bytes = stage_.size;
+  a->p2p_slot_bytes = p2p_slot_bytes_;
+  a->status = status_;
+  a->timeout_ns = timeout_ns_;
+  a->p2p_max_lanes = emu_ ? 2 : kP2PBlocks;
+  a->scale = 1.0f;
+}
+
+Status Comm::check_async() {
+  if (async_error_) return fail((Status)async_error_, "communicator is in an error state");
+  uint32_t code = __atomic_load_n(&status_[0], __ATOMIC_ACQUIRE);
+  if (code != 0) {
+    async_error_ = kInternalError;
+    aborted_ = true;
+    return fail(kInternalError, "device-side wait ran out (code %u): rank %u waited for rank %u in block %u at epoch %u", code,
+                status_[1], status_[2], status_[3], status_[4]);
+  }
+  return kSuccess;
+}
+
+Status Comm::check_usable(const char* what) {
+  // The reference only logs a backtrace here and lets NCCL run into unmapped memory
+  // (amem_nccl.cpp:452-464); refusing the call keeps the process alive.
+  if (paused_ || Registry::instance().is_paused(id())) {
+    LOGE("%s called while the communicator's memory is paused", what);
+    if (log_level_ref().load() >= kDebug) log_backtrace();
+    return fail(kInvalidUsage, "%s called while the communicator's memory is paused; call ncclResume first", what);
+  }
+  if (aborted_) return fail(kInternalError, "%s on an aborted communicator", what);
+  return check_async();
+}
+
+// Operations of one communicator are ordered: if the caller switches streams, the new stream
+// waits for everything the communicator enqueued on the previous one (staging reuse relies on
+// stream order).
+Status Comm::prepare_stream(cudaStream_t stream) {
+  if (!be_->is_device()) return kSuccess;
+  int cur = -1;
+  cudaGetDevice(&cur);
+  if (cur != dev_) return fail(kInvalidUsage, "current CUDA device is %d but the communicator lives on device %d", cur, dev_);
+  if (have_last_stream_ && last_stream_ != stream) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(stream, &cs);
+    if (cs == cudaStreamCaptureStatusNone) {
+      if (!order_event_) {
+        cudaEvent_t e;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return fail(kCudaError, "cudaEventCreate failed");
+        order_event_ = e;
+      }
+      if (cudaEventRecord((cudaEvent_t)order_event_, last_stream_) != cudaSuccess ||
+          cudaStreamWaitEvent(stream, (cudaEvent_t)order_event_, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(kCudaError, "could not order the new stream after the communicator's previous stream");
+      }
+    }
+  }
+  last_stream_ = stream;
+  have_last_stream_ = true;
+  return kSuccess;
+}
+
+Status Comm::run(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream) {
+  if (!be_->is_device()) {
+    int rc = host_run_collective(a, plan);
+    if (rc == kDevBadArgs) return fail(kInvalidArgument, "unsupported datatype %d -> %d with operator %d", a.dtype, a.out_dtype, a.redop);
+    if (rc != kDevOk) return check_async();
+    return kSuccess;
+  }
+  AMEM_TRY(prepare_stream(stream));
+  if (emu_) {
+    LaunchPlan p = plan;
+    int n = nranks_;
+    int tag = a.kind * 64 + a.algo * 16 + a.dtype;
+    return emu_->rendezvous(rank_, tag, &a, sizeof(a), stream, [p, n](const void* host_all, const void* dev_all, cudaStream_t s) {
+      const CollArgs* h = (const CollArgs*)host_all;
+      LaunchPlan q = p;
+      if (h[0].kind == kCollSendRecv) {
+        q.blocks = 1;
+        for (int r = 0; r < n; ++r) q.blocks = std::max(q.blocks, sendrecv_blocks(h[r]));
+      }
+      return launch_collective_emu((const CollArgs*)dev_all, h[0], n, q, s);
+    });
+  }
+  return launch_collective(a, plan, stream);
+}
+
+Status Comm::collective(int kind, const void* send, void* recv, size_t count, int dtype, int out_dtype, int redop, int root,
+                        float scale, bool has_scale, int algo, cudaStream_t stream) {
+  static const char* names[] = {"ncclAllReduce", "ncclAllGather", "ncclReduceScatter", "ncclBroadcast", "ncclReduce", "ncclAllToAll"};
+  AMEM_TRY(check_usable(names[kind]));
+  size_t es = dtype_size(dtype);
+  if (es == 0 || dtype_size(out_dtype) == 0) return fail(kInvalidArgument, "unknown datatype %d", dtype);
+  if (!send || !recv) return fail(kInvalidArgument, "null buffer");
+  if ((kind == kCollBroadcast || kind == kCollReduce) && (root < 0 || root >= nranks_)) return fail(kInvalidArgument, "root %d out of range", root);
+  if (redop < kSum || redop > kAvg) return fail(kInvalidArgument, "unknown reduction operator %d", redop);
+  if (count == 0) return kSuccess;
+  CollArgs a;
+  fill_args(&a);
+  a.kind = kind;
+  a.send = send;
+  a.recv = recv;
+  a.count = count;
+  a.dtype = dtype;
+  a.out_dtype = out_dtype;
+  a.redop = redop;
+  a.root = root;
+  a.scale = scale;
+  a.has_scale = has_scale ? 1 : 0;
+  bool reducing = kind == kCollAllReduce || kind == kCollReduceScatter || kind == kCollReduce;
+  if (reducing && redop == kAvg) {
+    a.scale = (has_scale ? scale : 1.0f) / (float)nranks_;
+    a.has_scale = 1;
+  }
+  if (!reducing) {  // pure data movement runs on bytes
+    a.count = count * es;
+    a.dtype = a.out_dtype = kU8;
+    a.redop = kSum;
+  }
+  TunerInput ti;
+  ti.kind = kind;
+  ti.count = a.count;
+  ti.dtype = a.dtype;
+  ti.redop = redop;
+  ti.nranks = nranks_;
+  ti.stage_bytes = stage_.size;
+  ti.p2p_slot_bytes = p2p_slot_bytes_;
+  ti.nvls = nvls();
+  ti.max_blocks = max_blocks_;
+  ti.forced_algo = algo;
+  LaunchPlan plan = plan_collective(ti);
+  if (kind == kCollAllReduce && algo != kAlgoAuto && plan.algo != algo)
+    return fail(kInvalidArgument, "all-reduce variant %d is not available for this size/type on this communicator", algo);
+  a.algo = plan.algo;
+  return run(a, plan, stream);
+}
+
+Status Comm::group_start() {
+  ++t_group_depth;
+  return kSuccess;
+}
+
+Status Comm::group_end() {
+  if (t_group_depth <= 0) return fail(kInvalidUsage, "ncclGroupEnd without ncclGroupStart");
+  if (--t_group_depth > 0) return kSuccess;
+  Status first = kSuccess;
+  std::vector<Comm*> comms;
+  comms.swap(t_group_comms);
+  for (Comm* c : comms) {
+    Status st = c->flush_p2p(c->pending_stream_);
+    if (st != kSuccess && first == kSuccess) first = st;
+  }
+  return first;
+}
+
+Status Comm::p2p(bool is_send, const void* src, void* dst, size_t bytes, int peer, cudaStream_t stream) {
+  AMEM_TRY(check_usable(is_send ? "ncclSend" : "ncclRecv"));
+  if (peer < 0 || peer >= nranks_) return fail(kInvalidArgument, "peer %d out of range", peer);
+  if (pending_.size() >= 2 * kMaxRanks) return fail(kInvalidUsage, "more than %d point-to-point operations in one group", 2 * kMaxRanks);
+  CollArgs::P2P e;
+  e.peer = peer;
+  e.is_send = is_send ? 1 : 0;
+  e.src = src;
+  e.dst = dst;
+  e.bytes = bytes;
+  if (pending_.empty()) pending_stream_ = stream;
+  pending_.push_back(e);
+  if (t_group_depth > 0) {
+    if (std::find(t_group_comms.begin(), t_group_comms.end(), this) == t_group_comms.end()) t_group_comms.push_back(this);
+    return kSuccess;
+  }
+  return flush_p2p(stream);
+}
+
+Status Comm::flush_p2p(cudaStream_t stream) {
+  std::vector<CollArgs::P2P> ops;
+  ops.swap(pending_);
+  if (ops.empty()) return kSuccess;
+  // Transfers to myself never touch the network: pair each self-send with a self-receive.
+  std::vector<CollArgs::P2P> net;
+  std::vector<CollArgs::P2P> self_send, self_recv;
+  for (auto& e : ops) {
+    if (e.peer != rank_) net.push_back(e);
+    else (e.is_send ? self_send : self_recv).push_back(e);
+  }
+  if (self_send.size() != self_recv.size()) return fail(kInvalidUsage, "send to self without a matching receive in the same group");
+  for (size_t i = 0; i < self_send.size(); ++i) {
+    if (self_send[i].bytes != self_recv[i].bytes) return fail(kInvalidArgument, "self send/recv sizes differ");
+    if (!self_send[i].bytes) continue;
+    if (be_->is_device()) {
+      AMEM_TRY(prepare_stream(stream));
+      if (cudaMemcpyAsync(self_recv[i].dst, self_send[i].src, self_send[i].bytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess)
+        return fail(kCudaError, "self copy failed");
+    } else {
+      memmove(self_recv[i].dst, self_send[i].src, self_send[i].bytes);
+    }
+  }
+  // Zero-byte transfers carry no credit traffic on either side.
+  net.erase(std::remove_if(net.begin(), net.end(), [](const CollArgs::P2P& e) { return e.bytes == 0; }), net.end());
+  if (net.empty() && !emu_) return kSuccess;
+  CollArgs a;
+  fill_args(&a);
+  a.kind = kCollSendRecv;
+  a.dtype = a.out_dtype = kU8;
+  a.n_p2p = (int)net.size();
+  for (size_t i = 0; i < net.size(); ++i) a.p2p[i] = net[i];
+  LaunchPlan plan;
+  plan.algo = 0;
+  plan.blocks = 1;
+  plan.threads = 512;
+  plan.chunk_elems = 0;
+  return run(a, plan, stream);
+}
+
+Status Comm::split(int color, int key, const CommConfig& cfg, Comm** out) {
+  AMEM_TRY(check_usable("ncclCommSplit"));
+  struct Vote {
+    int color, key;
+    UniqueId id;
+  };
+  Vote mine;
+  mine.color = color;
+  mine.key = key;
+  AMEM_TRY(make_unique_id(&mine.id));
+  std::vector<Vote> all(nranks_);
+  AMEM_TRY(mesh_->allgather(&mine, sizeof(mine), all.data()));
+  *out = nullptr;
+  if (color < 0) return kSuccess;
+  std::vector<int> members;
+  for (int r = 0; r < nranks_; ++r)
+    if (all[r].color == color) members.push_back(r);
+  std::stable_sort(members.begin(), members.end(), [&](int x, int y) { return all[x].key < all[y].key; });
+  int new_rank = (int)(std::find(members.begin(), members.end(), rank_) - members.begin());
+  // The child meets under the id proposed by its lowest parent rank.
+  int leader = *std::min_element(members.begin(), members.end());
+  return Comm::create(all[leader].id, (int)members.size(), new_rank, cfg, be_, out);
+}
+
+Status Comm::pause(PauseResumeStats* st) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (paused_) return kSuccess;
+  if (!pending_.empty()) return fail(kInvalidUsage, "ncclPause inside an open group");
+  Status s = pause_scope(Registry::instance(), be_, id(), dev_, mesh_, opt_, &stats_);
+  if (s == kSuccess) paused_ = true;
+  if (st) *st = stats_;
+  return s;
+}
+
+Status Comm::resume(PauseResumeStats* st) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (!paused_) return kSuccess;
+  Status s = resume_scope(Registry::instance(), be_, id(), dev_, mesh_, opt_, &stats_);
+  if (s == kSuccess) paused_ = false;
+  if (st) *st = stats_;
+  return s;
+}
+
+static void accumulate(PauseResumeStats* into, const PauseResumeStats& s, bool pause_part) {
+  if (!into) return;
+  if (pause_part) {
+    into->quiesce_us += s.quiesce_us;
+    into->offload_us += s.offload_us;
+    into->release_import_us += s.release_import_us;
+    into->release_local_us += s.release_local_us;
+    into->pause_barrier_us += s.pause_barrier_us;
+    into->bytes_offloaded += s.bytes_offloaded;
+    into->bytes_released_local += s.bytes_released_local;
+    into->bytes_released_peer += s.bytes_released_peer;
+    into->n_offload += s.n_offload;
+    into->n_release_local += s.n_release_local;
+    into->n_release_peer += s.n_release_peer;
+  } else {
+    into->create_map_us += s.create_map_us;
+    into->agree_us += s.agree_us;
+    into->exchange_us += s.exchange_us;
+    into->import_us += s.import_us;
+    into->preload_us += s.preload_us;
+    into->resume_barrier_us += s.resume_barrier_us;
+    into->bytes_preloaded += s.bytes_preloaded;
+  }
+}
+
+// Process-wide pause: every communicator in creation order (all ranks created them in the
+// same order, so the per-communicator barriers line up), then allocations that belong to no
+// communicator (ncclMemAlloc).  New allocations are refused until resume.
+Status Comm::pause_all(PauseResumeStats* st) {
+  Registry& reg = Registry::instance();
+  PauseResumeStats total;
+  memset(&total, 0, sizeof(total));
+  double t0 = now_ms();
+  VmmBackend* be = nullptr;
+  int dev = 0;
+  bool first = true;
+  for (Comm* c : all()) {
+    PauseResumeStats s;
+    memset(&s, 0, sizeof(s));
+    AMEM_TRY(c->pause(&s));
+    if (first) total.free_before_pause = s.free_before_pause;
+    first = false;
+    total.free_after_pause = s.free_after_pause;
+    accumulate(&total, s, true);
+    be = c->backend();
+    dev = c->device();
+  }
+  if (!be) be = default_backend();
+  if (be) {
+    if (be->is_device()) cudaGetDevice(&dev);
+    PauseResumeStats s;
+    memset(&s, 0, sizeof(s));
+    EngineOptions opt;
+    opt.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
+    if (reg.owner_state(0) != kRunPaused) {
+      AMEM_TRY(pause_scope(reg, be, 0, dev, nullptr, opt, &s));
+      if (first) total.free_before_pause = s.free_before_pause;
+      total.free_after_pause = s.free_after_pause;
+      accumulate(&total, s, true);
+    }
+  }
+  reg.set_process_paused(true);
+  total.pause_total_us = (now_ms() - t0) * 1000.0;
+  if (st) *st = total;
+  return kSuccess;
+}
+
+Status Comm::resume_all(PauseResumeStats* st) {
+  Registry& reg = Registry::instance();
+  PauseResumeStats total;
+  memset(&total, 0, sizeof(total));
+  double t0 = now_ms();
+  reg.set_process_paused(false);
+  VmmBackend* be = nullptr;
+  int dev = 0;
+  for (Comm* c : all()) {
+    PauseResumeStats s;
+    memset(&s, 0, sizeof(s));
+    Status r = c->resume(&s);
+    if (r != kSuccess) {
+      reg.set_process_paused(true);
+      return r;
+    }
+    total.free_after_resume = s.free_after_resume;
+    accumulate(&total, s, false);
+    be = c->backend();
+    dev = c->device();
+  }
+  if (!be) be = default_backend();
+  if (be && reg.owner_state(0) == kRunPaused) {
+    if (be->is_device()) cudaGetDevice(&dev);
+    PauseResumeStats s;
+    memset(&s, 0, sizeof(s));
+    EngineOptions opt;
+    opt.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
+    Status r = resume_scope(reg, be, 0, dev, nullptr, opt, &s);
+    if (r != kSuccess) {
+      reg.set_process_paused(true);
+      return r;
+    }
+    total.free_after_resume = s.free_after_resume;
+    accumulate(&total, s, false);
+  }
+  total.resume_total_us = (now_ms() - t0) * 1000.0;
+  if (st) *st = total;
+  return kSuccess;
+}
+
+}  // namespace amem

@@ -1,0 +1,190 @@
+/* NCCL-compatible C API of the B200-native pausable collective library.
+ *
+ * Function names, argument order, enum values and the 128-byte ncclUniqueId follow NCCL 2.27 so
+ * that code written against nccl.h (including ctypes loaders that look symbols up by name)
+ * works unchanged.  On top of that come the five AMem entry points the reference adds to
+ * nccl.h (nccl_patch/nccl_2.27.5-1.diff:329-355) -- ncclPause, ncclResume, ncclMemStats,
+ * ncclSetGroupID, ncclGetGroupID -- and a small set of amem* extensions for the fused
+ * operations and for observability.
+ */
+#ifndef AMEM_B200_NCCL_H_
+#define AMEM_B200_NCCL_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NCCL_MAJOR 2
+#define NCCL_MINOR 27
+#define NCCL_PATCH 5
+#define NCCL_SUFFIX "+amem.b200"
+#define NCCL_VERSION_CODE 22705
+#define NCCL_VERSION(X, Y, Z) (((X) <= 2 && (Y) <= 8) ? (X) * 1000 + (Y) * 100 + (Z) : (X) * 10000 + (Y) * 100 + (Z))
+
+typedef struct CUstream_st* cudaStream_t;
+typedef struct ncclComm* ncclComm_t;
+typedef struct ncclWindow* ncclWindow_t;
+#define NCCL_COMM_NULL NULL
+
+#define NCCL_UNIQUE_ID_BYTES 128
+typedef struct { char internal[NCCL_UNIQUE_ID_BYTES]; } ncclUniqueId;
+
+typedef enum {
+  ncclSuccess = 0,
+  ncclUnhandledCudaError = 1,
+  ncclSystemError = 2,
+  ncclInternalError = 3,
+  ncclInvalidArgument = 4,
+  ncclInvalidUsage = 5,
+  ncclRemoteError = 6,
+  ncclInProgress = 7,
+  ncclNumResults = 8
+} ncclResult_t;
+
+#define NCCL_CONFIG_UNDEF_INT INT32_MIN
+#define NCCL_CONFIG_UNDEF_PTR NULL
+#define NCCL_SPLIT_NOCOLOR -1
+
+typedef struct ncclConfig_v22700 {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  int blocking;
+  int cgaClusterSize;
+  int minCTAs;
+  int maxCTAs;
+  const char* netName;
+  int splitShare;
+  int trafficClass;
+  const char* commName;
+  int collnetEnable;
+  int CTAPolicy;
+  int shrinkShare;
+  int nvlsCTAs;
+} ncclConfig_t;
+
+#define NCCL_CONFIG_INITIALIZER {                                   \
+  sizeof(ncclConfig_t), 0xcafebeef, NCCL_VERSION_CODE,              \
+  NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT, \
+  NCCL_CONFIG_UNDEF_PTR, NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_PTR, \
+  NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT, NCCL_CONFIG_UNDEF_INT }
+
+typedef enum { ncclSum = 0, ncclProd = 1, ncclMax = 2, ncclMin = 3, ncclAvg = 4, ncclNumOps = 5, ncclMaxRedOp = 0x7fffffff } ncclRedOp_t;
+
+typedef enum {
+  ncclInt8 = 0, ncclChar = 0,
+  ncclUint8 = 1,
+  ncclInt32 = 2, ncclInt = 2,
+  ncclUint32 = 3,
+  ncclInt64 = 4,
+  ncclUint64 = 5,
+  ncclFloat16 = 6, ncclHalf = 6,
+  ncclFloat32 = 7, ncclFloat = 7,
+  ncclFloat64 = 8, ncclDouble = 8,
+  ncclBfloat16 = 9,
+  ncclNumTypes = 10
+} ncclDataType_t;
+
+/* ---- memory ------------------------------------------------------------------------- */
+/* VMM allocation on the current device, tracked by the registry and therefore pausable:
+ * its contents are saved on ncclPause and restored at the same address on ncclResume. */
+ncclResult_t ncclMemAlloc(void** ptr, size_t size);
+ncclResult_t ncclMemFree(void* ptr);
+
+/* ---- communicator ------------------------------------------------------------------- */
+ncclResult_t ncclGetVersion(int* version);
+ncclResult_t ncclGetUniqueId(ncclUniqueId* uniqueId);
+ncclResult_t ncclCommInitRank(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank);
+ncclResult_t ncclCommInitRankConfig(ncclComm_t* comm, int nranks, ncclUniqueId commId, int rank, ncclConfig_t* config);
+ncclResult_t ncclCommInitAll(ncclComm_t* comms, int ndev, const int* devlist);
+ncclResult_t ncclCommFinalize(ncclComm_t comm);
+ncclResult_t ncclCommDestroy(ncclComm_t comm);
+ncclResult_t ncclCommAbort(ncclComm_t comm);
+ncclResult_t ncclCommSplit(ncclComm_t comm, int color, int key, ncclComm_t* newcomm, ncclConfig_t* config);
+const char* ncclGetErrorString(ncclResult_t result);
+const char* ncclGetLastError(ncclComm_t comm);
+ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* asyncError);
+ncclResult_t ncclCommCount(const ncclComm_t comm, int* count);
+ncclResult_t ncclCommCuDevice(const ncclComm_t comm, int* device);
+ncclResult_t ncclCommUserRank(const ncclComm_t comm, int* rank);
+/* Buffer registration is accepted for source compatibility; the push protocol needs none. */
+ncclResult_t ncclCommRegister(const ncclComm_t comm, void* buff, size_t size, void** handle);
+ncclResult_t ncclCommDeregister(const ncclComm_t comm, void* handle);
+
+/* ---- collectives -------------------------------------------------------------------- */
+ncclResult_t ncclReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, int root, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclBroadcast(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclAllReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclReduceScatter(const void* sendbuff, void* recvbuff, size_t recvcount, ncclDataType_t datatype, ncclRedOp_t op, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclAllGather(const void* sendbuff, void* recvbuff, size_t sendcount, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
+/* count = elements exchanged with EACH peer; block j of sendbuff goes to rank j. */
+ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclSend(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t ncclGroupStart(void);
+ncclResult_t ncclGroupEnd(void);
+
+/* ---- AMem: pause / resume ------------------------------------------------------------ */
+/* comm == NULL (or *comm == NULL): every communicator of the process plus ncclMemAlloc
+ * memory.  Otherwise only that communicator.  Synchronous; every rank of the communicator
+ * must call; idempotent.  After ncclPause returns, the physical memory behind the
+ * communicator (this rank's and its mappings of the peers') has been returned to the driver
+ * while all virtual addresses stay reserved.  Collectives issued while paused fail with
+ * ncclInvalidUsage. */
+ncclResult_t ncclPause(ncclComm_t* comm);
+ncclResult_t ncclResume(ncclComm_t* comm);
+ncclResult_t ncclMemStats(void);
+/* Only before the first tracked allocation of the process; distinguishes co-located groups
+ * (for instance training = 100, inference = 200). */
+ncclResult_t ncclSetGroupID(int id);
+ncclResult_t ncclGetGroupID(int* id);
+
+/* ---- amem extensions ------------------------------------------------------------------ */
+typedef struct {
+  uint64_t bytes_by_tag[16];
+  uint64_t stateful_bytes, scratch_bytes, imported_bytes, multicast_bytes;
+  uint64_t live_bytes, paused_bytes, shadow_bytes;
+  uint64_t n_local, n_imported;
+  uint64_t pause_count, resume_count;
+  int group_id;
+  int paused;
+} amemMemStats_t;
+
+typedef struct {
+  double quiesce_us, offload_us, release_import_us, release_local_us, pause_barrier_us, pause_total_us;
+  double create_map_us, agree_us, exchange_us, import_us, preload_us, resume_barrier_us, resume_total_us;
+  uint64_t bytes_offloaded, bytes_preloaded;
+  uint64_t bytes_released_local, bytes_released_peer;
+  uint64_t n_offload, n_release_local, n_release_peer;
+  uint64_t free_before_pause, free_after_pause, free_after_resume;
+} amemPauseResumeStats_t;
+
+ncclResult_t amemMemStatsGet(amemMemStats_t* out);
+/* Phase timings and byte counts of the most recent pause and resume (comm NULL: process). */
+ncclResult_t amemPauseResumeStatsGet(ncclComm_t comm, amemPauseResumeStats_t* out);
+
+/* Reduce-scatter fused with a scale and an output type cast: recv[i] = (out_type)(scale *
+ * sum_r send_r[rank*recvcount + i]).  fp32 <-> bf16/fp16 and same-type are supported. */
+ncclResult_t amemReduceScatterScaleCast(const void* sendbuff, void* recvbuff, size_t recvcount, ncclDataType_t in_type,
+                                        ncclDataType_t out_type, float scale, ncclComm_t comm, cudaStream_t stream);
+/* All-reduce with a forced variant: 1 one-shot, 2 two-shot, 3 NVLS (0 lets the tuner pick). */
+ncclResult_t amemAllReduceAlgo(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op,
+                               int algo, ncclComm_t comm, cudaStream_t stream);
+/* 1 if the communicator's ranks share one GPU and run as one cooperative grid; 1 if NVLS is in use. */
+ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* stage_bytes);
+/* Host-side fault injection for tests: what = "uds:drop" | "uds:short" | "uds:nofd" |
+ * "uds:delay" | "uds:clear" | "vmm:create" | "vmm:map" | "vmm:import" | "vmm:export" |
+ * "vmm:host_alloc"; the nth next such call misbehaves. */
+ncclResult_t amemInject(const char* what, int nth, int param);
+/* Bytes of physical memory and number of mappings this process holds through the backend. */
+ncclResult_t amemBackendUsage(size_t* physical_bytes, size_t* mappings, const char** backend_name);
+const char* amemLastError(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AMEM_B200_NCCL_H_ */

@@ -1,0 +1,143 @@
+// Structures shared by the host launcher, the CUDA kernels and the host (mock) executor.
+//
+// Protocol in one paragraph.  Every rank owns a control segment (CtrlBlock, STATEFUL: it is
+// saved and restored by pause/resume) and a staging segment (SCRATCH: dropped on pause),
+// both mapped by every peer.  Collectives are "push" style: a rank stores its contribution
+// straight into the consumer's staging slot over NVLink, block b then raises flag
+// flags[b][my_rank] in the consumer's CtrlBlock to the block's current epoch and waits for
+// the same flag from every peer in its own CtrlBlock.  Epoch counters live on the device
+// (CtrlBlock::epoch[b]), so a captured CUDA graph replays correctly and nothing but the
+// control segment has to survive a pause.  Staging is split in two halves used by
+// alternate operations (CtrlBlock::opseq parity) and each half in two quarters used by
+// alternate chunks, which removes every trailing barrier.  All waits are bounded: on expiry
+// the block records {code, rank, peer, block, epoch} in a host-mapped status word and the
+// kernel runs to completion without faulting.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace amem {
+
+static const int kMaxRanks = 8;        // one NVLink/NVSwitch domain
+static const int kMaxBlocks = 512;     // flag rows available to one launch
+static const int kP2PBlocks = 32;      // blocks of a send/recv launch, per peer
+static const int kStatusWords = 16;
+
+// Collective kinds (values are part of the host<->kernel contract only).
+enum CollKind : int {
+  kCollAllReduce = 0,
+  kCollAllGather = 1,
+  kCollReduceScatter = 2,
+  kCollBroadcast = 3,
+  kCollReduce = 4,
+  kCollAllToAll = 5,
+  kCollSendRecv = 6,
+};
+
+// Allreduce variants chosen by the tuner.
+enum Algo : int { kAlgoAuto = 0, kAlgoOneShot = 1, kAlgoTwoShot = 2, kAlgoNvls = 3 };
+
+// ncclDataType_t / ncclRedOp_t numbering.
+enum DType : int { kI8 = 0, kU8 = 1, kI32 = 2, kU32 = 3, kI64 = 4, kU64 = 5, kF16 = 6, kF32 = 7, kF64 = 8, kBF16 = 9 };
+enum RedOp : int { kSum = 0, kProd = 1, kMax = 2, kMin = 3, kAvg = 4 };
+
+inline size_t dtype_size(int dt) {
+  switch (dt) {
+    case kI8: case kU8: return 1;
+    case kF16: case kBF16: return 2;
+    case kI32: case kU32: case kF32: return 4;
+    case kI64: case kU64: case kF64: return 8;
+    default: return 0;
+  }
+}
+
+struct alignas(128) CtrlBlock {
+  uint32_t opseq;                       // operations completed on this communicator (device side)
+  uint32_t done_blocks;                 // ticket counter used to bump opseq once per launch
+  uint32_t reserved[30];
+  uint32_t epoch[kMaxBlocks];           // my barrier epoch, per block index
+  uint32_t flags[kMaxBlocks][kMaxRanks];          // written by peers: flags[block][source rank]
+  // point-to-point credit protocol, indexed [peer][block]
+  uint32_t p2p_ready[kMaxRanks][kP2PBlocks];      // written by the sender: chunk sequence available
+  uint32_t p2p_taken[kMaxRanks][kP2PBlocks];      // written by the receiver: chunk sequence consumed
+  uint32_t p2p_sent[kMaxRanks][kP2PBlocks];       // my local count of chunks sent to peer
+  uint32_t p2p_rcvd[kMaxRanks][kP2PBlocks];       // my local count of chunks received from peer
+  // small all-to-all scratch for counts (MoE routing): xchg[source rank][i]
+  uint32_t xchg[kMaxRanks][256];
+};
+
+enum DeviceError : uint32_t { kDevOk = 0, kDevBarrierTimeout = 1, kDevP2PTimeout = 2, kDevBadArgs = 3, kDevGemmTimeout = 4 };
+
+struct CollArgs {
+  int kind, algo;
+  int rank, nranks;
+  int dtype, redop;
+  int out_dtype;           // differs from dtype only for the fused scale+cast reduce-scatter
+  int root;
+  const void* send;
+  void* recv;
+  size_t count;            // elements: allreduce/bcast/reduce total; allgather/reducescatter/alltoall per rank
+  float scale;             // multiplies the reduced value (1/n for avg, user scale for fused RS)
+  int has_scale;
+  CtrlBlock* ctrl[kMaxRanks];   // ctrl[rank] is mine, others are peers' blocks mapped here
+  char* stage[kMaxRanks];       // staging segments, same indexing
+  char* mc_stage;               // multicast mapping of the staging segments (NVLS) or null
+  size_t stage_bytes;           // bytes of one staging segment
+  size_t p2p_slot_bytes;        // bytes of one (peer, block) slot in the p2p area at the end of staging
+  uint32_t* status;             // host-mapped, kStatusWords words
+  unsigned long long timeout_ns;
+  // send/recv lists for grouped point-to-point (kind == kCollSendRecv)
+  int n_p2p;
+  int p2p_max_lanes;       // blocks one transfer may use (<= kP2PBlocks; small on emulated comms)
+  struct P2P {
+    int peer;
+    int is_send;
+    const void* src;
+    void* dst;
+    size_t bytes;
+  } p2p[2 * kMaxRanks];
+};
+
+// Plan computed identically on every rank from (kind, bytes, nranks).
+struct LaunchPlan {
+  int algo;
+  int blocks;
+  int threads;
+  size_t chunk_elems;   // elements of the per-chunk unit (meaning depends on kind)
+};
+
+// ---- staging layout, computed the same way on host and device --------------------------
+// [ half 0 | half 1 | p2p area ]; a half is two quarters.
+#if defined(__CUDACC__)
+#define AMEM_HD __host__ __device__ inline
+#else
+#define AMEM_HD inline
+#endif
+AMEM_HD size_t p2p_area_bytes(size_t p2p_slot_bytes) { return (size_t)kMaxRanks * 2 * kP2PBlocks * p2p_slot_bytes; }
+AMEM_HD size_t quarter_bytes(size_t stage_bytes, size_t p2p_slot_bytes) {
+  size_t q = (stage_bytes - p2p_area_bytes(p2p_slot_bytes)) / 4;
+  return q & ~(size_t)4095;
+}
+AMEM_HD size_t quarter_offset(size_t stage_bytes, size_t p2p_slot_bytes, uint32_t opseq, uint32_t chunk) {
+  return (size_t)((opseq & 1u) * 2u + (chunk & 1u)) * quarter_bytes(stage_bytes, p2p_slot_bytes);
+}
+AMEM_HD size_t half_offset(size_t stage_bytes, size_t p2p_slot_bytes, uint32_t opseq) {
+  return (size_t)(opseq & 1u) * 2u * quarter_bytes(stage_bytes, p2p_slot_bytes);
+}
+AMEM_HD size_t p2p_slot_offset(size_t stage_bytes, size_t p2p_slot_bytes, int src, uint32_t parity, int block) {
+  return stage_bytes - p2p_area_bytes(p2p_slot_bytes) + ((size_t)(src * 2 + (int)(parity & 1u)) * kP2PBlocks + block) * p2p_slot_bytes;
+}
+// Bytes one rank may put in its slot of a quarter (or of half a half, for two-shot).
+AMEM_HD size_t slot_bytes_of(size_t region_bytes, int nranks) { return (region_bytes / nranks) & ~(size_t)255; }
+
+// Blocks ("lanes") that carry one point-to-point transfer; depends only on its size, so both
+// ends agree.
+AMEM_HD int p2p_lanes(size_t bytes, size_t slot_bytes, int max_lanes) {
+  size_t l = (bytes + slot_bytes - 1) / slot_bytes;
+  return l < 1 ? 1 : (l > (size_t)max_lanes ? max_lanes : (int)l);
+}
+
+// Host executor for the mock backend (same protocol, runs on the calling thread).
+int host_run_collective(const CollArgs& a, const LaunchPlan& plan);
+
+}  // namespace amem

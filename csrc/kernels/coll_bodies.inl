@@ -1,0 +1,348 @@
+// Bodies of the push-style collectives.  This file is included twice: by collectives.cu
+// inside namespace amem::dev with AMEM_FN = __device__ __forceinline__ (CUDA kernels), and by
+// host_exec.cc inside namespace amem::hostx with AMEM_FN = inline (the mock backend runs the
+// very same protocol on the calling thread, one "block" of one "thread").  The enclosing
+// namespace supplies Proto, proto_begin/proto_end, block_barrier, block_sync, block_range,
+// copy_span and reduce_span.
+//
+// Conventions: `es` = bytes per input element, every staging offset is a multiple of 256
+// bytes, block ranges start on 16-byte boundaries, `p.opseq` picks the staging half and the
+// chunk index picks the quarter inside it.
+
+// Peer visited at step k (1..n-1) by `block`; different blocks start at different peers so
+// that the stores of one rank fan out over all NVLink destinations at once.
+AMEM_FN int peer_at(int rank, int n, int k, int block) { return (rank + 1 + (k - 1 + block) % (n - 1)) % n; }
+
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t B = a.count * es;  // bytes contributed by each rank
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(Q, n);
+  size_t cb = chunk_elems * es;
+  if (cb > slot) cb = slot;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  uint32_t c = 0;
+  for (size_t off = 0; off < B || (B == 0 && c == 0); off += cb, ++c) {
+    size_t len = B - off < cb ? B - off : cb;
+    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
+    size_t lo, hi;
+    block_range(len, p.block, p.nblocks, &lo, &hi);
+    if (send != recv + (size_t)r * B) copy_span(recv + (size_t)r * B + off + lo, send + off + lo, hi - lo);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo);
+    }
+    block_barrier(p);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo);
+    }
+    if (B == 0) break;
+  }
+}
+
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t B = a.count * es;  // bytes exchanged with each peer
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(Q, n);
+  size_t cb = chunk_elems * es;
+  if (cb > slot) cb = slot;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  uint32_t c = 0;
+  for (size_t off = 0; off < B || (B == 0 && c == 0); off += cb, ++c) {
+    size_t len = B - off < cb ? B - off : cb;
+    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
+    size_t lo, hi;
+    block_range(len, p.block, p.nblocks, &lo, &hi);
+    if (send != recv) copy_span(recv + (size_t)r * B + off + lo, send + (size_t)r * B + off + lo, hi - lo);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + (size_t)q * B + off + lo, hi - lo);
+    }
+    block_barrier(p);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo);
+    }
+    if (B == 0) break;
+  }
+}
+
+// Reduce-scatter with the optional fused scale and output-type cast (gradient averaging and
+// fp32 <-> bf16 conversion happen in the same pass that reduces).
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t R = a.count;  // elements each rank receives
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(Q, n);
+  size_t ce = chunk_elems;
+  if (ce * es > slot) ce = slot / es;
+  const char* send = (const char*)a.send;
+  TO* recv = (TO*)a.recv;
+  uint32_t c = 0;
+  for (size_t off = 0; off < R || (R == 0 && c == 0); off += ce, ++c) {
+    size_t len = R - off < ce ? R - off : ce;
+    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
+    size_t lo, hi;
+    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + ((size_t)q * R + off) * es + lo, hi - lo);
+    }
+    block_barrier(p);
+    const TI* slots[kMaxRanks];
+    for (int s = 0; s < n; ++s)
+      slots[s] = (s == r) ? (const TI*)(send + ((size_t)r * R + off) * es + lo)
+                          : (const TI*)(a.stage[r] + qoff + (size_t)s * slot + lo);
+    reduce_span<TI, TO, OP>(recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+    if (R == 0) break;
+  }
+}
+
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t B = a.count * es;
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(Q, n);
+  const char* send = (const char*)a.send;
+  size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, 0);
+  size_t lo, hi;
+  block_range(B, p.block, p.nblocks, &lo, &hi);
+  for (int k = 1; k < n; ++k) {
+    int q = peer_at(r, n, k, p.block);
+    copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + lo, hi - lo);
+  }
+  block_barrier(p);
+  const TI* slots[kMaxRanks];
+  for (int s = 0; s < n; ++s)
+    slots[s] = (s == r) ? (const TI*)(send + lo) : (const TI*)(a.stage[r] + qoff + (size_t)s * slot + lo);
+  reduce_span<TI, TO, OP>((TO*)a.recv + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+}
+
+// Two-shot: reduce-scatter of the chunk into region X, then all-gather of the reduced slices
+// through region Y; both regions live in the half selected by opseq, no quarter alternation
+// is needed because each chunk ends with a barrier of its own before Y is read.
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t N = a.count;
+  const size_t H = 2 * quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(H / 2, n);
+  const size_t hoff = half_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq);
+  const size_t xoff = hoff, yoff = hoff + H / 2;
+  const size_t vi = 16 / es;
+  size_t ce = chunk_elems;
+  if (ce > (slot / es) * n) ce = (slot / es) * n;
+  ce = ce / (vi * n) * (vi * n);
+  if (ce == 0) ce = vi * n;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  for (size_t off = 0; off < N; off += ce) {
+    size_t len = N - off < ce ? N - off : ce;
+    // slice length: equal parts rounded up to a whole 16-byte vector
+    size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      size_t b0 = (size_t)q * sl, b1 = b0 + sl;
+      if (b0 > len) b0 = len;
+      if (b1 > len) b1 = len;
+      size_t lo, hi;
+      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      copy_span(a.stage[q] + xoff + (size_t)r * slot + lo, send + (off + b0) * es + lo, hi - lo);
+    }
+    block_barrier(p);
+    {
+      size_t b0 = (size_t)r * sl, b1 = b0 + sl;
+      if (b0 > len) b0 = len;
+      if (b1 > len) b1 = len;
+      size_t lo, hi;
+      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      const TI* slots[kMaxRanks];
+      for (int s = 0; s < n; ++s)
+        slots[s] = (s == r) ? (const TI*)(send + (off + b0) * es + lo)
+                            : (const TI*)(a.stage[r] + xoff + (size_t)s * slot + lo);
+      char* mine = a.stage[r] + yoff + (size_t)r * slot + lo;
+      reduce_span<TI, TO, OP>((TO*)mine, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+      block_sync();
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(a.stage[q] + yoff + (size_t)r * slot + lo, mine, hi - lo);
+      }
+      copy_span(recv + (off + b0) * es + lo, mine, hi - lo);
+    }
+    block_barrier(p);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      size_t b0 = (size_t)q * sl, b1 = b0 + sl;
+      if (b0 > len) b0 = len;
+      if (b1 > len) b1 = len;
+      size_t lo, hi;
+      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      copy_span(recv + (off + b0) * es + lo, a.stage[r] + yoff + (size_t)q * slot + lo, hi - lo);
+    }
+  }
+}
+
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t B = a.count * es;
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  size_t cb = chunk_elems * es;
+  if (cb > Q) cb = Q;
+  cb &= ~(size_t)255;
+  if (cb == 0) cb = 256;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  uint32_t c = 0;
+  for (size_t off = 0; off < B; off += cb, ++c) {
+    size_t len = B - off < cb ? B - off : cb;
+    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
+    size_t lo, hi;
+    block_range(len, p.block, p.nblocks, &lo, &hi);
+    if (r == a.root) {
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(a.stage[q] + qoff + lo, send + off + lo, hi - lo);
+      }
+      if (send != recv) copy_span(recv + off + lo, send + off + lo, hi - lo);
+    }
+    block_barrier(p);
+    if (r != a.root) copy_span(recv + off + lo, a.stage[r] + qoff + lo, hi - lo);
+  }
+}
+
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_reduce(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI);
+  const size_t N = a.count;
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(Q, n);
+  size_t ce = chunk_elems;
+  if (ce * es > slot) ce = slot / es;
+  const char* send = (const char*)a.send;
+  uint32_t c = 0;
+  for (size_t off = 0; off < N; off += ce, ++c) {
+    size_t len = N - off < ce ? N - off : ce;
+    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
+    size_t lo, hi;
+    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    if (r != a.root) copy_span(a.stage[a.root] + qoff + (size_t)r * slot + lo, send + off * es + lo, hi - lo);
+    block_barrier(p);
+    if (r == a.root) {
+      const TI* slots[kMaxRanks];
+      for (int s = 0; s < n; ++s)
+        slots[s] = (s == r) ? (const TI*)(send + off * es + lo) : (const TI*)(a.stage[r] + qoff + (size_t)s * slot + lo);
+      reduce_span<TI, TO, OP>((TO*)a.recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+    }
+  }
+}
+
+// Grouped point-to-point: a credit protocol per (peer, lane).  The sender may run two
+// slots ahead of the receiver; `p2p_ready` (in the receiver's control block) announces a
+// filled slot, `p2p_taken` (in the sender's control block) hands it back.
+AMEM_FN void body_sendrecv(const CollArgs& a, int entry, int lane, int lanes, int* s_abort) {
+  const CollArgs::P2P& e = a.p2p[entry];
+  CtrlBlock* me = a.ctrl[a.rank];
+  CtrlBlock* pe = a.ctrl[e.peer];
+  const size_t slot = a.p2p_slot_bytes;
+  const size_t round_bytes = (size_t)lanes * slot;
+  if (thread_index() == 0) *s_abort = 0;
+  block_sync();
+  if (e.is_send) {
+    uint32_t seq = ld_volatile(&me->p2p_sent[e.peer][lane]);
+    for (size_t base = 0; base < e.bytes; base += round_bytes) {
+      size_t off = base + (size_t)lane * slot;
+      if (off >= e.bytes) break;
+      size_t len = e.bytes - off < slot ? e.bytes - off : slot;
+      if (thread_index() == 0 && *(volatile int*)s_abort == 0) {
+        if (!wait_flag_ge(&me->p2p_taken[e.peer][lane], seq - 1u, a.timeout_ns)) {
+          report_error(a.status, kDevP2PTimeout, a.rank, e.peer, lane, seq);
+          *(volatile int*)s_abort = 1;
+        }
+      }
+      block_sync();
+      copy_span(a.stage[e.peer] + p2p_slot_offset(a.stage_bytes, slot, a.rank, seq, lane), (const char*)e.src + off, len);
+      block_sync();
+      if (thread_index() == 0) {
+        fence_system();
+        st_release_sys(&pe->p2p_ready[a.rank][lane], seq + 1u);
+      }
+      seq += 1u;
+    }
+    block_sync();
+    if (thread_index() == 0) me->p2p_sent[e.peer][lane] = seq;
+  } else {
+    uint32_t seq = ld_volatile(&me->p2p_rcvd[e.peer][lane]);
+    for (size_t base = 0; base < e.bytes; base += round_bytes) {
+      size_t off = base + (size_t)lane * slot;
+      if (off >= e.bytes) break;
+      size_t len = e.bytes - off < slot ? e.bytes - off : slot;
+      if (thread_index() == 0 && *(volatile int*)s_abort == 0) {
+        if (!wait_flag_ge(&me->p2p_ready[e.peer][lane], seq + 1u, a.timeout_ns)) {
+          report_error(a.status, kDevP2PTimeout, a.rank, e.peer, lane, seq);
+          *(volatile int*)s_abort = 1;
+        }
+      }
+      block_sync();
+      copy_span((char*)e.dst + off, a.stage[a.rank] + p2p_slot_offset(a.stage_bytes, slot, e.peer, seq, lane), len);
+      block_sync();
+      if (thread_index() == 0) {
+        fence_system();
+        st_release_sys(&pe->p2p_taken[a.rank][lane], seq + 1u);
+      }
+      seq += 1u;
+    }
+    block_sync();
+    if (thread_index() == 0) me->p2p_rcvd[e.peer][lane] = seq;
+  }
+}
+
+// REDUCING selects which bodies are compiled into an instantiation: the copy-only
+// collectives are instantiated once for bytes, the reducing ones per (type, operator).
+template <typename TI, typename TO, int OP, bool REDUCING>
+AMEM_FN void run_body(const CollArgs& a, int block, int nblocks, int* s_abort, size_t chunk_elems) {
+  Proto p;
+  proto_begin(p, a, block, nblocks, s_abort);
+  if (a.nranks == 1) {
+    // Single rank: every collective degenerates to a (scaled, cast) copy.
+    size_t lo, hi;
+    block_range(a.count * sizeof(TI), block, nblocks, &lo, &hi);
+    const TI* slots[kMaxRanks];
+    slots[0] = (const TI*)((const char*)a.send + lo);
+    if ((const void*)a.send != (const void*)a.recv || a.has_scale || sizeof(TI) != sizeof(TO))
+      reduce_span<TI, TO, OP>((TO*)a.recv + lo / sizeof(TI), slots, 1, (hi - lo) / sizeof(TI), a.scale, a.has_scale != 0);
+  } else if constexpr (REDUCING) {
+    switch (a.kind) {
+      case kCollAllReduce:
+        if (a.algo == kAlgoOneShot) body_allreduce_oneshot<TI, TO, OP>(a, p);
+        else body_allreduce_twoshot<TI, TO, OP>(a, p, chunk_elems);
+        break;
+      case kCollReduceScatter: body_reducescatter<TI, TO, OP>(a, p, chunk_elems); break;
+      case kCollReduce: body_reduce<TI, TO, OP>(a, p, chunk_elems); break;
+      default: break;
+    }
+  } else {
+    switch (a.kind) {
+      case kCollAllGather: body_allgather<TI, TO, OP>(a, p, chunk_elems); break;
+      case kCollBroadcast: body_broadcast<TI, TO, OP>(a, p, chunk_elems); break;
+      case kCollAllToAll: body_alltoall<TI, TO, OP>(a, p, chunk_elems); break;
+      default: break;
+    }
+  }
+  proto_end(p);
+}

@@ -1,0 +1,238 @@
+// Device-side building blocks of the collective kernels: system-scope flag accesses,
+// the bounded block-level cross-rank barrier, 16-byte vector copy / reduce loops and the
+// element-type traits.  Everything here is plain sm_100a CUDA C++ with inline PTX for the
+// memory-model sensitive accesses; no library device code is used.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "coll_args.h"
+
+namespace amem {
+namespace dev {
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Records the first device-side error of a launch in the host-mapped status words.
+__device__ __forceinline__ void report_error(uint32_t* status, uint32_t code, int rank, int peer, int block, uint32_t epoch) {
+  if (atomicCAS(status, 0u, code) == 0u) {
+    status[1] = (uint32_t)rank;
+    status[2] = (uint32_t)peer;
+    status[3] = (uint32_t)block;
+    status[4] = epoch;
+    __threadfence_system();
+  }
+}
+
+// Spins until *flag has reached `want` (wrap-safe) or the time budget is spent.
+// Returns false on timeout; the caller records the error and carries on without waiting.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want, unsigned long long timeout_ns) {
+  if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+  unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+    }
+    if (globaltimer_ns() - t0 > timeout_ns) return false;
+  }
+}
+
+// Per-launch view of one rank's protocol state.
+struct Proto {
+  const CollArgs* a;
+  CtrlBlock* me;
+  uint32_t epoch;   // this block's epoch (valid in every thread)
+  uint32_t opseq;
+  int block;        // block index within this rank's part of the grid
+  int nblocks;
+  int* abort_flag;  // shared memory, one per block
+};
+
+__device__ __forceinline__ void proto_begin(Proto& p, const CollArgs& a, int block, int nblocks, int* s_abort) {
+  p.a = &a;
+  p.me = a.ctrl[a.rank];
+  p.block = block;
+  p.nblocks = nblocks;
+  p.abort_flag = s_abort;
+  if (threadIdx.x == 0) *s_abort = 0;
+  p.epoch = ld_volatile(&p.me->epoch[block]);
+  p.opseq = ld_volatile(&p.me->opseq);
+  __syncthreads();
+}
+
+// All threads of the block call this.  Makes every store issued by the block so far visible
+// to the peers before the flag, then waits for the same-index block of every peer.
+__device__ __forceinline__ void block_barrier(Proto& p) {
+  const CollArgs& a = *p.a;
+  p.epoch += 1;
+  __syncthreads();
+  int t = threadIdx.x;
+  if (t < a.nranks && t != a.rank) {
+    __threadfence_system();
+    st_release_sys(&a.ctrl[t]->flags[p.block][a.rank], p.epoch);
+    if (*(volatile int*)p.abort_flag == 0) {
+      if (!wait_flag_ge(&p.me->flags[p.block][t], p.epoch, a.timeout_ns)) {
+        report_error(a.status, kDevBarrierTimeout, a.rank, t, p.block, p.epoch);
+        *(volatile int*)p.abort_flag = 1;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// Stores the block's epoch back and bumps the operation counter once per launch.
+__device__ __forceinline__ void proto_end(Proto& p) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    p.me->epoch[p.block] = p.epoch;
+    __threadfence();
+    uint32_t ticket = atomicAdd(&p.me->done_blocks, 1u);
+    if (ticket == (uint32_t)p.nblocks - 1) {
+      p.me->done_blocks = 0;
+      p.me->opseq = p.opseq + 1;
+      __threadfence();
+    }
+  }
+}
+
+// ---------------------------------------------------------------- element traits
+template <typename T> struct Acc { using type = T; };
+template <> struct Acc<__half> { using type = float; };
+template <> struct Acc<__nv_bfloat16> { using type = float; };
+
+template <typename T> __device__ __forceinline__ typename Acc<T>::type to_acc(T v) { return v; }
+template <> __device__ __forceinline__ float to_acc<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_acc<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T, typename A> __device__ __forceinline__ T from_acc(A v) { return (T)v; }
+template <> __device__ __forceinline__ __half from_acc<__half, float>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16, float>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_acc<__half, double>(double v) { return __float2half_rn((float)v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_acc<__nv_bfloat16, double>(double v) { return __float2bfloat16_rn((float)v); }
+
+template <int OP, typename A> __device__ __forceinline__ A combine(A x, A y) {
+  if (OP == kSum || OP == kAvg) return x + y;
+  if (OP == kProd) return x * y;
+  if (OP == kMax) return x > y ? x : y;
+  return x < y ? x : y;
+}
+
+template <typename A> __device__ __forceinline__ A apply_scale(A v, float s) { return (A)((double)v * (double)s); }
+template <> __device__ __forceinline__ float apply_scale<float>(float v, float s) { return v * s; }
+
+__device__ __forceinline__ void block_sync() { __syncthreads(); }
+__device__ __forceinline__ int thread_index() { return threadIdx.x; }
+__device__ __forceinline__ void fence_system() { __threadfence_system(); }
+
+// ---------------------------------------------------------------- copy / reduce loops
+// Range [lo, hi) in bytes is this block's share; lo is a multiple of 16.
+__device__ __forceinline__ void block_range(size_t total_bytes, int block, int nblocks, size_t* lo, size_t* hi) {
+  size_t nvec = (total_bytes + 15) / 16;
+  size_t per = (nvec + nblocks - 1) / nblocks;
+  size_t l = (size_t)block * per * 16, h = l + per * 16;
+  if (l > total_bytes) l = total_bytes;
+  if (h > total_bytes) h = total_bytes;
+  *lo = l;
+  *hi = h;
+}
+
+__device__ __forceinline__ void copy_span(char* dst, const char* src, size_t bytes) {
+  if (bytes == 0) return;
+  int t = threadIdx.x, nt = blockDim.x;
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    size_t nvec = bytes / 16;
+    const uint4* s = (const uint4*)src;
+    uint4* d = (uint4*)dst;
+    size_t i = t;
+    // four independent 16-byte loads in flight per thread
+    for (; i + 3 * (size_t)nt < nvec; i += 4 * (size_t)nt) {
+      uint4 v0 = s[i], v1 = s[i + nt], v2 = s[i + 2 * (size_t)nt], v3 = s[i + 3 * (size_t)nt];
+      d[i] = v0;
+      d[i + nt] = v1;
+      d[i + 2 * (size_t)nt] = v2;
+      d[i + 3 * (size_t)nt] = v3;
+    }
+    for (; i < nvec; i += nt) d[i] = s[i];
+    for (size_t b = nvec * 16 + t; b < bytes; b += nt) dst[b] = src[b];
+  } else {
+    for (size_t b = t; b < bytes; b += nt) dst[b] = src[b];
+  }
+}
+
+// out[i] = cast(scale * OP_r(slot_r[i]))  for i in [0, n); reduction order is rank 0..nslots-1,
+// accumulated in Acc<TI> (fp32 for 16-bit floats) and rounded once.
+template <typename TI, typename TO, int OP>
+__device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale) {
+  using A = typename Acc<TI>::type;
+  constexpr int VI = 16 / sizeof(TI);
+  int t = threadIdx.x, nt = blockDim.x;
+  bool aligned = (((uintptr_t)out) % (VI * sizeof(TO)) == 0);
+  for (int r = 0; r < nslots; ++r) aligned = aligned && (((uintptr_t)slots[r] & 15) == 0);
+  size_t nvec = aligned ? n / VI : 0;
+  for (size_t i = t; i < nvec; i += nt) {
+    A acc[VI];
+    uint4 raw[kMaxRanks];
+    // issue every slot's load before the first add so they are all in flight together
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < nslots) raw[r] = ((const uint4*)slots[r])[i];
+    {
+      const TI* e = (const TI*)&raw[0];
+#pragma unroll
+      for (int k = 0; k < VI; ++k) acc[k] = to_acc<TI>(e[k]);
+    }
+#pragma unroll
+    for (int r = 1; r < kMaxRanks; ++r) {
+      if (r < nslots) {
+        const TI* e = (const TI*)&raw[r];
+#pragma unroll
+        for (int k = 0; k < VI; ++k) acc[k] = combine<OP, A>(acc[k], to_acc<TI>(e[k]));
+      }
+    }
+    alignas(16) TO res[VI];
+#pragma unroll
+    for (int k = 0; k < VI; ++k) {
+      A v = has_scale ? apply_scale<A>(acc[k], scale) : acc[k];
+      res[k] = from_acc<TO, A>(v);
+    }
+    if (sizeof(TO) * VI == 16) {
+      ((uint4*)out)[i] = *(const uint4*)res;
+    } else if (sizeof(TO) * VI == 32) {
+      ((uint4*)out)[2 * i] = ((const uint4*)res)[0];
+      ((uint4*)out)[2 * i + 1] = ((const uint4*)res)[1];
+    } else if (sizeof(TO) * VI == 8) {
+      ((uint2*)out)[i] = *(const uint2*)res;
+    } else {
+#pragma unroll
+      for (int k = 0; k < VI; ++k) out[i * VI + k] = res[k];
+    }
+  }
+  for (size_t i = nvec * VI + t; i < n; i += nt) {
+    A acc = to_acc<TI>(slots[0][i]);
+    for (int r = 1; r < nslots; ++r) acc = combine<OP, A>(acc, to_acc<TI>(slots[r][i]));
+    if (has_scale) acc = apply_scale<A>(acc, scale);
+    out[i] = from_acc<TO, A>(acc);
+  }
+}
+
+}  // namespace dev
+}  // namespace amem

@@ -1,0 +1,247 @@
+// CUDA kernels of the collectives (sm_100a) and their launchers.
+//
+// Data moves by plain peer stores/loads through the NVSwitch (push protocol described in
+// coll_args.h) or, for the NVLS all-reduce, by multimem.ld_reduce / multimem.st on the
+// multicast mapping of the staging segments, which reduces inside the switch.  No TMA and
+// no cluster multicast is used anywhere in this file.  Every spin is bounded (coll_device.cuh).
+//
+// "emu" launchers run all ranks of a communicator as ONE cooperative grid on one GPU
+// (blockIdx.y = rank): kernels of different ranks wait on one another, so they must never be
+// separate launches on the same device.  This is what lets the single-GPU test-suite cover
+// the multi-rank protocol.
+#include <cooperative_groups.h>
+
+#include "../core/log.h"
+#include "../core/status.h"
+#include "coll_device.cuh"
+#include "dispatch.h"
+#include "launch.h"
+
+namespace amem {
+namespace dev {
+#define AMEM_FN __device__ __forceinline__
+#include "coll_bodies.inl"
+#undef AMEM_FN
+
+// ------------------------------------------------------------------ NVLS all-reduce
+template <typename T> struct Multimem;
+template <> struct Multimem<float> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint4 scale(uint4 v, float s) {
+    v.x = __float_as_uint(__uint_as_float(v.x) * s);
+    v.y = __float_as_uint(__uint_as_float(v.y) * s);
+    v.z = __float_as_uint(__uint_as_float(v.z) * s);
+    v.w = __float_as_uint(__uint_as_float(v.w) * s);
+    return v;
+  }
+};
+template <> struct Multimem<__nv_bfloat16> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint32_t scale1(uint32_t w, float s) {
+    __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&w);
+    float2 f = __bfloat1622float2(h);
+    __nv_bfloat162 o = __floats2bfloat162_rn(f.x * s, f.y * s);
+    return *reinterpret_cast<uint32_t*>(&o);
+  }
+  static __device__ __forceinline__ uint4 scale(uint4 v, float s) {
+    return make_uint4(scale1(v.x, s), scale1(v.y, s), scale1(v.z, s), scale1(v.w, s));
+  }
+};
+template <> struct Multimem<__half> {
+  static __device__ __forceinline__ uint4 ld_reduce(const void* p) {
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+  }
+  static __device__ __forceinline__ uint32_t scale1(uint32_t w, float s) {
+    __half2 h = *reinterpret_cast<__half2*>(&w);
+    float2 f = __half22float2(h);
+    __half2 o = __floats2half2_rn(f.x * s, f.y * s);
+    return *reinterpret_cast<uint32_t*>(&o);
+  }
+  static __device__ __forceinline__ uint4 scale(uint4 v, float s) {
+    return make_uint4(scale1(v.x, s), scale1(v.y, s), scale1(v.z, s), scale1(v.w, s));
+  }
+};
+__device__ __forceinline__ void multimem_st(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Stage the chunk locally, let the switch add the n copies of my slice and broadcast the sum
+// back into every rank's staging, then copy out.  One region (the op's half) suffices: both
+// phases that write it are fenced by a barrier from the phase that reads it.
+template <typename T>
+__device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(T), vi = 16 / es;
+  const size_t N = a.count;
+  const size_t H = 2 * quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t hoff = half_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq);
+  size_t ce = chunk_elems;
+  if (ce * es > H) ce = H / es;
+  ce = ce / (vi * n) * (vi * n);
+  if (ce == 0) ce = vi * n;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  char* mine = a.stage[r] + hoff;
+  char* mc = a.mc_stage + hoff;
+  for (size_t off = 0; off < N; off += ce) {
+    size_t len = N - off < ce ? N - off : ce;
+    size_t lo, hi;
+    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    copy_span(mine + lo, send + off * es + lo, hi - lo);
+    block_barrier(p);
+    size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+    size_t b0 = (size_t)r * sl, b1 = b0 + sl;
+    if (b0 > len) b0 = len;
+    if (b1 > len) b1 = len;
+    size_t slo, shi;
+    block_range((b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
+    // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
+    size_t nvec = (shi - slo + 15) / 16;
+    char* base = mc + b0 * es + slo;
+    for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+      uint4 v = Multimem<T>::ld_reduce(base + i * 16);
+      if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
+      multimem_st(base + i * 16, v);
+    }
+    block_barrier(p);
+    copy_span(recv + off * es + lo, mine + lo, hi - lo);
+  }
+}
+
+// ------------------------------------------------------------------ kernels
+template <typename TI, typename TO, int OP, bool RED>
+__global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {
+  __shared__ int s_abort;
+  run_body<TI, TO, OP, RED>(a, blockIdx.x, gridDim.x, &s_abort, chunk_elems);
+}
+
+template <typename TI, typename TO, int OP, bool RED>
+__global__ void __launch_bounds__(512) coll_kernel_emu(const CollArgs* __restrict__ all, size_t chunk_elems) {
+  __shared__ int s_abort;
+  run_body<TI, TO, OP, RED>(all[blockIdx.y], blockIdx.x, gridDim.x, &s_abort, chunk_elems);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {
+  __shared__ int s_abort;
+  Proto p;
+  proto_begin(p, a, blockIdx.x, gridDim.x, &s_abort);
+  body_allreduce_nvls<T>(a, p, chunk_elems);
+  proto_end(p);
+}
+
+// blockIdx.x enumerates (entry, lane) pairs; lanes of an entry depend only on its byte count,
+// so sender and receiver agree on them.
+__device__ __forceinline__ void sendrecv_dispatch(const CollArgs& a, int* s_abort) {
+  int b = blockIdx.x;
+  for (int e = 0; e < a.n_p2p; ++e) {
+    int lanes = p2p_lanes(a.p2p[e].bytes, a.p2p_slot_bytes, a.p2p_max_lanes);
+    if (b < lanes) {
+      body_sendrecv(a, e, b, lanes, s_abort);
+      return;
+    }
+    b -= lanes;
+  }
+}
+__global__ void __launch_bounds__(512) sendrecv_kernel(const __grid_constant__ CollArgs a) {
+  __shared__ int s_abort;
+  sendrecv_dispatch(a, &s_abort);
+}
+// Emulation: ranks may have different numbers of (entry, lane) blocks; surplus blocks exit.
+__global__ void __launch_bounds__(512) sendrecv_kernel_emu(const CollArgs* __restrict__ all) {
+  __shared__ int s_abort;
+  sendrecv_dispatch(all[blockIdx.y], &s_abort);
+}
+
+}  // namespace dev
+
+// ------------------------------------------------------------------ launchers
+static Status check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(kCudaError, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return kSuccess;
+}
+
+int sendrecv_blocks(const CollArgs& a) {
+  int total = 0;
+  for (int e = 0; e < a.n_p2p; ++e) total += p2p_lanes(a.p2p[e].bytes, a.p2p_slot_bytes, a.p2p_max_lanes);
+  return total;
+}
+
+Status launch_collective(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream) {
+  dim3 grid(plan.blocks), block(plan.threads);
+  if (a.kind == kCollSendRecv) {
+    int nb = sendrecv_blocks(a);
+    if (nb == 0) return kSuccess;
+    dev::sendrecv_kernel<<<nb, plan.threads, 0, stream>>>(a);
+    return check_launch("sendrecv");
+  }
+  bool ok = true;
+  if (a.kind == kCollAllReduce && a.algo == kAlgoNvls && a.nranks > 1) {
+    if (a.dtype == kF32) dev::nvls_allreduce_kernel<float><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+    else if (a.dtype == kBF16) dev::nvls_allreduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+    else if (a.dtype == kF16) dev::nvls_allreduce_kernel<__half><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+    else return fail(kInvalidArgument, "NVLS all-reduce supports fp32, fp16 and bf16 sums only");
+    return check_launch("nvls allreduce");
+  }
+  bool reducing = a.kind == kCollAllReduce || a.kind == kCollReduceScatter || a.kind == kCollReduce;
+  if (reducing) {
+#define DEV_CALL(TI, TO, OP) dev::coll_kernel<TI, TO, OP, true><<<grid, block, 0, stream>>>(a, plan.chunk_elems)
+    AMEM_DISPATCH_REDUCE(a.dtype, a.out_dtype, a.redop, DEV_CALL);
+#undef DEV_CALL
+  } else {
+    dev::coll_kernel<unsigned char, unsigned char, kSum, false><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+  }
+  if (!ok) return fail(kInvalidArgument, "unsupported datatype %d -> %d with operator %d", a.dtype, a.out_dtype, a.redop);
+  return check_launch("collective");
+}
+
+template <typename K>
+static Status coop_launch(K kernel, dim3 grid, dim3 block, void** params, cudaStream_t stream, const char* what) {
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)kernel, grid, block, params, 0, stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(kCudaError, "%s cooperative launch (%u x %u blocks) failed: %s", what, grid.x, grid.y, cudaGetErrorString(e));
+  }
+  return kSuccess;
+}
+
+Status launch_collective_emu(const CollArgs* dev_all, const CollArgs& a, int nranks, const LaunchPlan& plan, cudaStream_t stream) {
+  dim3 block(plan.threads);
+  if (a.kind == kCollSendRecv) {
+    // `plan.blocks` carries the maximum (entry, lane) count over the ranks.
+    dim3 grid(plan.blocks, nranks);
+    void* params[] = {(void*)&dev_all};
+    return coop_launch(dev::sendrecv_kernel_emu, grid, block, params, stream, "sendrecv(emu)");
+  }
+  dim3 grid(plan.blocks, nranks);
+  size_t chunk = plan.chunk_elems;
+  void* params[] = {(void*)&dev_all, (void*)&chunk};
+  bool ok = true;
+  Status st = kSuccess;
+  bool reducing = a.kind == kCollAllReduce || a.kind == kCollReduceScatter || a.kind == kCollReduce;
+  if (reducing) {
+#define EMU_CALL(TI, TO, OP) st = coop_launch(dev::coll_kernel_emu<TI, TO, OP, true>, grid, block, params, stream, "collective(emu)")
+    AMEM_DISPATCH_REDUCE(a.dtype, a.out_dtype, a.redop, EMU_CALL);
+#undef EMU_CALL
+  } else {
+    st = coop_launch(dev::coll_kernel_emu<unsigned char, unsigned char, kSum, false>, grid, block, params, stream, "collective(emu)");
+  }
+  if (!ok) return fail(kInvalidArgument, "unsupported datatype %d -> %d with operator %d", a.dtype, a.out_dtype, a.redop);
+  return st;
+}
+
+}  // namespace amem

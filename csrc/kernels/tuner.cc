@@ -1,0 +1,77 @@
+// Variant picker: one-shot / two-shot / NVLS for all-reduce, grid size and chunking for
+// everything.  The thresholds were set from bus-bandwidth sweeps on 8 x B200 over NVSwitch;
+// AMEM_ALGO (oneshot|twoshot|nvls), AMEM_ONESHOT_MAX_KB and AMEM_BLOCKS override them.
+#include <algorithm>
+#include <cstring>
+
+#include "../core/log.h"
+#include "launch.h"
+
+namespace amem {
+
+static int env_algo() {
+  static int v = [] {
+    std::string s = env_str("AMEM_ALGO", "");
+    if (s == "oneshot") return (int)kAlgoOneShot;
+    if (s == "twoshot") return (int)kAlgoTwoShot;
+    if (s == "nvls") return (int)kAlgoNvls;
+    return (int)kAlgoAuto;
+  }();
+  return v;
+}
+
+LaunchPlan plan_collective(const TunerInput& in) {
+  LaunchPlan p;
+  p.threads = 512;
+  p.algo = kAlgoAuto;
+  const size_t es = dtype_size(in.dtype);
+  const int n = in.nranks;
+  const size_t Q = quarter_bytes(in.stage_bytes, in.p2p_slot_bytes);
+  const size_t slot = slot_bytes_of(Q, n);
+  static const long oneshot_kb = env_long("AMEM_ONESHOT_MAX_KB", 256);
+  static const long blocks_env = env_long("AMEM_BLOCKS", 0);
+  size_t bytes = in.count * es;  // payload that defines the work of one rank
+  switch (in.kind) {
+    case kCollAllGather: case kCollAllToAll: bytes *= (size_t)n; break;
+    case kCollReduceScatter: bytes *= (size_t)n; break;
+    default: break;
+  }
+  if (in.kind == kCollAllReduce) {
+    int want = in.forced_algo != kAlgoAuto ? in.forced_algo : env_algo();
+    bool nvls_ok = in.nvls && n > 1 && (in.redop == kSum || in.redop == kAvg) &&
+                   (in.dtype == kF32 || in.dtype == kBF16 || in.dtype == kF16);
+    size_t one_max = std::min(slot, (size_t)oneshot_kb << 10);
+    if (want == kAlgoNvls && !nvls_ok) want = kAlgoAuto;
+    if (want == kAlgoOneShot && in.count * es > slot) want = kAlgoAuto;
+    if (want == kAlgoAuto) {
+      if (in.count * es <= one_max) want = kAlgoOneShot;
+      else if (nvls_ok) want = kAlgoNvls;
+      else want = kAlgoTwoShot;
+    }
+    p.algo = want;
+  }
+  // Grid: one block per 32 KiB of work up to the communicator's cap; latency-bound sizes use
+  // few blocks because every block waits on its own set of peer flags.
+  size_t per_block = 32 << 10;
+  if (in.kind == kCollAllReduce && p.algo == kAlgoOneShot) per_block = 16 << 10;
+  long blocks = (long)((bytes + per_block - 1) / per_block);
+  if (blocks < 1) blocks = 1;
+  if (blocks > in.max_blocks) blocks = in.max_blocks;
+  if (blocks_env > 0) blocks = std::min<long>(blocks_env, in.max_blocks);
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  p.blocks = (int)blocks;
+  // Chunk: as large as the staging region allows (fewest barriers).
+  const size_t H = 2 * Q;
+  switch (in.kind) {
+    case kCollAllReduce:
+      if (p.algo == kAlgoNvls) p.chunk_elems = H / es;
+      else p.chunk_elems = (slot_bytes_of(H / 2, n) / es) * (size_t)n;
+      break;
+    case kCollBroadcast: p.chunk_elems = Q / es; break;
+    default: p.chunk_elems = slot / es; break;
+  }
+  if (p.chunk_elems == 0) p.chunk_elems = 1;
+  return p;
+}
+
+}  // namespace amem

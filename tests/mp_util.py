@@ -1,0 +1,44 @@
+"""Helpers to run a function as N CPU rank processes over the mock backend."""
+import multiprocessing as mp
+import os
+import traceback
+
+
+def _entry(fn, rank, world, uid, q, env, args):
+    try:
+        os.environ.update(env)
+        res = fn(rank, world, uid, *args)
+        q.put((rank, "ok", res))
+    except BaseException as e:  # noqa: BLE001
+        q.put((rank, "err", f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
+
+
+def run_ranks(fn, world, args=(), env=None, timeout=120, expect_fail=False):
+    """Spawns `world` processes running fn(rank, world, unique_id, *args) with the mock backend.
+    Returns the list of per-rank results (or (status, payload) pairs when expect_fail)."""
+    base_env = {"AMEM_BACKEND": "mock", "GMM_LOG": os.environ.get("GMM_LOG", "2")}
+    base_env.update(env or {})
+    os.environ.update(base_env)
+    from asystem_amem_b200 import get_unique_id
+    uid = get_unique_id()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_entry, args=(fn, r, world, uid, q, base_env, args)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = {}
+    try:
+        for _ in range(world):
+            rank, status, payload = q.get(timeout=timeout)
+            out[rank] = (status, payload)
+    finally:
+        for p in procs:
+            p.join(timeout=10)
+            if p.is_alive():
+                p.kill()
+    if expect_fail:
+        return [out.get(r, ("missing", None)) for r in range(world)]
+    for r in range(world):
+        status, payload = out.get(r, ("missing", None))
+        assert status == "ok", f"rank {r}: {payload}"
+    return [out[r][1] for r in range(world)]
