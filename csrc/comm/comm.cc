@@ -78,7 +78,7 @@ Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cf
                       "(or all ranks in one process on one GPU, which is emulated as a single grid)", r, q, infos[r].dev);
   }
   bool emulate = be_->is_device() && same_proc_dev;
-  if (emulate) emu_ = EmuGroup::get(this->id(), nranks);
+  if (emulate) emu_ = EmuGroup::get(group_key(), nranks);
 
   // Sizes.
   AMEM_TRY(be_->granularity(dev_, &gran_));
@@ -315,10 +315,10 @@ Status Comm::destroy() {
   for (auto& s : extra_) sym_free(&s);
   sym_free(&stage_);
   sym_free(&ctrl_);
-  uint64_t cid = id();
+  uint64_t cid = id(), gkey = group_key();
   Registry::instance().forget_owner(cid);
   emu_.reset();
-  EmuGroup::drop(cid);
+  EmuGroup::drop(gkey);
   delete this;
   return kSuccess;
 }

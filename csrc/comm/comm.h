@@ -53,7 +53,11 @@ class Comm {
   int rank() const { return rank_; }
   int nranks() const { return nranks_; }
   int device() const { return dev_; }
-  uint64_t id() const { return mesh_ ? mesh_->comm_id() : 0; }
+  // Registry owner key: unique per rank object, because several ranks of one communicator may
+  // share a process (and therefore the registry).
+  uint64_t id() const { return mesh_ ? mesh_->comm_id() + 2ull * (uint64_t)rank_ : 0; }
+  // Same on every rank of the communicator.
+  uint64_t group_key() const { return mesh_ ? mesh_->comm_id() : 0; }
   bool emulated() const { return emu_ != nullptr; }
   bool nvls() const { return stage_.mc_va != 0; }
   VmmBackend* backend() const { return be_; }

@@ -4,6 +4,8 @@
 
 #include <algorithm>
 #include <cstring>
+#include <functional>
+#include <thread>
 
 #include "../core/log.h"
 #include "../kernels/launch.h"
@@ -305,6 +307,40 @@ static void accumulate(PauseResumeStats* into, const PauseResumeStats& s, bool p
   }
 }
 
+
+// Runs fn on every live communicator in creation order.  Several ranks of ONE communicator may
+// live in this process (emulated ranks, ncclCommInitAll): their pause/resume steps contain
+// cross-rank barriers, so those ranks run on helper threads side by side.
+static Status for_each_comm_grouped(const std::function<Status(Comm*)>& fn) {
+  std::vector<Comm*> comms = Comm::all();
+  std::vector<uint64_t> order;
+  for (Comm* c : comms)
+    if (std::find(order.begin(), order.end(), c->group_key()) == order.end()) order.push_back(c->group_key());
+  for (uint64_t cid : order) {
+    std::vector<Comm*> members;
+    for (Comm* c : comms)
+      if (c->group_key() == cid) members.push_back(c);
+    if (members.size() == 1) {
+      AMEM_TRY(fn(members[0]));
+      continue;
+    }
+    std::vector<Status> res(members.size(), kSuccess);
+    std::vector<std::string> msgs(members.size());
+    std::vector<std::thread> th;
+    for (size_t i = 0; i < members.size(); ++i) {
+      th.emplace_back([&, i] {
+        if (members[i]->backend()->is_device()) cudaSetDevice(members[i]->device());
+        res[i] = fn(members[i]);
+        if (res[i] != kSuccess) msgs[i] = last_error_slot();
+      });
+    }
+    for (auto& t : th) t.join();
+    for (size_t i = 0; i < members.size(); ++i)
+      if (res[i] != kSuccess) return fail(res[i], "%s", msgs[i].c_str());
+  }
+  return kSuccess;
+}
+
 // Process-wide pause: every communicator in creation order (all ranks created them in the
 // same order, so the per-communicator barriers line up), then allocations that belong to no
 // communicator (ncclMemAlloc).  New allocations are refused until resume.
@@ -316,17 +352,20 @@ Status Comm::pause_all(PauseResumeStats* st) {
   VmmBackend* be = nullptr;
   int dev = 0;
   bool first = true;
-  for (Comm* c : all()) {
+  std::mutex acc_mu;
+  AMEM_TRY(for_each_comm_grouped([&](Comm* c) -> Status {
     PauseResumeStats s;
     memset(&s, 0, sizeof(s));
     AMEM_TRY(c->pause(&s));
+    std::lock_guard<std::mutex> g(acc_mu);
     if (first) total.free_before_pause = s.free_before_pause;
     first = false;
     total.free_after_pause = s.free_after_pause;
     accumulate(&total, s, true);
     be = c->backend();
     dev = c->device();
-  }
+    return kSuccess;
+  }));
   if (!be) be = default_backend();
   if (be) {
     if (be->is_device()) cudaGetDevice(&dev);
@@ -355,18 +394,21 @@ Status Comm::resume_all(PauseResumeStats* st) {
   reg.set_process_paused(false);
   VmmBackend* be = nullptr;
   int dev = 0;
-  for (Comm* c : all()) {
+  std::mutex acc_mu;
+  Status all_st = for_each_comm_grouped([&](Comm* c) -> Status {
     PauseResumeStats s;
     memset(&s, 0, sizeof(s));
-    Status r = c->resume(&s);
-    if (r != kSuccess) {
-      reg.set_process_paused(true);
-      return r;
-    }
+    AMEM_TRY(c->resume(&s));
+    std::lock_guard<std::mutex> g(acc_mu);
     total.free_after_resume = s.free_after_resume;
     accumulate(&total, s, false);
     be = c->backend();
     dev = c->device();
+    return kSuccess;
+  });
+  if (all_st != kSuccess) {
+    reg.set_process_paused(true);
+    return all_st;
   }
   if (!be) be = default_backend();
   if (be && reg.owner_state(0) == kRunPaused) {

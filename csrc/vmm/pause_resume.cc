@@ -115,7 +115,7 @@ Status pause_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, PeerE
     AMEM_TRY(px->barrier());
   }
   reg.set_owner_state(owner, kRunPaused);
-  reg.count_pause();
+  if (st->n_release_local + st->n_release_peer > 0) reg.count_pause();  // empty scopes do not count
   be->mem_info(dev, &free_b, &total_b);
   st->free_after_pause = free_b;
   st->pause_total_us = (now_ms() - t_begin) * 1000.0;
@@ -246,7 +246,7 @@ Status resume_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, Peer
     AMEM_TRY(px->barrier());
   }
   reg.set_owner_state(owner, kRunResumed);
-  reg.count_resume();
+  if (!made.empty() || st->bytes_preloaded > 0) reg.count_resume();
   size_t free_b = 0, total_b = 0;
   be->mem_info(dev, &free_b, &total_b);
   st->free_after_resume = free_b;

@@ -27,10 +27,23 @@ def run_ranks(fn, world, args=(), env=None, timeout=120, expect_fail=False):
     for p in procs:
         p.start()
     out = {}
+    import queue as _queue
+    import time as _time
+    deadline = _time.monotonic() + timeout
     try:
-        for _ in range(world):
-            rank, status, payload = q.get(timeout=timeout)
-            out[rank] = (status, payload)
+        while len(out) < world and _time.monotonic() < deadline:
+            try:
+                rank, status, payload = q.get(timeout=0.25)
+                out[rank] = (status, payload)
+            except _queue.Empty:
+                # a rank that exited without reporting will never report
+                if all((not p.is_alive()) for r, p in enumerate(procs) if r not in out):
+                    try:
+                        while True:
+                            rank, status, payload = q.get(timeout=0.25)
+                            out[rank] = (status, payload)
+                    except _queue.Empty:
+                        break
     finally:
         for p in procs:
             p.join(timeout=10)

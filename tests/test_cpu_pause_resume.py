@@ -1,0 +1,156 @@
+"""Pause / resume over the mock VMM backend: the plumbing configuration of the baseline
+(world_size 2 over gloo, allreduce of 1,048,576 fp32 N(0,1) values seeded per rank, ten
+pause/resume cycles, bitwise-equal results, no leaked allocations) plus scope, idempotence,
+guard and split-communicator behaviour."""
+import os
+
+import numpy as np
+import pytest
+
+from mp_util import run_ranks
+
+
+def _config1(rank, world, uid, port):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from asystem_amem_b200 import Communicator, backend_usage, mem_stats, pause_all, resume_all
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    comm = Communicator.from_torch_distributed()
+    g = torch.Generator().manual_seed(rank)  # "seed 0 per rank" stream: seed = rank
+    x = torch.randn(1048576, generator=g, dtype=torch.float32)
+    ref = x.clone()
+    dist.all_reduce(ref)  # gloo's answer, for a tolerance check
+    out0 = x.clone()
+    comm.all_reduce(out0)
+    close = bool(torch.allclose(out0, ref, rtol=1e-6, atol=1e-6))
+    base = backend_usage()
+    st0 = mem_stats()
+    bitwise = True
+    freed = []
+    for cycle in range(10):
+        pause_all()
+        during = backend_usage()
+        freed.append(base["physical_bytes"] - during["physical_bytes"])
+        assert during["mappings"] == 0, during
+        resume_all()
+        y = x.clone()
+        comm.all_reduce(y)
+        bitwise = bitwise and bool(torch.equal(y, out0))
+    after = backend_usage()
+    st1 = mem_stats()
+    comm.destroy()
+    end = backend_usage()
+    dist.destroy_process_group()
+    return {
+        "close": close, "bitwise": bitwise, "freed": freed,
+        "leak_bytes": after["physical_bytes"] - base["physical_bytes"],
+        "leak_maps": after["mappings"] - base["mappings"],
+        "end_bytes": end["physical_bytes"], "end_maps": end["mappings"],
+        "pauses": st1["pause_count"] - st0["pause_count"],
+        "live": st1["live_bytes"], "paused_bytes": st1["paused_bytes"],
+    }
+
+
+def test_config1_gloo_world2_ten_cycles():
+    port = 29000 + os.getpid() % 2000
+    res = run_ranks(_config1, 2, args=(port,), timeout=300)
+    for r in res:
+        assert r["close"] and r["bitwise"], r
+        assert r["leak_bytes"] == 0 and r["leak_maps"] == 0, r
+        assert r["end_bytes"] == 0 and r["end_maps"] == 0, r
+        assert all(f > 0 and f == r["freed"][0] for f in r["freed"]), r
+        assert r["pauses"] == 10 and r["paused_bytes"] == 0, r
+
+
+def _scope_and_guard(rank, world, uid):
+    import numpy as np
+    from asystem_amem_b200 import Communicator, NcclError, backend_usage, mem_alloc, mem_free, pause_all, resume_all
+    import ctypes
+    comm = Communicator(world, rank, uid)
+    out = {}
+    x = np.arange(1000, dtype=np.float32) + rank
+    exp = sum(np.arange(1000, dtype=np.float32) + r for r in range(world))
+    # user allocation: contents must survive a process-wide pause at the same address
+    p = mem_alloc(1 << 16)
+    buf = (ctypes.c_uint8 * (1 << 16)).from_address(p)
+    for i in range(0, 1 << 16, 997):
+        buf[i] = (i * 7 + rank) & 0xFF
+    # communicator-scoped pause is idempotent and guards collectives
+    comm.pause()
+    comm.pause()
+    try:
+        comm.all_reduce(x.copy())
+        out["guard"] = False
+    except NcclError as e:
+        out["guard"] = e.code == 5
+    comm.resume()
+    comm.resume()
+    y = x.copy()
+    comm.all_reduce(y)
+    out["after_scoped"] = bool(np.array_equal(y, exp))
+    pause_all()
+    out["nothing_mapped"] = backend_usage()["mappings"] == 0
+    try:
+        mem_alloc(4096)
+        out["alloc_refused"] = False
+    except NcclError as e:
+        out["alloc_refused"] = e.code == 5
+    resume_all()
+    out["user_contents"] = all(buf[i] == ((i * 7 + rank) & 0xFF) for i in range(0, 1 << 16, 997))
+    y = x.copy()
+    comm.all_reduce(y)
+    out["after_all"] = bool(np.array_equal(y, exp))
+    st = comm.pause_resume_stats()
+    out["stateful_only"] = 0 < st["bytes_offloaded"] < st["bytes_released_local"]
+    mem_free(p)
+    comm.destroy()
+    out["clean"] = backend_usage()["physical_bytes"] == 0
+    return out
+
+
+def test_scope_guard_and_user_memory():
+    for r in run_ranks(_scope_and_guard, 2):
+        assert all(r.values()), r
+
+
+def _split_hybrid(rank, world, uid, cycles):
+    """TP=2 x EP/DP=world/2 split communicators, all paused and resumed together."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator, backend_usage, pause_all, resume_all
+    comm = Communicator(world, rank, uid)
+    tp = comm.split(rank // 2, rank)      # pairs
+    ep = comm.split(rank % 2, rank)       # strided groups
+    none = comm.split(-1 if rank else 0, 0)
+    ok = (tp.nranks == 2 and ep.nranks == world // 2 and (none is None) == (rank != 0))
+    x = np.full(4096, float(rank + 1), dtype=np.float32)
+    def run():
+        a, b, c = x.copy(), x.copy(), x.copy()
+        comm.all_reduce(a)
+        tp.all_reduce(b)
+        ep.all_reduce(c)
+        return a, b, c
+    first = run()
+    exp_world = sum(range(1, world + 1))
+    base = (rank // 2) * 2
+    exp_tp = (base + 1) + (base + 2)
+    exp_ep = sum(r + 1 for r in range(world) if r % 2 == rank % 2)
+    ok = ok and first[0][0] == exp_world and first[1][0] == exp_tp and first[2][0] == exp_ep
+    usage0 = backend_usage()["physical_bytes"]
+    for _ in range(cycles):
+        pause_all()
+        assert backend_usage()["mappings"] == 0
+        resume_all()
+        again = run()
+        ok = ok and all(np.array_equal(p, q) for p, q in zip(first, again))
+    ok = ok and backend_usage()["physical_bytes"] == usage0
+    for c in (none, ep, tp, comm):
+        if c is not None:
+            c.destroy()
+    return bool(ok)
+
+
+def test_split_communicators_pause_together():
+    assert all(run_ranks(_split_hybrid, 4, args=(5,), env={"AMEM_STAGE_MB": "8"}))
