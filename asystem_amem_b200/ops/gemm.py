@@ -1,0 +1,58 @@
+"""Tensor-core GEMMs of the library (hand-written tcgen05 / TMEM / TMA kernels).
+
+All take bf16 CUDA tensors with K contiguous: ``a`` is [M, K] (activations), ``b`` is [N, K]
+(a ``torch.nn.Linear`` weight), the result is [M, N] = a @ b.T in bf16 with fp32 accumulation.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import bindings as B
+
+
+def _check(a: torch.Tensor, b: torch.Tensor) -> None:
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise TypeError("bf16 tensors expected")
+    if not (a.is_cuda and b.is_cuda and a.is_contiguous() and b.is_contiguous()):
+        raise ValueError("contiguous CUDA tensors expected")
+    if a.shape[-1] != b.shape[-1]:
+        raise ValueError(f"inner dimensions differ: {tuple(a.shape)} vs {tuple(b.shape)}")
+
+
+def _stream(stream) -> int:
+    return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ b[N, K].T on one GPU."""
+    _check(a, b)
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device) if out is None else out
+    lib = B.load_library()
+    B.check(lib.amemGemmBf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, _stream(stream)), "amemGemmBf16")
+    return out
+
+
+def all_gather_gemm(comm, a_shard: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """out[M, N] = all_gather_rows(a_shard)[M, K] @ b[N, K].T in ONE kernel (column-parallel
+    linear under sequence parallelism).  ``a_shard`` holds this rank's M / nranks rows."""
+    _check(a_shard, b)
+    m_local, K = a_shard.shape
+    M, N = m_local * comm.nranks, b.shape[0]
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=a_shard.device) if out is None else out
+    B.check(comm.lib.amemAllGatherGemm(a_shard.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, comm._h, _stream(stream)),
+            "amemAllGatherGemm")
+    return out
+
+
+def gemm_reduce_scatter(comm, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
+    """out[M / nranks, N] = reduce_scatter_rows(a[M, K_local] @ b[N, K_local].T) in ONE kernel
+    (row-parallel linear under sequence parallelism)."""
+    _check(a, b)
+    M, K = a.shape
+    N = b.shape[0]
+    out = torch.empty(M // comm.nranks, N, dtype=torch.bfloat16, device=a.device) if out is None else out
+    B.check(comm.lib.amemGemmReduceScatter(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, comm._h, _stream(stream)),
+            "amemGemmReduceScatter")
+    return out

@@ -1,0 +1,184 @@
+// C entry points of the fused compute + collective operations (tensor-parallel GEMMs).
+// The reference has no counterpart: its tensor-parallel users call cuBLAS and NCCL back to
+// back; here the collective rides inside the GEMM kernel (kernels/gemm_sm100.cu).
+#include <cuda_runtime.h>
+
+#include <cstring>
+#include <vector>
+
+#include "../comm/comm.h"
+#include "../comm/emu.h"
+#include "../core/log.h"
+#include "../include/nccl.h"
+#include "../kernels/gemm_sm100.h"
+
+using namespace amem;
+
+namespace {
+
+inline ncclResult_t R(Status s) {
+  if (s != kSuccess) LOGW("%s: %s", status_name(s), last_error_slot().c_str());
+  return (ncclResult_t)s;
+}
+
+Status check_shape(int M, int N, int K) {
+  if (M <= 0 || N <= 0 || K <= 0) return fail(kInvalidArgument, "empty GEMM %d x %d x %d", M, N, K);
+  if (N % 8 || K % 8) return fail(kInvalidArgument, "N and K must be multiples of 8 (16-byte rows), got N=%d K=%d", N, K);
+  return kSuccess;
+}
+
+void fill_fused(Comm* c, GemmParams* p) {
+  c->fill_args(&p->coll);
+  for (int r = 0; r < c->nranks(); ++r) p->fflags[r] = (FusedFlags*)c->fused_flags(r);
+}
+
+Status run_gemm(Comm* c, GemmLaunch& g, cudaStream_t stream) {
+  if (c && c->emulated()) {
+    int n = c->nranks();
+    return c->emu()->rendezvous(c->rank(), 1000 + g.p.mode, &g, sizeof(g), stream,
+                                [n](const void* host_all, const void*, cudaStream_t s) { return launch_gemm_emu((const GemmLaunch*)host_all, n, s); });
+  }
+  return launch_gemm(g, stream);
+}
+
+int emu_grid(int nranks) {
+  int sms = gemm_default_grid(0);
+  int per = sms / nranks;  // one CTA per SM and every CTA of every rank must be resident
+  return per < 3 ? 3 : (per > 16 ? 16 : per);
+}
+
+}  // namespace
+
+extern "C" {
+
+ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
+  Status s = check_shape(M, N, K);
+  if (s != kSuccess) return R(s);
+  static thread_local uint32_t dummy_status[kStatusWords];
+  // A communicator-free launch still needs protocol words (epoch, operation counter): a small
+  // private control block per device.
+  static CtrlBlock* ctrl[64] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!ctrl[dev]) {
+    if (cudaMalloc((void**)&ctrl[dev], sizeof(CtrlBlock) + sizeof(FusedFlags)) != cudaSuccess) return ncclUnhandledCudaError;
+    cudaMemset(ctrl[dev], 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
+  }
+  static uint32_t* status_dev[64] = {nullptr};
+  if (!status_dev[dev]) {
+    if (cudaHostAlloc((void**)&status_dev[dev], kStatusWords * 4, cudaHostAllocMapped) != cudaSuccess) return ncclUnhandledCudaError;
+    memset(status_dev[dev], 0, kStatusWords * 4);
+  }
+  (void)dummy_status;
+  GemmLaunch g;
+  memset(&g, 0, sizeof(g));
+  g.p.M = M;
+  g.p.N = N;
+  g.p.K = K;
+  g.p.mode = kGemmPlain;
+  g.p.C = C;
+  g.p.ldc = N;
+  g.p.rows_per_rank = M;
+  g.p.coll.rank = 0;
+  g.p.coll.nranks = 1;
+  g.p.coll.ctrl[0] = ctrl[dev];
+  g.p.coll.status = status_dev[dev];
+  g.p.coll.timeout_ns = 5ull * 1000000000ull;
+  g.p.fflags[0] = (FusedFlags*)(ctrl[dev] + 1);
+  if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);
+  g.map_a_local = g.map_a;
+  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
+  int tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + kGemmBN - 1) / kGemmBN);
+  int sms = gemm_default_grid(dev);
+  g.grid = tiles < sms ? tiles : sms;
+  s = launch_gemm(g, stream);
+  if (s == kSuccess && status_dev[dev][0]) s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_dev[dev][0]);
+  return R(s);
+}
+
+// C[M, N] = allgather_rows(a_shard)[M, K] * B[N, K]^T.  Every rank passes its M/nranks rows;
+// B and C are per rank (column-parallel weight shard and its output).
+ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int M, int N, int K, ncclComm_t comm, cudaStream_t stream) {
+  if (!comm) return ncclInvalidArgument;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  Status s = c->check_usable("amemAllGatherGemm");
+  if (s != kSuccess) return R(s);
+  if ((s = check_shape(M, N, K)) != kSuccess) return R(s);
+  int n = c->nranks();
+  if (M % n) return R(fail(kInvalidArgument, "M=%d is not divisible by %d ranks", M, n));
+  int rpr = M / n;
+  if ((rpr + kAgUnitRows - 1) / kAgUnitRows > kMaxUnits) return R(fail(kInvalidArgument, "more than %d rows per rank", kAgUnitRows * kMaxUnits));
+  if ((s = c->prepare_stream(stream)) != kSuccess) return R(s);
+  GemmLaunch g;
+  memset(&g, 0, sizeof(g));
+  fill_fused(c, &g.p);
+  g.p.M = M;
+  g.p.N = N;
+  g.p.K = K;
+  g.p.C = C;
+  g.p.ldc = N;
+  g.p.rows_per_rank = rpr;
+  g.p.a_local = a_shard;
+  if (n == 1) {
+    g.p.mode = kGemmPlain;
+    if ((s = make_tensor_map_bf16(&g.map_a, a_shard, M, K, K, kGemmBM)) != kSuccess) return R(s);
+    g.map_a_local = g.map_a;
+  } else {
+    g.p.mode = kGemmAllGather;
+    Segment* seg = nullptr;
+    if ((s = c->fused_segment(0, (size_t)M * K * 2, &seg)) != kSuccess) return R(s);
+    for (int r = 0; r < n; ++r) g.p.ag_buf[r] = (void*)seg->va[r];
+    if ((s = make_tensor_map_bf16(&g.map_a, g.p.ag_buf[c->rank()], M, K, K, kGemmBM)) != kSuccess) return R(s);
+    if ((s = make_tensor_map_bf16(&g.map_a_local, a_shard, rpr, K, K, kGemmBM)) != kSuccess) return R(s);
+  }
+  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
+  if (c->emulated()) {
+    g.grid = emu_grid(n);
+    g.p.comm_ctas = 1;
+  } else {
+    g.grid = gemm_default_grid(c->device());
+    g.p.comm_ctas = n > 1 ? (int)env_long("AMEM_AG_COMM_CTAS", 16) : 0;
+    if (g.p.comm_ctas > g.grid / 2) g.p.comm_ctas = g.grid / 2;
+  }
+  return R(run_gemm(c, g, stream));
+}
+
+// out[M/nranks, N] = reduce_scatter_rows(A[M, K] * B[N, K]^T): every rank holds a K-slice
+// (row-parallel weight shard) and ends up with its M/nranks rows of the sum.
+ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int M, int N, int K, ncclComm_t comm, cudaStream_t stream) {
+  if (!comm) return ncclInvalidArgument;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  Status s = c->check_usable("amemGemmReduceScatter");
+  if (s != kSuccess) return R(s);
+  if ((s = check_shape(M, N, K)) != kSuccess) return R(s);
+  int n = c->nranks();
+  if (M % n) return R(fail(kInvalidArgument, "M=%d is not divisible by %d ranks", M, n));
+  int rpr = M / n;
+  if ((rpr + kGemmBM - 1) / kGemmBM > kMaxUnits) return R(fail(kInvalidArgument, "more than %d rows per rank", kGemmBM * kMaxUnits));
+  if ((s = c->prepare_stream(stream)) != kSuccess) return R(s);
+  GemmLaunch g;
+  memset(&g, 0, sizeof(g));
+  fill_fused(c, &g.p);
+  g.p.M = M;
+  g.p.N = N;
+  g.p.K = K;
+  g.p.rows_per_rank = rpr;
+  g.p.rs_out = out;
+  if (n == 1) {
+    g.p.mode = kGemmPlain;
+    g.p.C = out;
+    g.p.ldc = N;
+  } else {
+    g.p.mode = kGemmReduceScatter;
+    Segment* seg = nullptr;
+    if ((s = c->fused_segment(1, (size_t)M * N * 2, &seg)) != kSuccess) return R(s);
+    for (int r = 0; r < n; ++r) g.p.rs_buf[r] = (void*)seg->va[r];
+  }
+  if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);
+  g.map_a_local = g.map_a;
+  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
+  g.grid = c->emulated() ? emu_grid(n) : gemm_default_grid(c->device());
+  return R(run_gemm(c, g, stream));
+}
+
+}  // extern "C"

@@ -200,6 +200,25 @@ Status Comm::sym_alloc(size_t size, int category, int tag, Segment* out) {
   return kSuccess;
 }
 
+Status Comm::fused_segment(int which, size_t bytes, Segment** out) {
+  if (which < 0 || which >= 4) return fail(kInvalidArgument, "fused segment index %d", which);
+  Segment& s = fused_[which];
+  if (s.window && s.size >= bytes) {
+    *out = &s;
+    return kSuccess;
+  }
+  // Grow: every rank takes this path in the same call (sizes derive from the call's shape).
+  if (s.window) {
+    if (be_->is_device()) AMEM_TRY(be_->device_sync(dev_));
+    if (nranks_ > 1) AMEM_TRY(mesh_->barrier());  // peers are done with the old mapping
+    AMEM_TRY(sym_free(&s));
+  }
+  AMEM_TRY(sym_alloc(bytes, kScratch, kTagSymm, &s));
+  if (nranks_ > 1) AMEM_TRY(mesh_->barrier());
+  *out = &s;
+  return kSuccess;
+}
+
 Status Comm::sym_free(Segment* seg) {
   Registry& reg = Registry::instance();
   for (int r = 0; r < nranks_; ++r) {
@@ -312,7 +331,8 @@ Status Comm::destroy() {
   if (be_->is_device()) be_->device_sync(dev_);
   // Peers must be done with my memory before I unmap it.
   if (!aborted_ && mesh_ && nranks_ > 1) mesh_->barrier();
-  for (auto& s : extra_) sym_free(&s);
+  for (auto& s : fused_)
+    if (s.window) sym_free(&s);
   sym_free(&stage_);
   sym_free(&ctrl_);
   uint64_t cid = id(), gkey = group_key();

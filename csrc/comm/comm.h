@@ -93,6 +93,13 @@ class Comm {
   Status sym_alloc(size_t size, int category, int tag, Segment* out);
   Status sym_free(Segment* seg);
 
+  // Cached scratch segments of the fused kernels (0: gathered activations, 1: reduce-scatter
+  // partial slots, 2: MoE receive buffers, 3: MoE return buffers); grown collectively when a
+  // call needs more.
+  Status fused_segment(int which, size_t bytes, Segment** out);
+  // Address, in this process, of rank r's fused-kernel flag area (inside its control segment).
+  void* fused_flags(int r) const { return (void*)(ctrl_.va[r] + ((sizeof(CtrlBlock) + 255) & ~(size_t)255)); }
+
   // Process-wide operations over every live communicator, in creation order.
   static Status pause_all(PauseResumeStats* st);
   static Status resume_all(PauseResumeStats* st);
@@ -110,7 +117,7 @@ class Comm {
   Mesh* mesh_ = nullptr;
   int rank_ = 0, nranks_ = 1, dev_ = 0;
   Segment ctrl_, stage_;
-  std::vector<Segment> extra_;
+  Segment fused_[4];
   uint32_t next_sym_ = 1;
   size_t p2p_slot_bytes_ = 0;
   size_t gran_ = 0;

@@ -174,6 +174,16 @@ ncclResult_t amemReduceScatterScaleCast(const void* sendbuff, void* recvbuff, si
 /* All-reduce with a forced variant: 1 one-shot, 2 two-shot, 3 NVLS (0 lets the tuner pick). */
 ncclResult_t amemAllReduceAlgo(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op,
                                int algo, ncclComm_t comm, cudaStream_t stream);
+/* tcgen05 GEMM, bf16 in / fp32 accumulate / bf16 out: C[M,N] = A[M,K] * B[N,K]^T (both operands
+ * row-major with K contiguous, the layout of activations and of Linear weights).  N and K must
+ * be multiples of 8. */
+ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream);
+/* One kernel: C[M,N] = allgather_rows(a_shard)[M,K] * B[N,K]^T.  a_shard holds this rank's
+ * M/nranks rows; the transfer of the other ranks' rows overlaps the tensor-core work. */
+ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int M, int N, int K, ncclComm_t comm, cudaStream_t stream);
+/* One kernel: out[M/nranks,N] = reduce_scatter_rows(A[M,K] * B[N,K]^T); partial tiles travel
+ * to their owner from the epilogue and are summed there in rank order. */
+ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int M, int N, int K, ncclComm_t comm, cudaStream_t stream);
 /* 1 if the communicator's ranks share one GPU and run as one cooperative grid; 1 if NVLS is in use. */
 ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* stage_bytes);
 /* Host-side fault injection for tests: what = "uds:drop" | "uds:short" | "uds:nofd" |

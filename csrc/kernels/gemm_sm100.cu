@@ -1,0 +1,501 @@
+// tcgen05 / TMEM / TMA GEMM for sm_100a, alone and fused with its neighbouring collective.
+//
+//   plain            C = A * B^T
+//   all-gather->GEMM  A's row shards live on different ranks.  A few CTAs of the same kernel
+//                    stream this rank's shard into every peer's gathered buffer with bulk
+//                    async copies (global -> shared once, shared -> each peer) and announce
+//                    every 32 rows with a flag; the compute CTAs start on the local shard at
+//                    once and pick up remote row blocks in the order they arrive.
+//   GEMM->reduce-scatter  each output row block belongs to one rank.  The epilogue stores
+//                    bf16 partial tiles straight into the owner's slot buffer over NVLink and
+//                    counts them in; when a CTA runs out of tiles it reduces finished row
+//                    blocks of its own shard in fixed rank order (deterministic).
+//
+// One CTA per SM, persistent over tiles of 128 x 256, K step 64, 4-stage TMA ring, one elected
+// thread issues tcgen05.mma (kind::f16, M128 N256 K16) into one of two 256-column TMEM
+// accumulators so the epilogue of tile i overlaps the main loop of tile i+1.  TMA loads never
+// use cluster multicast and only ever read this GPU's own memory; peers are reached with plain
+// or bulk stores.  Every wait is bounded and ends in an error status, not a hang.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+
+#include "../core/log.h"
+#include "coll_device.cuh"
+#include "gemm_sm100.h"
+#include "sm100_prims.cuh"
+
+namespace amem {
+namespace gemmk {
+
+using namespace sm100;
+
+constexpr int BM = kGemmBM, BN = kGemmBN, BK = kGemmBK, STAGES = kGemmStages;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int UMMA_K = 16;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy of the all-gather mover
+
+struct __align__(8) SmemCtl {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint64_t copy_full[STAGES];
+  uint32_t tmem_base;
+  int abort;
+  int s_abort_coll;
+};
+
+struct Tile {
+  int shard;      // owner rank of the rows (0 when not fused)
+  int m_in;       // row-block index inside the shard
+  int n_blk;
+};
+
+// Tile order.  plain: row blocks fastest (CTAs that run together share the B tile in L2).
+// all-gather: the local shard first, then row block by row block across the source ranks
+// nearest-sender first, the order in which the movers deliver.  reduce-scatter: remote
+// owners first (rank+1, rank+2, ...), my own rows last.
+__device__ __forceinline__ Tile tile_of(const GemmParams& p, int t, int tiles_m, int tiles_n) {
+  const int n = p.coll.nranks, r = p.coll.rank;
+  Tile o;
+  if (p.mode == kGemmAllGather && n > 1) {
+    int own = tiles_m * tiles_n;
+    if (t < own) {
+      o.shard = r;
+      o.m_in = t % tiles_m;
+      o.n_blk = t / tiles_m;
+    } else {
+      int u = t - own;
+      int per_m = (n - 1) * tiles_n;
+      o.m_in = u / per_m;
+      int v = u % per_m;
+      o.shard = (r - 1 - (v % (n - 1)) + 2 * n) % n;
+      o.n_blk = v / (n - 1);
+    }
+  } else {
+    int per_shard = tiles_m * tiles_n;
+    int s = t / per_shard, v = t % per_shard;
+    o.shard = (p.mode == kGemmReduceScatter && n > 1) ? (r + 1 + s) % n : s;
+    o.m_in = v % tiles_m;
+    o.n_blk = v / tiles_m;
+  }
+  return o;
+}
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// ---- all-gather mover: one thread per CTA drives bulk copies through the (otherwise unused)
+// operand ring; unit = kAgUnitRows rows of my shard, contiguous in memory.
+__device__ void ag_mover(const GemmParams& p, char* ring, SmemCtl* ctl, int cta, uint32_t epoch) {
+  const int n = p.coll.nranks, r = p.coll.rank;
+  const size_t row_bytes = (size_t)p.K * 2;
+  const int units = (p.rows_per_rank + kAgUnitRows - 1) / kAgUnitRows;
+  const char* src = (const char*)p.a_local;
+  uint32_t phase_bits = 0;  // parity of copy_full[s], one bit per stage
+  int stage = 0;
+  for (int u = cta; u < units; u += p.comm_ctas) {
+    int rows = min(kAgUnitRows, p.rows_per_rank - u * kAgUnitRows);
+    size_t bytes = (size_t)rows * row_bytes;
+    size_t off0 = (size_t)u * kAgUnitRows * row_bytes;
+    size_t dst_off = (size_t)r * p.rows_per_rank * row_bytes + off0;
+    for (size_t o = 0; o < bytes; o += COPY_PIECE) {
+      uint32_t len = (uint32_t)min((size_t)COPY_PIECE, bytes - o);
+      char* buf = ring + (size_t)stage * STAGE_BYTES;
+      // the stores that last read this buffer were drained by wait_group.read below
+      mbar_expect_tx(&ctl->copy_full[stage], len);
+      bulk_g2s(buf, src + off0 + o, len, &ctl->copy_full[stage]);
+      if (!mbar_wait(&ctl->copy_full[stage], (phase_bits >> stage) & 1u, p.coll.timeout_ns, &ctl->abort)) return;
+      phase_bits ^= 1u << stage;
+      for (int k = 1; k < n; ++k) {
+        int q = (r + k) % n;
+        bulk_s2g((char*)p.ag_buf[q] + dst_off + o, buf, len);
+      }
+      if (p.copy_own) bulk_s2g((char*)p.ag_buf[r] + dst_off + o, buf, len);
+      bulk_commit();
+      stage = (stage + 1) % STAGES;
+      if (stage == 0) bulk_wait_read0();  // ring wrapped: sources must have been read
+    }
+    bulk_wait_all();  // this unit's bytes have been written
+    __threadfence_system();
+    for (int k = 1; k < n; ++k) {
+      int q = (r + k) % n;
+      dev::st_release_sys(&p.fflags[q]->ag_ready[r][u], epoch);
+    }
+    if (p.copy_own) dev::st_release_sys(&p.fflags[r]->ag_ready[r][u], epoch);
+  }
+}
+
+// ---- reduce phase of GEMM -> reduce-scatter: out = sum over source slots, fixed order.
+__device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas, int tiles_m, int tiles_n) {
+  const int n = p.coll.nranks, r = p.coll.rank;
+  const int tid = threadIdx.x;
+  const FusedFlags* mine = p.fflags[r];
+  const __nv_bfloat16* slots = (const __nv_bfloat16*)p.rs_buf[r];
+  __nv_bfloat16* out = (__nv_bfloat16*)p.rs_out;
+  const size_t slot_elems = (size_t)p.rows_per_rank * p.N;
+  const uint32_t per_call = (uint32_t)tiles_n * 4u;  // four epilogue warps count each tile in
+  for (int item = cta; item < tiles_m * tiles_n; item += nctas) {
+    int m_in = item % tiles_m, n_blk = item / tiles_m;
+    if (tid < n) {
+      uint32_t want = dev::ld_volatile(&mine->rs_expect[tid][m_in]) + per_call;
+      if (!ctl->abort && !dev::wait_flag_ge(&mine->rs_done[tid][m_in], want, p.coll.timeout_ns)) {
+        dev::report_error(p.coll.status, kDevGemmTimeout, r, tid, m_in, want);
+        ctl->abort = 1;
+      }
+    }
+    __syncthreads();
+    int row0 = m_in * BM, col0 = n_blk * BN;
+    int rows = min(BM, p.rows_per_rank - row0);
+    int cols = min(BN, p.N - col0);
+    int vec_per_row = cols / 8;  // N % 8 == 0
+    for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
+      int rr = i / vec_per_row, cv = i % vec_per_row;
+      size_t e = (size_t)(row0 + rr) * p.N + col0 + cv * 8;
+      float acc[8];
+      uint4 raw[kMaxRanks];
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s)
+        if (s < n) raw[s] = *(const uint4*)(slots + (size_t)s * slot_elems + e);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s) {
+        if (s < n) {
+          const __nv_bfloat16* h = (const __nv_bfloat16*)&raw[s];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(h[j]);
+        }
+      }
+      alignas(16) __nv_bfloat16 res[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) res[j] = __float2bfloat16_rn(acc[j]);
+      *(uint4*)(out + e) = *(const uint4*)res;
+    }
+    __syncthreads();
+  }
+}
+
+// ---- the kernel body, shared by the one-rank-per-GPU kernel and the emulation kernel -------
+__device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const CUtensorMap* map_a_local, const CUtensorMap* map_b,
+                          int cta, int nctas, char* smem_raw) {
+  // operand ring first (1024-byte aligned for the 128-byte swizzle), control words after it
+  char* ring = (char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  SmemCtl* ctl = (SmemCtl*)(ring + (size_t)STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int n = p.coll.nranks, r = p.coll.rank;
+  const bool fused = n > 1 && p.mode != kGemmPlain;
+  volatile int* abort = &ctl->abort;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&ctl->full[s], 1);
+      mbar_init(&ctl->empty[s], 1);
+      mbar_init(&ctl->copy_full[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&ctl->tfull[b], 1);
+      mbar_init(&ctl->tempty[b], 4);
+    }
+    ctl->abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(map_a);
+    tma_prefetch_desc(map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  // protocol state of this launch (epochs, operation counter)
+  dev::Proto proto;
+  dev::proto_begin(proto, p.coll, cta, nctas, &ctl->s_abort_coll);  // contains a __syncthreads
+  tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const uint32_t epoch = proto.opseq + 1u;  // value of this launch's all-gather ready flags
+
+  const int comm_ctas = (p.mode == kGemmAllGather && fused) ? p.comm_ctas : 0;
+  const bool is_mover = cta < comm_ctas;
+  // Cross-launch guard: before anything of this launch lands in a peer's buffer, the peer must
+  // have left the previous launch (it signals this barrier only after starting this one).
+  if (fused && (is_mover || p.mode == kGemmReduceScatter)) dev::block_barrier(proto);
+
+  const int tiles_m = (p.rows_per_rank + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int shards = (p.mode == kGemmPlain || n == 1) ? 1 : n;
+  const int total_tiles = tiles_m * tiles_n * shards;
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int g = cta - comm_ctas, G = nctas - comm_ctas;  // compute CTA index / count
+  const uint32_t idesc = make_idesc_bf16(BM, BN);
+
+  if (is_mover) {
+    if (threadIdx.x == 0) ag_mover(p, ring, ctl, cta, epoch);
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, issued = 0, issued_phase = 0;
+      bool ok = true;
+      for (int t = g; t < total_tiles && ok; t += G) {
+        Tile tl = tile_of(p, t, tiles_m, tiles_n);
+        const bool remote = p.mode == kGemmAllGather && fused && tl.shard != r;
+        if (remote) {
+          // wait for every 32-row unit this 128-row tile covers
+          int u0 = tl.m_in * (BM / kAgUnitRows);
+          int u1 = min(u0 + BM / kAgUnitRows, (p.rows_per_rank + kAgUnitRows - 1) / kAgUnitRows);
+          for (int u = u0; u < u1 && ok; ++u) {
+            if (*abort || !dev::wait_flag_ge(&p.fflags[r]->ag_ready[tl.shard][u], epoch, p.coll.timeout_ns)) {
+              dev::report_error(p.coll.status, kDevGemmTimeout, r, tl.shard, u, epoch);
+              *abort = 1;
+              ok = false;
+            }
+          }
+          fence_proxy_async();  // peers' stores -> my TMA reads
+        }
+        const CUtensorMap* ma = (p.mode == kGemmAllGather && fused && !remote) ? map_a_local : map_a;
+        int row0 = tl.m_in * BM + ((p.mode == kGemmAllGather && fused && !remote) ? 0 : tl.shard * p.rows_per_rank);
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(&ctl->empty[stage], phase ^ 1u, p.coll.timeout_ns, abort);
+          if (!ok) break;
+          mbar_expect_tx(&ctl->full[stage], STAGE_BYTES);
+          tma_load_2d(ring + (size_t)stage * STAGE_BYTES, ma, &ctl->full[stage], kb * BK, row0);
+          tma_load_2d(ring + (size_t)stage * STAGE_BYTES + A_BYTES, map_b, &ctl->full[stage], kb * BK, tl.n_blk * BN);
+          issued |= 1u << stage;
+          issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // gave up: let the copies already in flight land before the CTA exits
+        dev::report_error(p.coll.status, kDevGemmTimeout, r, r, cta, 0xdead0001u);
+        for (int s = 0; s < STAGES; ++s) {
+          if (!(issued & (1u << s))) continue;
+          for (int i = 0; i < 100000 && !mbar_try_wait(&ctl->full[s], (issued_phase >> s) & 1u); ++i) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = g; t < total_tiles && ok; t += G, ++it) {
+        const int buf = it & 1;
+        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        ok = mbar_wait(&ctl->tempty[buf], acc_phase ^ 1u, p.coll.timeout_ns, abort);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&ctl->full[stage], phase, p.coll.timeout_ns, abort);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint64_t da = make_smem_desc_sw128(ring + (size_t)stage * STAGE_BYTES);
+          const uint64_t db = make_smem_desc_sw128(ring + (size_t)stage * STAGE_BYTES + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            // 16 bf16 = 32 bytes further along K inside the 128-byte swizzled row
+            tc_mma_f16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) ? 1u : 0u);
+          }
+          tc_commit(&ctl->empty[stage]);  // frees the stage when these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) tc_commit(&ctl->tfull[buf]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int lane_grp = warp % 4;  // TMEM lanes [32 * lane_grp, +32) belong to this warp
+    int it = 0;
+    bool ok = true;
+    for (int t = g; t < total_tiles && ok; t += G, ++it) {
+      Tile tl = tile_of(p, t, tiles_m, tiles_n);
+      const int buf = it & 1;
+      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      ok = mbar_wait(&ctl->tfull[buf], acc_phase, p.coll.timeout_ns, abort);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row_in = tl.m_in * BM + lane_grp * 32 + lane;  // row inside the shard
+      const bool row_ok = row_in < p.rows_per_rank;
+      __nv_bfloat16* dst_row;
+      int ld;
+      if (p.mode == kGemmReduceScatter && fused) {
+        // partial tile goes to the owner's slot number `r`
+        ld = p.N;
+        dst_row = (__nv_bfloat16*)p.rs_buf[tl.shard] + ((size_t)r * p.rows_per_rank + row_in) * ld;
+      } else {
+        ld = p.ldc;
+        dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * ld;
+      }
+      const uint32_t t_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_grp * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
+        tmem_ld_wait();
+        const int col = tl.n_blk * BN + c * 32;
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (col + j * 8 < p.N) {
+              alignas(16) __nv_bfloat162 h[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                h[q] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]), __uint_as_float(v[j * 8 + 2 * q + 1]));
+              *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
+      if (p.mode == kGemmReduceScatter && fused) {
+        // everything this warp stored for the tile is visible before the count
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(&p.fflags[tl.shard]->rs_done[r][tl.m_in], 1u);
+      }
+    }
+  }
+
+  __syncthreads();
+  if (p.mode == kGemmReduceScatter && fused) rs_reduce(p, ctl, cta, nctas, tiles_m, tiles_n);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (threadIdx.x == 0) {
+    if (*abort) dev::report_error(p.coll.status, kDevGemmTimeout, r, r, cta, 0xdead0002u);
+  }
+  // A single-rank launch keeps no protocol state (launches on different streams may overlap).
+  if (threadIdx.x == 0 && n > 1) {
+    CtrlBlock* me = p.coll.ctrl[r];
+    me->epoch[cta] = proto.epoch;
+    __threadfence();
+    uint32_t ticket = atomicAdd(&me->done_blocks, 1u);
+    if (ticket == (uint32_t)nctas - 1) {  // last CTA of this rank: close the operation
+      me->done_blocks = 0;
+      if (p.mode == kGemmReduceScatter && fused) {
+        FusedFlags* f = p.fflags[r];
+        for (int s = 0; s < n; ++s)
+          for (int m = 0; m < tiles_m; ++m) f->rs_expect[s][m] += (uint32_t)tiles_n * 4u;
+      }
+      me->opseq = proto.opseq + 1u;
+      __threadfence();
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
+            const __grid_constant__ CUtensorMap map_a_local, const __grid_constant__ CUtensorMap map_b) {
+  extern __shared__ char smem_raw[];
+  gemm_body(p, &map_a, &map_a_local, &map_b, blockIdx.x, gridDim.x, smem_raw);
+}
+
+struct EmuGemmParams {
+  GemmLaunch rank[kMaxRanks];
+};
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel_emu(const __grid_constant__ EmuGemmParams all) {
+  extern __shared__ char smem_raw[];
+  const GemmLaunch& g = all.rank[blockIdx.y];
+  gemm_body(g.p, &g.map_a, &g.map_a_local, &g.map_b, blockIdx.x, gridDim.x, smem_raw);
+}
+
+}  // namespace gemmk
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    return (EncodeTiledFn)p;
+  }();
+  return fn;
+}
+
+Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(kCudaError, "cuTensorMapEncodeTiled is not available in this driver");
+  if (((uintptr_t)base & 15) || (ld_elems * 2) % 16) return fail(kInvalidArgument, "TMA needs a 16-byte aligned base and row pitch");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld_elems * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kGemmBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled failed: %d (rows %llu cols %llu ld %llu)", (int)r,
+                                     (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld_elems);
+  return kSuccess;
+}
+
+size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
+
+int gemm_default_grid(int device) {
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  return sms > 0 ? sms : 148;
+}
+
+static Status prepare_kernel(const void* fn) {
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm_smem_bytes());
+  if (e != cudaSuccess) return fail(kCudaError, "cudaFuncSetAttribute(%zu bytes of shared memory): %s", gemm_smem_bytes(), cudaGetErrorString(e));
+  return kSuccess;
+}
+
+Status launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
+  static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel);
+  if (ready != kSuccess) return ready;
+  gemmk::gemm_kernel<<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(kCudaError, "gemm launch failed: %s", cudaGetErrorString(e));
+  return kSuccess;
+}
+
+Status launch_gemm_emu(const GemmLaunch* ranks, int nranks, cudaStream_t stream) {
+  static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel_emu);
+  if (ready != kSuccess) return ready;
+  static gemmk::EmuGemmParams all;  // launches are serialised by the emulation rendez-vous
+  for (int r = 0; r < nranks; ++r) all.rank[r] = ranks[r];
+  void* params[] = {(void*)&all};
+  dim3 grid(ranks[0].grid, nranks), block(kGemmThreads);
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)gemmk::gemm_kernel_emu, grid, block, params, gemm_smem_bytes(), stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(kCudaError, "emulated gemm cooperative launch (%d x %d CTAs) failed: %s", ranks[0].grid, nranks, cudaGetErrorString(e));
+  }
+  return kSuccess;
+}
+
+}  // namespace amem

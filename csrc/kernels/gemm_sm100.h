@@ -1,0 +1,62 @@
+// Host-visible description of the tcgen05 GEMM kernels (plain, all-gather -> GEMM,
+// GEMM -> reduce-scatter).  C[M,N] = A[M,K] * B[N,K]^T, bf16 operands (both K-major, i.e. the
+// layout of activations [tokens, features] and of torch Linear weights [out, in]), fp32
+// accumulation in tensor memory, bf16 output.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../core/status.h"
+#include "coll_args.h"
+
+namespace amem {
+
+static const int kGemmBM = 128, kGemmBN = 256, kGemmBK = 64, kGemmStages = 4;
+static const int kGemmThreads = 192;       // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+static const int kAgUnitRows = 32;         // rows of A announced by one all-gather ready flag
+static const int kMaxUnits = 256;          // flag slots per source rank
+
+enum GemmMode : int { kGemmPlain = 0, kGemmAllGather = 1, kGemmReduceScatter = 2 };
+
+// Flags of the fused kernels; lives in every rank's control segment right after CtrlBlock,
+// so it is saved and restored by pause/resume like the rest of the protocol state.
+struct FusedFlags {
+  uint32_t ag_ready[kMaxRanks][kMaxUnits];   // written by source rank s: unit u of its shard has landed (value = epoch)
+  uint32_t rs_done[kMaxRanks][kMaxUnits];    // incremented by source rank s: partial tiles of row block u delivered
+  uint32_t rs_expect[kMaxRanks][kMaxUnits];  // my running total of deliveries to expect per (source, row block)
+};
+
+struct GemmParams {
+  int M, N, K;              // problem of this rank (M = all rows, gathered or to be scattered)
+  int mode;
+  void* C;                  // plain / all-gather: bf16 [M, N] row-major, leading dimension ldc
+  int ldc;
+  int rows_per_rank;        // M / nranks (M when nranks == 1)
+  int comm_ctas;            // all-gather: CTAs [0, comm_ctas) move data, the rest compute
+  int copy_own;             // all-gather: also place my own shard in the gathered buffer
+  const void* a_local;      // all-gather: my shard, bf16 [rows_per_rank, K]
+  void* ag_buf[kMaxRanks];  // all-gather: every rank's gathered-A buffer [M, K]; [rank] is mine
+  void* rs_buf[kMaxRanks];  // reduce-scatter: every rank's partial buffer [nranks][rows_per_rank][N]
+  void* rs_out;             // reduce-scatter: bf16 [rows_per_rank, N]
+  FusedFlags* fflags[kMaxRanks];
+  CollArgs coll;            // rank, nranks, control blocks, status words, timeout
+};
+
+struct GemmLaunch {
+  GemmParams p;
+  CUtensorMap map_a;        // plain/RS: A [M, K]; all-gather: the gathered buffer [M, K]
+  CUtensorMap map_a_local;  // all-gather: my own shard [rows_per_rank, K]
+  CUtensorMap map_b;        // B [N, K]
+  int grid;                 // CTAs (per rank)
+};
+
+// Encodes a 2-D bf16 row-major tensor map with a [box_rows, 64] box and the 128-byte swizzle.
+Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems, uint32_t box_rows);
+
+size_t gemm_smem_bytes();
+Status launch_gemm(const GemmLaunch& g, cudaStream_t stream);
+// All ranks of an emulated communicator in one cooperative grid (blockIdx.y = rank).
+Status launch_gemm_emu(const GemmLaunch* ranks, int nranks, cudaStream_t stream);
+int gemm_default_grid(int device);
+
+}  // namespace amem

@@ -168,17 +168,6 @@ class CudaBackend : public VmmBackend {
     return kSuccess;
   }
   Status release(uint64_t handle) override {
-    {
-      // A handle imported inside the process that created it comes back as the very same
-      // driver handle without a reference of its own (seen as CUDA_ERROR_INVALID_VALUE on the
-      // second cuMemRelease); such duplicates are counted here and released once.
-      std::lock_guard<std::mutex> g(mu_);
-      auto it = dups_.find(handle);
-      if (it != dups_.end() && it->second > 0) {
-        if (--it->second == 0) dups_.erase(it);
-        return kSuccess;
-      }
-    }
     DRV(drv().MemRelease((CUmemGenericAllocationHandle)handle), "cuMemRelease");
     note_phys(handle, 0, -1);
     return kSuccess;
@@ -198,14 +187,8 @@ class CudaBackend : public VmmBackend {
     DRV(drv().MemImportFromShareableHandle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
         "cuMemImportFromShareableHandle");
     *handle = (uint64_t)h;
-    {
-      std::lock_guard<std::mutex> g(mu_);
-      static const bool dedup = env_long("AMEM_SAME_PROCESS_IMPORT_DEDUP", 1) != 0;
-      if (dedup && sizes_.count((uint64_t)h)) {  // same-process import of a handle we already hold
-        dups_[(uint64_t)h]++;
-        return kSuccess;
-      }
-    }
+    // (An import inside the exporting process yields a handle with a reference of its own,
+    // so emulated ranks release imports exactly like ranks in other processes do.)
     note_phys(h, size, +1);
     return kSuccess;
   }
@@ -360,7 +343,6 @@ class CudaBackend : public VmmBackend {
   std::mutex mu_;
   std::map<int, cudaStream_t> streams_;
   std::map<uint64_t, size_t> sizes_;
-  std::map<uint64_t, int> dups_;
   std::map<std::string, int> inject_;
   size_t live_bytes_ = 0;
   std::atomic<long> mappings_{0};
