@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <vector>
 
 #include "../comm/comm.h"
@@ -11,6 +13,7 @@
 #include "../core/log.h"
 #include "../include/nccl.h"
 #include "../kernels/gemm_sm100.h"
+#include "../kernels/moe.h"
 
 using namespace amem;
 
@@ -179,6 +182,107 @@ ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int 
   if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
   g.grid = c->emulated() ? emu_grid(n) : gemm_default_grid(c->device());
   return R(run_gemm(c, g, stream));
+}
+
+// ---- MoE expert parallelism -------------------------------------------------------------
+// Collective: (re)allocates the symmetric receive and expert-output buffers of `capacity_rows`
+// rows of d bf16 each and returns this rank's views.  Both are scratch: dropped on pause.
+ncclResult_t amemMoeBuffers(ncclComm_t comm, int capacity_rows, int d, void** recv_x, void** y) {
+  if (!comm || capacity_rows <= 0 || d <= 0 || d % 8) return ncclInvalidArgument;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  Status s = c->check_usable("amemMoeBuffers");
+  if (s != kSuccess) return R(s);
+  Segment *a = nullptr, *b = nullptr;
+  size_t bytes = (size_t)capacity_rows * d * 2;
+  if ((s = c->fused_segment(2, bytes, &a)) != kSuccess) return R(s);
+  if ((s = c->fused_segment(3, bytes, &b)) != kSuccess) return R(s);
+  if (recv_x) *recv_x = (void*)a->va[c->rank()];
+  if (y) *y = (void*)b->va[c->rank()];
+  return ncclSuccess;
+}
+
+static Status moe_args(Comm* c, int T, int k, int d, int E, int capacity_rows, MoeArgs* a) {
+  if (T < 0 || k <= 0 || d <= 0 || d % 8 || E <= 0 || E > kMoeMaxExperts || E % c->nranks())
+    return fail(kInvalidArgument, "MoE shape: T=%d k=%d d=%d (multiple of 8) E=%d (<= %d, divisible by %d ranks)", T, k, d, E, kMoeMaxExperts, c->nranks());
+  Segment *rx = nullptr, *yb = nullptr;
+  size_t bytes = (size_t)capacity_rows * d * 2;
+  AMEM_TRY(c->fused_segment(2, bytes, &rx));
+  AMEM_TRY(c->fused_segment(3, bytes, &yb));
+  memset(a, 0, sizeof(*a));
+  c->fill_args(&a->coll);
+  a->T = T;
+  a->k = k;
+  a->d = d;
+  a->E = E;
+  a->capacity_rows = capacity_rows;
+  for (int r = 0; r < c->nranks(); ++r) {
+    a->recv[r] = (char*)rx->va[r];
+    a->ybuf[r] = (char*)yb->va[r];
+  }
+  // small per-communicator work area in ordinary device memory
+  static std::mutex mu;
+  static std::map<Comm*, int*> work;
+  std::lock_guard<std::mutex> g(mu);
+  int*& w = work[c];
+  if (!w) {
+    size_t ints = (size_t)kMoeSegments * kMoeMaxExperts * 2 + kMoeMaxExperts;
+    if (cudaMalloc((void**)&w, ints * sizeof(int)) != cudaSuccess) return fail(kCudaError, "cudaMalloc of the MoE work area failed");
+  }
+  a->seg_hist = w;
+  a->seg_base = w + (size_t)kMoeSegments * kMoeMaxExperts;
+  a->send_off = w + (size_t)kMoeSegments * kMoeMaxExperts * 2;
+  return kSuccess;
+}
+
+// Routes this rank's T tokens to their experts' ranks.  On return (stream order) this rank's
+// receive buffer holds the rows of its local experts, grouped by expert in (source rank, token)
+// order; expert_counts[E/nranks] and expert_offsets[E/nranks + 1] describe the groups and
+// send_pos[T*k] remembers where every (token, choice) went (needed by amemMoeCombine).
+ncclResult_t amemMoeDispatch(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
+                             int* expert_offsets, int* send_pos, ncclComm_t comm, cudaStream_t stream) {
+  if (!comm) return ncclInvalidArgument;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  Status s = c->check_usable("amemMoeDispatch");
+  if (s != kSuccess) return R(s);
+  MoeArgs a;
+  if ((s = moe_args(c, T, k, d, E, capacity_rows, &a)) != kSuccess) return R(s);
+  if ((s = c->prepare_stream(stream)) != kSuccess) return R(s);
+  a.x = x;
+  a.topk_idx = topk_idx;
+  a.expert_counts = expert_counts;
+  a.expert_offsets = expert_offsets;
+  a.send_pos = send_pos;
+  if (c->emulated()) {
+    int n = c->nranks();
+    return R(c->emu()->rendezvous(c->rank(), 2001, &a, sizeof(a), stream, [n](const void* h, const void* dv, cudaStream_t st) {
+      return launch_moe_dispatch_emu((const MoeArgs*)h, (const MoeArgs*)dv, n, st);
+    }));
+  }
+  return R(launch_moe_dispatch(a, stream));
+}
+
+// out[T, d] = sum_j topk_w[t, j] * (expert output row of (t, j)), read from the expert ranks'
+// output buffers (the `y` of amemMoeBuffers, rows in the layout the dispatch produced).
+ncclResult_t amemMoeCombine(const int* topk_idx, const float* topk_w, const int* send_pos, void* out, int T, int k, int d, int E,
+                            int capacity_rows, ncclComm_t comm, cudaStream_t stream) {
+  if (!comm) return ncclInvalidArgument;
+  Comm* c = reinterpret_cast<Comm*>(comm);
+  Status s = c->check_usable("amemMoeCombine");
+  if (s != kSuccess) return R(s);
+  MoeArgs a;
+  if ((s = moe_args(c, T, k, d, E, capacity_rows, &a)) != kSuccess) return R(s);
+  if ((s = c->prepare_stream(stream)) != kSuccess) return R(s);
+  a.topk_idx = topk_idx;
+  a.topk_w = topk_w;
+  a.send_pos = const_cast<int*>(send_pos);
+  a.out = out;
+  if (c->emulated()) {
+    int n = c->nranks();
+    return R(c->emu()->rendezvous(c->rank(), 2002, &a, sizeof(a), stream, [n](const void* h, const void* dv, cudaStream_t st) {
+      return launch_moe_combine_emu((const MoeArgs*)h, (const MoeArgs*)dv, n, st);
+    }));
+  }
+  return R(launch_moe_combine(a, stream));
 }
 
 }  // extern "C"

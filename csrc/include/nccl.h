@@ -184,6 +184,17 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
 /* One kernel: out[M/nranks,N] = reduce_scatter_rows(A[M,K] * B[N,K]^T); partial tiles travel
  * to their owner from the epilogue and are summed there in rank order. */
 ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int M, int N, int K, ncclComm_t comm, cudaStream_t stream);
+/* MoE expert parallelism.  Experts are spread evenly over the communicator (expert e lives on
+ * rank e / (E / nranks)).  amemMoeBuffers (collective) returns this rank's receive buffer and
+ * expert-output buffer, both bf16 [capacity_rows, d] in symmetric scratch memory.
+ * amemMoeDispatch writes every (token, choice) row into its expert's rank at its final
+ * expert-sorted position (the permutation is fused into the all-to-all); amemMoeCombine pulls
+ * the expert outputs back and applies the routing weights in one pass. */
+ncclResult_t amemMoeBuffers(ncclComm_t comm, int capacity_rows, int d, void** recv_x, void** y);
+ncclResult_t amemMoeDispatch(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
+                             int* expert_offsets, int* send_pos, ncclComm_t comm, cudaStream_t stream);
+ncclResult_t amemMoeCombine(const int* topk_idx, const float* topk_w, const int* send_pos, void* out, int T, int k, int d, int E,
+                            int capacity_rows, ncclComm_t comm, cudaStream_t stream);
 /* 1 if the communicator's ranks share one GPU and run as one cooperative grid; 1 if NVLS is in use. */
 ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* stage_bytes);
 /* Host-side fault injection for tests: what = "uds:drop" | "uds:short" | "uds:nofd" |
