@@ -265,7 +265,8 @@ class CudaBackend : public VmmBackend {
   }
   Status mc_granularity(int ndev, size_t size, size_t* out) override {
     CUmulticastObjectProp p = mc_prop(ndev, size);
-    DRV(drv().MulticastGetGranularity(out, &p, CU_MULTICAST_GRANULARITY_RECOMMENDED), "cuMulticastGetGranularity");
+    // The recommended granularity is 512 MiB on B200; the minimum (2 MiB) is what binding needs.
+    DRV(drv().MulticastGetGranularity(out, &p, CU_MULTICAST_GRANULARITY_MINIMUM), "cuMulticastGetGranularity");
     return kSuccess;
   }
   Status mc_create(int ndev, size_t size, uint64_t* mc) override {
