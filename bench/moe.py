@@ -1,0 +1,160 @@
+#!/usr/bin/env python
+"""Hybrid-parallel MoE layer with split communicators (TP=2 x EP=world/2 through ncclCommSplit):
+64 experts, top-8 routing from N(0,1) logits, d=4096, expert FFN 1536, 16384 tokens per rank,
+bf16.  Measures the fused dispatch and combine against torch index_select + NCCL all-to-all,
+then pauses and resumes ALL communicators together for --cycles cycles, checking that the
+layer's output stays bit-identical and that device memory use is flat.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29540 bench/moe.py --cycles 100
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from asystem_amem_b200 import Communicator, pause_all, resume_all  # noqa: E402
+from asystem_amem_b200.models import MoELayer  # noqa: E402
+from asystem_amem_b200.parallel import make_grid  # noqa: E402
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=16384)
+    ap.add_argument("--dim", type=int, default=4096)
+    ap.add_argument("--ffn", type=int, default=1536)
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--tp", type=int, default=2)
+    ap.add_argument("--cycles", type=int, default=100)
+    ap.add_argument("--out", default="gpurun_out/moe.jsonl")
+    args = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", rank=rank, world_size=world)
+    dist.all_reduce(torch.zeros(1, device="cuda"))
+    gloo = dist.new_group(backend="gloo")
+    world_comm = Communicator.from_torch_distributed(gloo)
+    tp = args.tp if world % args.tp == 0 and world > 1 else 1
+    tp_comm, ep_comm = make_grid(world_comm, tp)
+    ep_ranks = [r for r in range(world) if r % tp == rank % tp]
+    ep_group = None
+    for pos in range(tp):  # every rank must take part in every new_group call
+        grp = dist.new_group([r for r in range(world) if r % tp == pos])
+        if pos == rank % tp:
+            ep_group = grp
+    n_ep = ep_comm.nranks
+    T, D, E, K = args.tokens, args.dim, args.experts, args.topk
+    layer = MoELayer(ep_comm, D, args.ffn, E, K, tokens_per_rank=T, capacity_factor=2.0, seed=3)
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    x = torch.randn(T, D, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    top = logits.topk(K, dim=1)
+    idx, w = top.indices.to(torch.int32), torch.softmax(top.values, dim=1)
+    disp = layer.dispatcher
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+
+    def timed(fn, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier(group=gloo)
+        tot = 0.0
+        for _ in range(iters):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            tot += s.elapsed_time(e)
+        t = torch.tensor([tot / iters], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=gloo)
+        return float(t.item())
+
+    state = {}
+
+    def fused_dispatch():
+        state["res"] = disp.dispatch(x, idx)
+
+    def fused_combine():
+        disp.combine(idx, w, state["res"].send_pos)
+
+    # baseline: sort pairs by expert, exchange counts, all_to_all_single of the rows, and back
+    El = E // n_ep
+    flat = idx.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    send_rows_idx = order // K
+    counts = torch.bincount(flat, minlength=E).view(n_ep, El).sum(1)
+    in_splits = counts.tolist()
+    out_counts = torch.empty_like(counts)
+    dist.all_to_all_single(out_counts, counts, group=ep_group)
+    out_splits = out_counts.tolist()
+    recv_base = torch.empty(sum(out_splits), D, device="cuda", dtype=torch.bfloat16)
+    back = torch.empty(T * K, D, device="cuda", dtype=torch.bfloat16)
+
+    def base_dispatch():
+        send = x.index_select(0, send_rows_idx)
+        dist.all_to_all_single(recv_base, send, out_splits, in_splits, group=ep_group)
+
+    def base_combine():
+        dist.all_to_all_single(back, recv_base, in_splits, out_splits, group=ep_group)
+        un = torch.empty_like(back)
+        un[order] = back
+        return (un.view(T, K, D).float() * w.unsqueeze(2)).sum(1).to(torch.bfloat16)
+
+    res = {"n_gpus": world, "tp": tp, "ep": n_ep, "tokens_per_rank": T, "dim": D, "experts": E, "topk": K}
+    res["dispatch_fused_ms"] = timed(fused_dispatch)
+    torch.cuda.synchronize()
+    total = int(state["res"].expert_offsets[-1])
+    disp.y[:total] = state["res"].recv_x[:total]
+    res["combine_fused_ms"] = timed(fused_combine)
+    res["dispatch_torch_nccl_ms"] = timed(base_dispatch)
+    res["combine_torch_nccl_ms"] = timed(base_combine)
+    row_bytes = D * 2
+    remote = T * K * (n_ep - 1) / n_ep * row_bytes
+    res["dispatch_link_gbs"] = remote / (res["dispatch_fused_ms"] * 1e-3) / 1e9
+    res["combine_link_gbs"] = remote / (res["combine_fused_ms"] * 1e-3) / 1e9
+    res["dispatch_frac_of_770"] = res["dispatch_link_gbs"] / 770.0
+    res["combine_frac_of_770"] = res["combine_link_gbs"] / 770.0
+
+    # all communicators paused and resumed together
+    first = layer(x).clone()
+    torch.cuda.synchronize()
+    dist.barrier(group=gloo)
+    used0 = torch.cuda.mem_get_info()[0]
+    same, drift, freed = True, 0, 0
+    for c in range(args.cycles):
+        pause_all()
+        freed = torch.cuda.mem_get_info()[0] - used0
+        resume_all()
+        if c % 10 == 9 or c == args.cycles - 1:
+            out = layer(x)
+            torch.cuda.synchronize()
+            same = same and torch.equal(out, first)
+        drift = max(drift, abs(torch.cuda.mem_get_info()[0] - used0))
+    flag = torch.tensor([1 if same else 0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=gloo)
+    res["cycles"] = args.cycles
+    res["bitwise_equal_after_cycles"] = bool(flag.item())
+    res["gib_freed_per_gpu_on_pause"] = freed / 2**30
+    res["memory_drift_mib"] = drift / 2**20
+    res["device_errors"] = world_comm.async_error() + ep_comm.async_error() + (tp_comm.async_error() if tp_comm else 0)
+    if rank == 0:
+        res = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items()}
+        print(json.dumps(res), flush=True)
+        with open(args.out, "a") as f:
+            f.write(json.dumps(res) + "\n")
+    dist.barrier(group=gloo)
+    for c in (ep_comm, tp_comm, world_comm):
+        if c is not None:
+            c.destroy()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

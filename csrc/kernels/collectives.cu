@@ -111,7 +111,27 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
     // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
     size_t nvec = (shi - slo + 15) / 16;
     char* base = mc + b0 * es + slo;
-    for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+    // four switch reductions in flight per thread: one round trip through the NVSwitch takes
+    // a few microseconds, so the link only fills with several hundred KiB outstanding per SM
+    const size_t nt = blockDim.x;
+    size_t i = threadIdx.x;
+    for (; i + 3 * nt < nvec; i += 4 * nt) {
+      uint4 v0 = Multimem<T>::ld_reduce(base + i * 16);
+      uint4 v1 = Multimem<T>::ld_reduce(base + (i + nt) * 16);
+      uint4 v2 = Multimem<T>::ld_reduce(base + (i + 2 * nt) * 16);
+      uint4 v3 = Multimem<T>::ld_reduce(base + (i + 3 * nt) * 16);
+      if (a.has_scale) {
+        v0 = Multimem<T>::scale(v0, a.scale);
+        v1 = Multimem<T>::scale(v1, a.scale);
+        v2 = Multimem<T>::scale(v2, a.scale);
+        v3 = Multimem<T>::scale(v3, a.scale);
+      }
+      multimem_st(base + i * 16, v0);
+      multimem_st(base + (i + nt) * 16, v1);
+      multimem_st(base + (i + 2 * nt) * 16, v2);
+      multimem_st(base + (i + 3 * nt) * 16, v3);
+    }
+    for (; i < nvec; i += nt) {
       uint4 v = Multimem<T>::ld_reduce(base + i * 16);
       if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
       multimem_st(base + i * 16, v);

@@ -163,6 +163,37 @@ def main():
     exp_total = sum(int(((i >= rank * El) & (i < (rank + 1) * El)).sum()) for i in all_idx)
     report("moe dispatch+combine", total == exp_total and torch.allclose(out.cpu().float(), exp, rtol=2e-2, atol=2e-2), rows=total)
 
+    # ---- sharded data-parallel training steps on a tiny Llama, with and without a pause
+    import torch.nn.functional as F
+    from asystem_amem_b200.models import LlamaConfig, LlamaDecoder
+    from asystem_amem_b200.models.llama import rope_tables
+    from asystem_amem_b200.parallel import FSDP, ShardedAdamW
+    cfg = LlamaConfig.tiny()
+
+    def train(with_pause):
+        torch.manual_seed(0)
+        fsdp = FSDP(LlamaDecoder(cfg, device="cuda"), comm)
+        opt = ShardedAdamW(fsdp, lr=1e-2)
+        hist = []
+        for step in range(3):
+            ids = torch.randint(0, cfg.vocab_size, (2, 64), generator=torch.Generator().manual_seed(10 * step + rank)).cuda()
+            cos, sin = rope_tables(64, cfg.dim // cfg.n_heads, cfg.rope_theta, "cuda")
+            logits = fsdp.forward_units(ids, cos, sin)
+            loss = F.cross_entropy(logits.float().view(-1, cfg.vocab_size), ids.view(-1))
+            fsdp.zero_grad()
+            loss.backward()
+            hist.append((float(loss), float(fsdp.grad_norm())))
+            opt.step()
+            if with_pause:
+                torch.cuda.synchronize()
+                pause_all()
+                resume_all()
+        return hist
+
+    h0, h1 = train(False), train(True)
+    norms = gather_cpu(torch.tensor([h[1] for h in h0]))
+    report("fsdp tiny llama, pause between steps", h0 == h1 and all(torch.equal(norms[0], t) for t in norms), losses=[round(h[0], 4) for h in h0])
+
     err = comm.async_error()
     report("no device-side errors", err == 0)
     comm.destroy()
