@@ -77,8 +77,16 @@ __device__ __forceinline__ Tile tile_of(const GemmParams& p, int t, int tiles_m,
     int per_shard = tiles_m * tiles_n;
     int s = t / per_shard, v = t % per_shard;
     o.shard = (p.mode == kGemmReduceScatter && n > 1) ? (r + 1 + s) % n : s;
-    o.m_in = v % tiles_m;
-    o.n_blk = v / tiles_m;
+    // Bands of 16 row blocks: the ~148 tiles in flight then span 16 row blocks x ~9 column
+    // blocks, so both operands are re-used out of L2 instead of streaming all of A from HBM
+    // once per column block.
+    const int GM = 16;
+    const int band = v / (GM * tiles_n);
+    const int first_m = band * GM;
+    const int gm = min(GM, tiles_m - first_m);
+    const int w = v - band * GM * tiles_n;
+    o.m_in = first_m + w % gm;
+    o.n_blk = w / gm;
   }
   return o;
 }
