@@ -6,7 +6,9 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <mutex>
 #include <thread>
+#include <utility>
 #include <vector>
 
 #include "../comm/comm.h"
@@ -41,6 +43,26 @@ CommConfig config_from(const ncclConfig_t* cfg) {
   CommConfig c;
   if (cfg && cfg->maxCTAs != NCCL_CONFIG_UNDEF_INT && cfg->maxCTAs > 0) c.max_blocks = cfg->maxCTAs;
   return c;
+}
+
+// Operators made by ncclRedOpCreatePreMulSum: id = ncclNumOps + slot; value = the scalar.
+std::mutex g_ops_mu;
+std::vector<std::pair<bool, float>> g_premul;  // (in use, scalar)
+
+bool resolve_op(int op, int* redop, float* scale, bool* has_scale) {
+  *scale = 1.0f;
+  *has_scale = false;
+  if (op >= 0 && op < (int)ncclNumOps) {
+    *redop = op;
+    return true;
+  }
+  std::lock_guard<std::mutex> g(g_ops_mu);
+  int slot = op - (int)ncclNumOps;
+  if (slot < 0 || slot >= (int)g_premul.size() || !g_premul[slot].first) return false;
+  *redop = kSum;
+  *scale = g_premul[slot].second;
+  *has_scale = true;
+  return true;
 }
 
 }  // namespace
@@ -149,6 +171,62 @@ ncclResult_t ncclCommRegister(const ncclComm_t, void* buff, size_t, void** handl
 }
 ncclResult_t ncclCommDeregister(const ncclComm_t, void*) { return ncclSuccess; }
 
+ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t, ncclWindow_t* win, int) {
+  if (!comm || !win) return ncclInvalidArgument;
+  *win = reinterpret_cast<ncclWindow_t>(buff);  // the push protocol reaches peers through its own staging
+  return ncclSuccess;
+}
+ncclResult_t ncclCommWindowDeregister(ncclComm_t, ncclWindow_t) { return ncclSuccess; }
+
+ncclResult_t ncclCommInitRankScalable(ncclComm_t* newcomm, int nranks, int myrank, int nId, ncclUniqueId* commIds, ncclConfig_t* config) {
+  if (!commIds || nId < 1) return ncclInvalidArgument;
+  return ncclCommInitRankConfig(newcomm, nranks, commIds[0], myrank, config);
+}
+
+ncclResult_t ncclCommShrink(ncclComm_t, int*, int, ncclComm_t* newcomm, ncclConfig_t*, int) {
+  if (newcomm) *newcomm = nullptr;
+  return R(fail(kInvalidUsage, "ncclCommShrink is not supported: create a new communicator over the surviving ranks"));
+}
+
+ncclResult_t ncclRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, ncclScalarResidence_t residence, ncclComm_t) {
+  if (!op || !scalar) return ncclInvalidArgument;
+  unsigned char raw[8] = {0};
+  size_t es = dtype_size(datatype);
+  if (es == 0) return ncclInvalidArgument;
+  if (residence == ncclScalarDevice) {
+    if (cudaMemcpy(raw, scalar, es, cudaMemcpyDeviceToHost) != cudaSuccess) return ncclUnhandledCudaError;
+  } else {
+    memcpy(raw, scalar, es);
+  }
+  float v;
+  switch ((int)datatype) {
+    case kF32: memcpy(&v, raw, 4); break;
+    case kF64: { double d; memcpy(&d, raw, 8); v = (float)d; break; }
+    case kF16: { uint16_t h; memcpy(&h, raw, 2); uint32_t sign = (h >> 15) & 1, e = (h >> 10) & 31, m = h & 1023; float f;
+                 if (e == 0) f = (float)m / 1024.0f / 16384.0f; else if (e == 31) f = 65504.0f; else { uint32_t bits = ((e + 112) << 23) | (m << 13); memcpy(&f, &bits, 4); }
+                 v = sign ? -f : f; break; }
+    case kBF16: { uint16_t h; memcpy(&h, raw, 2); uint32_t bits = (uint32_t)h << 16; memcpy(&v, &bits, 4); break; }
+    case kI32: { int i; memcpy(&i, raw, 4); v = (float)i; break; }
+    case kI64: { long long i; memcpy(&i, raw, 8); v = (float)i; break; }
+    default: return R(fail(kInvalidArgument, "pre-multiplied sum is not supported for datatype %d", (int)datatype));
+  }
+  std::lock_guard<std::mutex> g(g_ops_mu);
+  size_t slot = 0;
+  while (slot < g_premul.size() && g_premul[slot].first) ++slot;
+  if (slot == g_premul.size()) g_premul.emplace_back(false, 1.0f);
+  g_premul[slot] = {true, v};
+  *op = (ncclRedOp_t)((int)ncclNumOps + (int)slot);
+  return ncclSuccess;
+}
+
+ncclResult_t ncclRedOpDestroy(ncclRedOp_t op, ncclComm_t) {
+  std::lock_guard<std::mutex> g(g_ops_mu);
+  int slot = (int)op - (int)ncclNumOps;
+  if (slot < 0 || slot >= (int)g_premul.size()) return ncclInvalidArgument;
+  g_premul[slot].first = false;
+  return ncclSuccess;
+}
+
 // ---- memory ---------------------------------------------------------------------------
 ncclResult_t ncclMemAlloc(void** ptr, size_t size) {
   if (!ptr || size == 0) return ncclInvalidArgument;
@@ -216,7 +294,11 @@ ncclResult_t ncclMemFree(void* ptr) {
 
 ncclResult_t ncclAllReduce(const void* s, void* r, size_t count, ncclDataType_t dt, ncclRedOp_t op, ncclComm_t comm, cudaStream_t st) {
   NEED_COMM(comm);
-  return R(C(comm)->collective(kCollAllReduce, s, r, count, dt, dt, op, 0, 1.0f, false, kAlgoAuto, st));
+  int redop;
+  float scale;
+  bool has;
+  if (!resolve_op(op, &redop, &scale, &has)) return R(fail(kInvalidArgument, "unknown reduction operator %d", (int)op));
+  return R(C(comm)->collective(kCollAllReduce, s, r, count, dt, dt, redop, 0, scale, has, kAlgoAuto, st));
 }
 ncclResult_t amemAllReduceAlgo(const void* s, void* r, size_t count, ncclDataType_t dt, ncclRedOp_t op, int algo, ncclComm_t comm, cudaStream_t st) {
   NEED_COMM(comm);
@@ -224,7 +306,11 @@ ncclResult_t amemAllReduceAlgo(const void* s, void* r, size_t count, ncclDataTyp
 }
 ncclResult_t ncclReduce(const void* s, void* r, size_t count, ncclDataType_t dt, ncclRedOp_t op, int root, ncclComm_t comm, cudaStream_t st) {
   NEED_COMM(comm);
-  return R(C(comm)->collective(kCollReduce, s, r, count, dt, dt, op, root, 1.0f, false, kAlgoAuto, st));
+  int redop;
+  float scale;
+  bool has;
+  if (!resolve_op(op, &redop, &scale, &has)) return R(fail(kInvalidArgument, "unknown reduction operator %d", (int)op));
+  return R(C(comm)->collective(kCollReduce, s, r, count, dt, dt, redop, root, scale, has, kAlgoAuto, st));
 }
 ncclResult_t ncclBroadcast(const void* s, void* r, size_t count, ncclDataType_t dt, int root, ncclComm_t comm, cudaStream_t st) {
   NEED_COMM(comm);
@@ -235,7 +321,11 @@ ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t dt, int root, nc
 }
 ncclResult_t ncclReduceScatter(const void* s, void* r, size_t recvcount, ncclDataType_t dt, ncclRedOp_t op, ncclComm_t comm, cudaStream_t st) {
   NEED_COMM(comm);
-  return R(C(comm)->collective(kCollReduceScatter, s, r, recvcount, dt, dt, op, 0, 1.0f, false, kAlgoAuto, st));
+  int redop;
+  float scale;
+  bool has;
+  if (!resolve_op(op, &redop, &scale, &has)) return R(fail(kInvalidArgument, "unknown reduction operator %d", (int)op));
+  return R(C(comm)->collective(kCollReduceScatter, s, r, recvcount, dt, dt, redop, 0, scale, has, kAlgoAuto, st));
 }
 ncclResult_t amemReduceScatterScaleCast(const void* s, void* r, size_t recvcount, ncclDataType_t in_t, ncclDataType_t out_t, float scale,
                                         ncclComm_t comm, cudaStream_t st) {

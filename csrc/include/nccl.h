@@ -113,6 +113,17 @@ ncclResult_t ncclCommUserRank(const ncclComm_t comm, int* rank);
 /* Buffer registration is accepted for source compatibility; the push protocol needs none. */
 ncclResult_t ncclCommRegister(const ncclComm_t comm, void* buff, size_t size, void** handle);
 ncclResult_t ncclCommDeregister(const ncclComm_t comm, void* handle);
+ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t size, ncclWindow_t* win, int winFlags);
+ncclResult_t ncclCommWindowDeregister(ncclComm_t comm, ncclWindow_t win);
+/* Several unique ids may be passed for source compatibility; the first one is the meeting point. */
+ncclResult_t ncclCommInitRankScalable(ncclComm_t* newcomm, int nranks, int myrank, int nId, ncclUniqueId* commIds, ncclConfig_t* config);
+/* Not supported (returns ncclInvalidUsage): a communicator cannot lose ranks; create a new one. */
+ncclResult_t ncclCommShrink(ncclComm_t comm, int* excludeRanksList, int excludeRanksCount, ncclComm_t* newcomm, ncclConfig_t* config, int shrinkFlags);
+
+/* Pre-multiplied sum: sum_r (scalar * x_r).  The scalar is read when the operator is created. */
+typedef enum { ncclScalarDevice = 0, ncclScalarHostImmediate = 1 } ncclScalarResidence_t;
+ncclResult_t ncclRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, ncclScalarResidence_t residence, ncclComm_t comm);
+ncclResult_t ncclRedOpDestroy(ncclRedOp_t op, ncclComm_t comm);
 
 /* ---- collectives -------------------------------------------------------------------- */
 ncclResult_t ncclReduce(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclRedOp_t op, int root, ncclComm_t comm, cudaStream_t stream);

@@ -1,0 +1,82 @@
+"""C API surface through ctypes on the mock backend: version / error strings, group ids,
+ncclCommInitAll with in-process ranks, pre-multiplied-sum operators, unsupported calls,
+memory statistics by category."""
+import ctypes
+import os
+import threading
+
+import numpy as np
+
+from mp_util import run_ranks
+
+
+def _api(rank, world, uid):
+    import ctypes
+    import numpy as np
+    from asystem_amem_b200 import Communicator, bindings as B, get_group_id, mem_stats
+    lib = B.load_library()
+    out = {}
+    v = ctypes.c_int()
+    lib.ncclGetVersion(ctypes.byref(v))
+    out["version"] = v.value == 22705
+    out["errstr"] = lib.ncclGetErrorString(5) == b"invalid usage"
+    out["group_env"] = get_group_id() == 170           # AMEM_GROUPID from the environment
+    comm = Communicator(world, rank, uid)
+    out["group_locked"] = lib.ncclSetGroupID(7) != 0   # too late: memory is already tracked
+    # pre-multiplied sum
+    lib.ncclRedOpCreatePreMulSum.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
+    op = ctypes.c_int()
+    scalar = ctypes.c_float(0.5)
+    assert lib.ncclRedOpCreatePreMulSum(ctypes.byref(op), ctypes.byref(scalar), B.DTYPES["float32"], 1, comm._h) == 0
+    x = np.full(1000, float(rank + 1), dtype=np.float32)
+    assert lib.ncclAllReduce(x.ctypes.data, x.ctypes.data, 1000, B.DTYPES["float32"], op.value, comm._h, None) == 0
+    out["premul"] = bool(np.all(x == 0.5 * sum(range(1, world + 1))))
+    lib.ncclRedOpDestroy.argtypes = [ctypes.c_int, ctypes.c_void_p]
+    assert lib.ncclRedOpDestroy(op.value, comm._h) == 0
+    out["destroyed_op_refused"] = lib.ncclAllReduce(x.ctypes.data, x.ctypes.data, 1000, B.DTYPES["float32"], op.value, comm._h, None) == 4
+    # unsupported / compatibility calls
+    lib.ncclCommShrink.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_int]
+    nc = ctypes.c_void_p()
+    out["shrink"] = lib.ncclCommShrink(comm._h, None, 0, ctypes.byref(nc), None, 0) == 5
+    st = mem_stats()
+    out["stats"] = (st["n_local"] == 2 and st["n_imported"] == 2 * (world - 1) and st["scratch_bytes"] > st["stateful_bytes"] > 0
+                    and st["bytes_by_tag"][1] > 0 and st["bytes_by_tag"][7] > 0 and st["group_id"] == 170)
+    bad = np.zeros(4, dtype=np.float32)
+    out["bad_root"] = lib.ncclBroadcast(bad.ctypes.data, bad.ctypes.data, 4, B.DTYPES["float32"], world + 3, comm._h, None) == 4
+    comm.destroy()
+    return out
+
+
+def test_c_api_surface():
+    for r in run_ranks(_api, 2, env={"AMEM_GROUPID": "170"}):
+        assert all(r.values()), r
+
+
+def test_comm_init_all_in_one_process():
+    os.environ["AMEM_BACKEND"] = "mock"
+    from asystem_amem_b200 import bindings as B
+    lib = B.load_library()
+    n = 3
+    comms = (ctypes.c_void_p * n)()
+    lib.ncclCommInitAll.argtypes = [ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_void_p]
+    assert lib.ncclCommInitAll(comms, n, None) == 0
+    bufs = [np.full(5000, float(i + 1), dtype=np.float32) for i in range(n)]
+
+    def run(i):
+        assert lib.ncclAllReduce(bufs[i].ctypes.data, bufs[i].ctypes.data, 5000, B.DTYPES["float32"], 0, comms[i], None) == 0
+
+    th = [threading.Thread(target=run, args=(i,)) for i in range(n)]
+    [t.start() for t in th]
+    [t.join(60) for t in th]
+    assert all(np.all(b == 6.0) for b in bufs)
+    # process-wide pause with several ranks of one communicator in this process
+    assert lib.ncclPause(None) == 0
+    assert lib.ncclAllReduce(bufs[0].ctypes.data, bufs[0].ctypes.data, 5000, B.DTYPES["float32"], 0, comms[0], None) == 5
+    assert lib.ncclResume(None) == 0
+    th = [threading.Thread(target=run, args=(i,)) for i in range(n)]
+    [t.start() for t in th]
+    [t.join(60) for t in th]
+    assert all(np.all(b == 18.0) for b in bufs)
+    th = [threading.Thread(target=lambda i=i: lib.ncclCommDestroy(comms[i])) for i in range(n)]
+    [t.start() for t in th]
+    [t.join(60) for t in th]
