@@ -79,6 +79,16 @@ def backend_usage() -> dict:
     return {"physical_bytes": phys.value, "mappings": maps.value, "backend": name.value.decode()}
 
 
+def backend_timings(reset: bool = False) -> dict:
+    """Wall time and call count of every kind of VMM driver call made so far."""
+    import json
+    buf = ctypes.create_string_buffer(2048)
+    lib = B.load_library()
+    lib.amemBackendTimings.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.c_int]
+    B.check(lib.amemBackendTimings(buf, 2048, 1 if reset else 0), "amemBackendTimings")
+    return json.loads(buf.value.decode() or "{}")
+
+
 def pause_all() -> None:
     B.check(B.load_library().ncclPause(None), "ncclPause")
 

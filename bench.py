@@ -130,6 +130,7 @@ def main() -> None:
 
     if args.impl == "amem":
         from asystem_amem_b200 import Communicator, get_unique_id, pause_all, process_pause_resume_stats, resume_all
+        from asystem_amem_b200.comm import backend_timings
         comm = Communicator.from_torch_distributed() if multi else Communicator(1, 0, get_unique_id())
 
         def collective():
@@ -162,6 +163,8 @@ def main() -> None:
         host_barrier()
         t0 = time.perf_counter()
         x.copy_(host_in, non_blocking=True)                      # H2D of this step's input
+        torch.cuda.synchronize()
+        host_barrier()                                           # ranks enter the collective together
         ev[0].record()
         collective()
         ev[1].record()
@@ -181,6 +184,8 @@ def main() -> None:
 
     for _ in range(args.warmup):
         step(False)
+    if args.impl == "amem":
+        backend_timings(reset=True)
     rows = []
     torch.cuda.synchronize()
     host_barrier()
@@ -203,6 +208,7 @@ def main() -> None:
     detail = {}
     if args.impl == "amem":
         detail = {k: round(v, 1) if isinstance(v, float) else v for k, v in process_pause_resume_stats().items()}
+        detail["driver_calls_rank0_all_steps"] = backend_timings()
     if rank == 0:
         value = pause_ms + resume_ms
         print(json.dumps({

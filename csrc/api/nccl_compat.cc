@@ -422,6 +422,13 @@ ncclResult_t amemInject(const char* what, int nth, int param) {
   }
   return ncclInvalidArgument;
 }
+ncclResult_t amemBackendTimings(char* buf, size_t len, int reset) {
+  VmmBackend* be = default_backend();
+  if (!be || !buf || !len) return ncclInvalidArgument;
+  std::string s = be->timings(reset != 0);
+  snprintf(buf, len, "%s", s.c_str());
+  return ncclSuccess;
+}
 ncclResult_t amemBackendUsage(size_t* physical_bytes, size_t* mappings, const char** backend_name) {
   VmmBackend* be = default_backend();
   if (!be) return ncclInvalidUsage;

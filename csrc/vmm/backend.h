@@ -10,6 +10,7 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <string>
 
 #include "../core/status.h"
 
@@ -67,6 +68,8 @@ class VmmBackend {
   // (created or imported and not yet released).  Used by leak checks.
   virtual size_t live_physical_bytes() = 0;
   virtual size_t live_mappings() = 0;
+  // JSON object with the wall time and call count of every kind of driver call so far.
+  virtual std::string timings(bool reset) { (void)reset; return "{}"; }
 };
 
 // Process-wide backends.  `cuda_backend()` returns nullptr when no CUDA driver is usable.

@@ -14,6 +14,7 @@
 #include <cstring>
 #include <map>
 #include <mutex>
+#include <string>
 
 #include "../core/log.h"
 #include "backend.h"
@@ -117,8 +118,39 @@ CUmemAllocationProp device_prop(int dev) {
   return p;
 }
 
+// Wall time spent in each kind of driver call (AMEM tooling: amemBackendTimings).
+struct CallTimer {
+  std::atomic<uint64_t> ns{0}, calls{0};
+};
+enum { kTCreate, kTRelease, kTMap, kTAccess, kTUnmap, kTImport, kTExport, kTBind, kTUnbind, kTCount };
+static CallTimer g_timers[kTCount];
+static const char* kTimerNames[kTCount] = {"create", "release", "map", "set_access", "unmap", "import", "export", "mc_bind", "mc_unbind"};
+struct Timed {
+  int which;
+  double t0;
+  explicit Timed(int w) : which(w), t0(now_ms()) {}
+  ~Timed() {
+    g_timers[which].ns.fetch_add((uint64_t)((now_ms() - t0) * 1e6));
+    g_timers[which].calls.fetch_add(1);
+  }
+};
+
 class CudaBackend : public VmmBackend {
  public:
+  std::string timings(bool reset) override {
+    char buf[64];
+    std::string out = "{";
+    for (int i = 0; i < kTCount; ++i) {
+      snprintf(buf, sizeof(buf), "%s\"%s_us\": %.1f, \"%s_calls\": %llu", i ? ", " : "", kTimerNames[i], g_timers[i].ns.load() / 1e3,
+               kTimerNames[i], (unsigned long long)g_timers[i].calls.load());
+      out += buf;
+      if (reset) {
+        g_timers[i].ns = 0;
+        g_timers[i].calls = 0;
+      }
+    }
+    return out + "}";
+  }
   const char* name() const override { return "cuda"; }
   bool is_device() const override { return true; }
 
@@ -162,19 +194,26 @@ class CudaBackend : public VmmBackend {
     if (should_fail("create")) return fail(kCudaError, "cuMemCreate: injected out-of-memory");
     CUmemAllocationProp p = device_prop(dev);
     CUmemGenericAllocationHandle h = 0;
-    DRV(drv().MemCreate(&h, size, &p, 0), "cuMemCreate");
+    {
+      Timed t(kTCreate);
+      DRV(drv().MemCreate(&h, size, &p, 0), "cuMemCreate");
+    }
     *handle = (uint64_t)h;
     note_phys(h, size, +1);
     return kSuccess;
   }
   Status release(uint64_t handle) override {
-    DRV(drv().MemRelease((CUmemGenericAllocationHandle)handle), "cuMemRelease");
+    {
+      Timed t(kTRelease);
+      DRV(drv().MemRelease((CUmemGenericAllocationHandle)handle), "cuMemRelease");
+    }
     note_phys(handle, 0, -1);
     return kSuccess;
   }
   Status export_fd(uint64_t handle, int* fd) override {
     if (should_fail("export")) return fail(kCudaError, "cuMemExportToShareableHandle: injected failure");
     int out = -1;
+    Timed t(kTExport);
     DRV(drv().MemExportToShareableHandle(&out, (CUmemGenericAllocationHandle)handle,
                                          CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
         "cuMemExportToShareableHandle");
@@ -184,6 +223,7 @@ class CudaBackend : public VmmBackend {
   Status import_fd(int fd, size_t size, uint64_t* handle) override {
     if (should_fail("import")) return fail(kCudaError, "cuMemImportFromShareableHandle: injected failure");
     CUmemGenericAllocationHandle h = 0;
+    Timed t(kTImport);
     DRV(drv().MemImportFromShareableHandle(&h, (void*)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR),
         "cuMemImportFromShareableHandle");
     *handle = (uint64_t)h;
@@ -195,7 +235,11 @@ class CudaBackend : public VmmBackend {
 
   Status map(uint64_t va, size_t size, uint64_t handle, int dev) override {
     if (should_fail("map")) return fail(kCudaError, "cuMemMap: injected failure");
-    DRV(drv().MemMap((CUdeviceptr)va, size, 0, (CUmemGenericAllocationHandle)handle, 0), "cuMemMap");
+    {
+      Timed t(kTMap);
+      DRV(drv().MemMap((CUdeviceptr)va, size, 0, (CUmemGenericAllocationHandle)handle, 0), "cuMemMap");
+    }
+    Timed t2(kTAccess);
     CUmemAccessDesc a;
     memset(&a, 0, sizeof(a));
     a.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
@@ -210,7 +254,10 @@ class CudaBackend : public VmmBackend {
     return kSuccess;
   }
   Status unmap(uint64_t va, size_t size) override {
-    DRV(drv().MemUnmap((CUdeviceptr)va, size), "cuMemUnmap");
+    {
+      Timed t(kTUnmap);
+      DRV(drv().MemUnmap((CUdeviceptr)va, size), "cuMemUnmap");
+    }
     mappings_.fetch_sub(1);
     return kSuccess;
   }
@@ -281,11 +328,13 @@ class CudaBackend : public VmmBackend {
     return kSuccess;
   }
   Status mc_bind(uint64_t mc, size_t mc_off, uint64_t handle, size_t size) override {
+    Timed t(kTBind);
     DRV(drv().MulticastBindMem((CUmemGenericAllocationHandle)mc, mc_off, (CUmemGenericAllocationHandle)handle, 0, size, 0),
         "cuMulticastBindMem");
     return kSuccess;
   }
   Status mc_unbind(uint64_t mc, int dev, size_t mc_off, size_t size) override {
+    Timed t(kTUnbind);
     DRV(drv().MulticastUnbind((CUmemGenericAllocationHandle)mc, (CUdevice)dev, mc_off, size), "cuMulticastUnbind");
     return kSuccess;
   }
