@@ -174,7 +174,9 @@ ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int 
   } else {
     g.p.mode = kGemmReduceScatter;
     Segment* seg = nullptr;
-    if ((s = c->fused_segment(1, (size_t)M * N * 2, &seg)) != kSuccess) return R(s);
+    // tile-major partials: every (row block, column block) occupies a full 128 x 256 tile
+    size_t tiles = (size_t)((rpr + kGemmBM - 1) / kGemmBM) * (size_t)((N + kGemmBN - 1) / kGemmBN);
+    if ((s = c->fused_segment(1, (size_t)n * tiles * kGemmBM * kGemmBN * 2, &seg)) != kSuccess) return R(s);
     for (int r = 0; r < n; ++r) g.p.rs_buf[r] = (void*)seg->va[r];
   }
   if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);

@@ -13,6 +13,12 @@
 // that the stores of one rank fan out over all NVLink destinations at once.
 AMEM_FN int peer_at(int rank, int n, int k, int block) { return (rank + 1 + (k - 1 + block) % (n - 1)) % n; }
 
+// All-gather, all-to-all and reduce-scatter share one skeleton.  Chunk t is PUSHED into the
+// peers' staging (NVLink-bound) while chunk t-1 is DRAINED from my own staging into the user's
+// buffer (HBM-bound): two groups of warps do the two jobs side by side and meet at one barrier
+// per chunk, so a large message moves at link speed instead of link + memory time.  Quarter
+// t % 2 of the operation's staging half holds chunk t; a quarter is rewritten only after the
+// barrier that follows its drain.
 template <typename TI, typename TO, int OP>
 AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
@@ -24,23 +30,35 @@ AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   if (cb > slot) cb = slot;
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
-  uint32_t c = 0;
-  for (size_t off = 0; off < B || (B == 0 && c == 0); off += cb, ++c) {
-    size_t len = B - off < cb ? B - off : cb;
-    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
-    size_t lo, hi;
-    block_range(len, p.block, p.nblocks, &lo, &hi);
-    if (send != recv + (size_t)r * B) copy_span(recv + (size_t)r * B + off + lo, send + off + lo, hi - lo);
-    for (int k = 1; k < n; ++k) {
-      int q = peer_at(r, n, k, p.block);
-      copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo);
+  const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
+  Lane lp, ld;
+  bool do_push, do_drain;
+  split_lanes(nch > 1, 10, &lp, &ld, &do_push, &do_drain);
+  for (uint32_t t = 0; t <= nch; ++t) {
+    if (do_push && t < nch) {
+      size_t off = (size_t)t * cb;
+      size_t len = B - off < cb ? B - off : cb;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
+      size_t lo, hi;
+      block_range(len, p.block, p.nblocks, &lo, &hi);
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo, lp);
+      }
+      if (send != recv + (size_t)r * B) copy_span(recv + (size_t)r * B + off + lo, send + off + lo, hi - lo, lp);
     }
-    block_barrier(p);
-    for (int k = 1; k < n; ++k) {
-      int q = peer_at(r, n, k, p.block);
-      copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo);
+    if (do_drain && t >= 1) {
+      size_t off = (size_t)(t - 1) * cb;
+      size_t len = B - off < cb ? B - off : cb;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t - 1);
+      size_t lo, hi;
+      block_range(len, p.block, p.nblocks, &lo, &hi);
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ld);
+      }
     }
-    if (B == 0) break;
+    if (t < nch) block_barrier(p);
   }
 }
 
@@ -55,23 +73,35 @@ AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
   if (cb > slot) cb = slot;
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
-  uint32_t c = 0;
-  for (size_t off = 0; off < B || (B == 0 && c == 0); off += cb, ++c) {
-    size_t len = B - off < cb ? B - off : cb;
-    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
-    size_t lo, hi;
-    block_range(len, p.block, p.nblocks, &lo, &hi);
-    if (send != recv) copy_span(recv + (size_t)r * B + off + lo, send + (size_t)r * B + off + lo, hi - lo);
-    for (int k = 1; k < n; ++k) {
-      int q = peer_at(r, n, k, p.block);
-      copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + (size_t)q * B + off + lo, hi - lo);
+  const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
+  Lane lp, ld;
+  bool do_push, do_drain;
+  split_lanes(nch > 1, 10, &lp, &ld, &do_push, &do_drain);
+  for (uint32_t t = 0; t <= nch; ++t) {
+    if (do_push && t < nch) {
+      size_t off = (size_t)t * cb;
+      size_t len = B - off < cb ? B - off : cb;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
+      size_t lo, hi;
+      block_range(len, p.block, p.nblocks, &lo, &hi);
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + (size_t)q * B + off + lo, hi - lo, lp);
+      }
+      if (send != recv) copy_span(recv + (size_t)r * B + off + lo, send + (size_t)r * B + off + lo, hi - lo, lp);
     }
-    block_barrier(p);
-    for (int k = 1; k < n; ++k) {
-      int q = peer_at(r, n, k, p.block);
-      copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo);
+    if (do_drain && t >= 1) {
+      size_t off = (size_t)(t - 1) * cb;
+      size_t len = B - off < cb ? B - off : cb;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t - 1);
+      size_t lo, hi;
+      block_range(len, p.block, p.nblocks, &lo, &hi);
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ld);
+      }
     }
-    if (B == 0) break;
+    if (t < nch) block_barrier(p);
   }
 }
 
@@ -88,23 +118,35 @@ AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems)
   if (ce * es > slot) ce = slot / es;
   const char* send = (const char*)a.send;
   TO* recv = (TO*)a.recv;
-  uint32_t c = 0;
-  for (size_t off = 0; off < R || (R == 0 && c == 0); off += ce, ++c) {
-    size_t len = R - off < ce ? R - off : ce;
-    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
-    size_t lo, hi;
-    block_range(len * es, p.block, p.nblocks, &lo, &hi);
-    for (int k = 1; k < n; ++k) {
-      int q = peer_at(r, n, k, p.block);
-      copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + ((size_t)q * R + off) * es + lo, hi - lo);
+  const uint32_t nch = (uint32_t)((R + ce - 1) / ce);
+  Lane lp, ld;
+  bool do_push, do_drain;
+  split_lanes(nch > 1, 10, &lp, &ld, &do_push, &do_drain);
+  for (uint32_t t = 0; t <= nch; ++t) {
+    if (do_push && t < nch) {
+      size_t off = (size_t)t * ce;
+      size_t len = R - off < ce ? R - off : ce;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
+      size_t lo, hi;
+      block_range(len * es, p.block, p.nblocks, &lo, &hi);
+      for (int k = 1; k < n; ++k) {
+        int q = peer_at(r, n, k, p.block);
+        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + ((size_t)q * R + off) * es + lo, hi - lo, lp);
+      }
     }
-    block_barrier(p);
-    const TI* slots[kMaxRanks];
-    for (int s = 0; s < n; ++s)
-      slots[s] = (s == r) ? (const TI*)(send + ((size_t)r * R + off) * es + lo)
-                          : (const TI*)(a.stage[r] + qoff + (size_t)s * slot + lo);
-    reduce_span<TI, TO, OP>(recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
-    if (R == 0) break;
+    if (do_drain && t >= 1) {
+      size_t off = (size_t)(t - 1) * ce;
+      size_t len = R - off < ce ? R - off : ce;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t - 1);
+      size_t lo, hi;
+      block_range(len * es, p.block, p.nblocks, &lo, &hi);
+      const TI* slots[kMaxRanks];
+      for (int s2 = 0; s2 < n; ++s2)
+        slots[s2] = (s2 == r) ? (const TI*)(send + ((size_t)r * R + off) * es + lo)
+                              : (const TI*)(a.stage[r] + qoff + (size_t)s2 * slot + lo);
+      reduce_span<TI, TO, OP>(recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, ld);
+    }
+    if (t < nch) block_barrier(p);
   }
 }
 
@@ -121,13 +163,13 @@ AMEM_FN void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
   block_range(B, p.block, p.nblocks, &lo, &hi);
   for (int k = 1; k < n; ++k) {
     int q = peer_at(r, n, k, p.block);
-    copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + lo, hi - lo);
+    copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + lo, hi - lo, full_lane());
   }
   block_barrier(p);
   const TI* slots[kMaxRanks];
   for (int s = 0; s < n; ++s)
     slots[s] = (s == r) ? (const TI*)(send + lo) : (const TI*)(a.stage[r] + qoff + (size_t)s * slot + lo);
-  reduce_span<TI, TO, OP>((TO*)a.recv + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+  reduce_span<TI, TO, OP>((TO*)a.recv + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, full_lane());
 }
 
 // Two-shot: reduce-scatter of the chunk into region X, then all-gather of the reduced slices
@@ -160,7 +202,7 @@ AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_el
       if (b1 > len) b1 = len;
       size_t lo, hi;
       block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
-      copy_span(a.stage[q] + xoff + (size_t)r * slot + lo, send + (off + b0) * es + lo, hi - lo);
+      copy_span(a.stage[q] + xoff + (size_t)r * slot + lo, send + (off + b0) * es + lo, hi - lo, full_lane());
     }
     block_barrier(p);
     {
@@ -174,13 +216,13 @@ AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_el
         slots[s] = (s == r) ? (const TI*)(send + (off + b0) * es + lo)
                             : (const TI*)(a.stage[r] + xoff + (size_t)s * slot + lo);
       char* mine = a.stage[r] + yoff + (size_t)r * slot + lo;
-      reduce_span<TI, TO, OP>((TO*)mine, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+      reduce_span<TI, TO, OP>((TO*)mine, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, full_lane());
       block_sync();
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + yoff + (size_t)r * slot + lo, mine, hi - lo);
+        copy_span(a.stage[q] + yoff + (size_t)r * slot + lo, mine, hi - lo, full_lane());
       }
-      copy_span(recv + (off + b0) * es + lo, mine, hi - lo);
+      copy_span(recv + (off + b0) * es + lo, mine, hi - lo, full_lane());
     }
     block_barrier(p);
     for (int k = 1; k < n; ++k) {
@@ -190,7 +232,7 @@ AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_el
       if (b1 > len) b1 = len;
       size_t lo, hi;
       block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
-      copy_span(recv + (off + b0) * es + lo, a.stage[r] + yoff + (size_t)q * slot + lo, hi - lo);
+      copy_span(recv + (off + b0) * es + lo, a.stage[r] + yoff + (size_t)q * slot + lo, hi - lo, full_lane());
     }
   }
 }
@@ -216,12 +258,12 @@ AMEM_FN void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
     if (r == a.root) {
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + qoff + lo, send + off + lo, hi - lo);
+        copy_span(a.stage[q] + qoff + lo, send + off + lo, hi - lo, full_lane());
       }
-      if (send != recv) copy_span(recv + off + lo, send + off + lo, hi - lo);
+      if (send != recv) copy_span(recv + off + lo, send + off + lo, hi - lo, full_lane());
     }
     block_barrier(p);
-    if (r != a.root) copy_span(recv + off + lo, a.stage[r] + qoff + lo, hi - lo);
+    if (r != a.root) copy_span(recv + off + lo, a.stage[r] + qoff + lo, hi - lo, full_lane());
   }
 }
 
@@ -241,13 +283,13 @@ AMEM_FN void body_reduce(const CollArgs& a, Proto& p, size_t chunk_elems) {
     size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
     size_t lo, hi;
     block_range(len * es, p.block, p.nblocks, &lo, &hi);
-    if (r != a.root) copy_span(a.stage[a.root] + qoff + (size_t)r * slot + lo, send + off * es + lo, hi - lo);
+    if (r != a.root) copy_span(a.stage[a.root] + qoff + (size_t)r * slot + lo, send + off * es + lo, hi - lo, full_lane());
     block_barrier(p);
     if (r == a.root) {
       const TI* slots[kMaxRanks];
       for (int s = 0; s < n; ++s)
         slots[s] = (s == r) ? (const TI*)(send + off * es + lo) : (const TI*)(a.stage[r] + qoff + (size_t)s * slot + lo);
-      reduce_span<TI, TO, OP>((TO*)a.recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0);
+      reduce_span<TI, TO, OP>((TO*)a.recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, full_lane());
     }
   }
 }
@@ -276,7 +318,7 @@ AMEM_FN void body_sendrecv(const CollArgs& a, int entry, int lane, int lanes, in
         }
       }
       block_sync();
-      copy_span(a.stage[e.peer] + p2p_slot_offset(a.stage_bytes, slot, a.rank, seq, lane), (const char*)e.src + off, len);
+      copy_span(a.stage[e.peer] + p2p_slot_offset(a.stage_bytes, slot, a.rank, seq, lane), (const char*)e.src + off, len, full_lane());
       block_sync();
       if (thread_index() == 0) {
         fence_system();
@@ -299,7 +341,7 @@ AMEM_FN void body_sendrecv(const CollArgs& a, int entry, int lane, int lanes, in
         }
       }
       block_sync();
-      copy_span((char*)e.dst + off, a.stage[a.rank] + p2p_slot_offset(a.stage_bytes, slot, e.peer, seq, lane), len);
+      copy_span((char*)e.dst + off, a.stage[a.rank] + p2p_slot_offset(a.stage_bytes, slot, e.peer, seq, lane), len, full_lane());
       block_sync();
       if (thread_index() == 0) {
         fence_system();
@@ -325,7 +367,7 @@ AMEM_FN void run_body(const CollArgs& a, int block, int nblocks, int* s_abort, s
     const TI* slots[kMaxRanks];
     slots[0] = (const TI*)((const char*)a.send + lo);
     if ((const void*)a.send != (const void*)a.recv || a.has_scale || sizeof(TI) != sizeof(TO))
-      reduce_span<TI, TO, OP>((TO*)a.recv + lo / sizeof(TI), slots, 1, (hi - lo) / sizeof(TI), a.scale, a.has_scale != 0);
+      reduce_span<TI, TO, OP>((TO*)a.recv + lo / sizeof(TI), slots, 1, (hi - lo) / sizeof(TI), a.scale, a.has_scale != 0, full_lane());
   } else if constexpr (REDUCING) {
     switch (a.kind) {
       case kCollAllReduce:

@@ -155,9 +155,35 @@ __device__ __forceinline__ void block_range(size_t total_bytes, int block, int n
   *hi = h;
 }
 
-__device__ __forceinline__ void copy_span(char* dst, const char* src, size_t bytes) {
+// A lane is the slice of a block's threads that executes one loop: the whole block, or the
+// "push" / "drain" group of warps when a collective overlaps its two phases.
+struct Lane {
+  int tid, nt;
+};
+__device__ __forceinline__ Lane full_lane() { return Lane{(int)threadIdx.x, (int)blockDim.x}; }
+
+// Splits the block's warps: the first `push_sixteenths`/16 of them push over NVLink, the rest
+// drain staging into the user's buffer.  Without overlap every thread does both in turn.
+__device__ __forceinline__ void split_lanes(bool overlap, int push_sixteenths, Lane* push, Lane* drain, bool* do_push, bool* do_drain) {
+  if (!overlap) {
+    *push = *drain = full_lane();
+    *do_push = *do_drain = true;
+    return;
+  }
+  int nwarps = blockDim.x / 32;
+  int wp = nwarps * push_sixteenths / 16;
+  if (wp < 1) wp = 1;
+  if (wp > nwarps - 1) wp = nwarps - 1;
+  int t = threadIdx.x;
+  *do_push = t < wp * 32;
+  *do_drain = !*do_push;
+  *push = Lane{t, wp * 32};
+  *drain = Lane{t - wp * 32, (nwarps - wp) * 32};
+}
+
+__device__ __forceinline__ void copy_span(char* dst, const char* src, size_t bytes, Lane ln) {
   if (bytes == 0) return;
-  int t = threadIdx.x, nt = blockDim.x;
+  int t = ln.tid, nt = ln.nt;
   if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
     size_t nvec = bytes / 16;
     const uint4* s = (const uint4*)src;
@@ -181,10 +207,10 @@ __device__ __forceinline__ void copy_span(char* dst, const char* src, size_t byt
 // out[i] = cast(scale * OP_r(slot_r[i]))  for i in [0, n); reduction order is rank 0..nslots-1,
 // accumulated in Acc<TI> (fp32 for 16-bit floats) and rounded once.
 template <typename TI, typename TO, int OP>
-__device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale) {
+__device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale, Lane ln) {
   using A = typename Acc<TI>::type;
   constexpr int VI = 16 / sizeof(TI);
-  int t = threadIdx.x, nt = blockDim.x;
+  int t = ln.tid, nt = ln.nt;
   bool aligned = (((uintptr_t)out) % (VI * sizeof(TO)) == 0);
   for (int r = 0; r < nslots; ++r) aligned = aligned && (((uintptr_t)slots[r] & 15) == 0);
   size_t nvec = aligned ? n / VI : 0;

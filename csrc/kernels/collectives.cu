@@ -78,9 +78,12 @@ __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// Stage the chunk locally, let the switch add the n copies of my slice and broadcast the sum
-// back into every rank's staging, then copy out.  One region (the op's half) suffices: both
-// phases that write it are fenced by a barrier from the phase that reads it.
+// NVLS all-reduce as a three-stage software pipeline over chunks: while one group of warps lets
+// the switch add and re-broadcast my slice of chunk t-1 (multimem.ld_reduce + multimem.st on
+// the multicast mapping, NVLink-bound), the other group copies chunk t from the user's buffer
+// into staging and chunk t-2 from staging to the user's output (HBM-bound).  One barrier per
+// stage; three staging regions rotate.  A message of one chunk degenerates to copy-in,
+// barrier, reduce, barrier, copy-out.
 template <typename T>
 __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
@@ -88,56 +91,68 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   const size_t N = a.count;
   const size_t H = 2 * quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
   const size_t hoff = half_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq);
+  const size_t region = (H / 3) & ~(size_t)4095;
   size_t ce = chunk_elems;
-  if (ce * es > H) ce = H / es;
+  if (ce * es > region) ce = region / es;
   ce = ce / (vi * n) * (vi * n);
   if (ce == 0) ce = vi * n;
+  const uint32_t nch = (uint32_t)((N + ce - 1) / ce);
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
-  char* mine = a.stage[r] + hoff;
-  char* mc = a.mc_stage + hoff;
-  for (size_t off = 0; off < N; off += ce) {
-    size_t len = N - off < ce ? N - off : ce;
-    size_t lo, hi;
-    block_range(len * es, p.block, p.nblocks, &lo, &hi);
-    copy_span(mine + lo, send + off * es + lo, hi - lo);
-    block_barrier(p);
-    size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
-    size_t b0 = (size_t)r * sl, b1 = b0 + sl;
-    if (b0 > len) b0 = len;
-    if (b1 > len) b1 = len;
-    size_t slo, shi;
-    block_range((b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
-    // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
-    size_t nvec = (shi - slo + 15) / 16;
-    char* base = mc + b0 * es + slo;
-    // four switch reductions in flight per thread: one round trip through the NVSwitch takes
-    // a few microseconds, so the link only fills with several hundred KiB outstanding per SM
-    const size_t nt = blockDim.x;
-    size_t i = threadIdx.x;
-    for (; i + 3 * nt < nvec; i += 4 * nt) {
-      uint4 v0 = Multimem<T>::ld_reduce(base + i * 16);
-      uint4 v1 = Multimem<T>::ld_reduce(base + (i + nt) * 16);
-      uint4 v2 = Multimem<T>::ld_reduce(base + (i + 2 * nt) * 16);
-      uint4 v3 = Multimem<T>::ld_reduce(base + (i + 3 * nt) * 16);
-      if (a.has_scale) {
-        v0 = Multimem<T>::scale(v0, a.scale);
-        v1 = Multimem<T>::scale(v1, a.scale);
-        v2 = Multimem<T>::scale(v2, a.scale);
-        v3 = Multimem<T>::scale(v3, a.scale);
+  Lane lr, lc;
+  bool do_red, do_copy;
+  split_lanes(nch > 1, 8, &lr, &lc, &do_red, &do_copy);
+  for (uint32_t t = 0; t <= nch + 1; ++t) {
+    if (do_copy && t < nch) {  // stage in chunk t
+      size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce, lo, hi;
+      block_range(len * es, p.block, p.nblocks, &lo, &hi);
+      copy_span(a.stage[r] + hoff + (t % 3) * region + lo, send + off * es + lo, hi - lo, lc);
+    }
+    if (do_red && t >= 1 && t - 1 < nch) {  // switch-reduce my slice of chunk t-1, broadcast it
+      uint32_t c = t - 1;
+      size_t off = (size_t)c * ce, len = N - off < ce ? N - off : ce;
+      size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+      size_t b0 = (size_t)r * sl, b1 = b0 + sl;
+      if (b0 > len) b0 = len;
+      if (b1 > len) b1 = len;
+      size_t slo, shi;
+      block_range((b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
+      // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
+      size_t nvec = (shi - slo + 15) / 16;
+      char* base = a.mc_stage + hoff + (c % 3) * region + b0 * es + slo;
+      const size_t nt = lr.nt;
+      size_t i = lr.tid;
+      // four switch reductions in flight per thread: a round trip through the NVSwitch takes
+      // microseconds, the link only fills with a lot of data outstanding
+      for (; i + 3 * nt < nvec; i += 4 * nt) {
+        uint4 v0 = Multimem<T>::ld_reduce(base + i * 16);
+        uint4 v1 = Multimem<T>::ld_reduce(base + (i + nt) * 16);
+        uint4 v2 = Multimem<T>::ld_reduce(base + (i + 2 * nt) * 16);
+        uint4 v3 = Multimem<T>::ld_reduce(base + (i + 3 * nt) * 16);
+        if (a.has_scale) {
+          v0 = Multimem<T>::scale(v0, a.scale);
+          v1 = Multimem<T>::scale(v1, a.scale);
+          v2 = Multimem<T>::scale(v2, a.scale);
+          v3 = Multimem<T>::scale(v3, a.scale);
+        }
+        multimem_st(base + i * 16, v0);
+        multimem_st(base + (i + nt) * 16, v1);
+        multimem_st(base + (i + 2 * nt) * 16, v2);
+        multimem_st(base + (i + 3 * nt) * 16, v3);
       }
-      multimem_st(base + i * 16, v0);
-      multimem_st(base + (i + nt) * 16, v1);
-      multimem_st(base + (i + 2 * nt) * 16, v2);
-      multimem_st(base + (i + 3 * nt) * 16, v3);
+      for (; i < nvec; i += nt) {
+        uint4 v = Multimem<T>::ld_reduce(base + i * 16);
+        if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
+        multimem_st(base + i * 16, v);
+      }
     }
-    for (; i < nvec; i += nt) {
-      uint4 v = Multimem<T>::ld_reduce(base + i * 16);
-      if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
-      multimem_st(base + i * 16, v);
+    if (do_copy && t >= 2) {  // stage out chunk t-2
+      uint32_t c = t - 2;
+      size_t off = (size_t)c * ce, len = N - off < ce ? N - off : ce, lo, hi;
+      block_range(len * es, p.block, p.nblocks, &lo, &hi);
+      copy_span(recv + off * es + lo, a.stage[r] + hoff + (c % 3) * region + lo, hi - lo, lc);
     }
-    block_barrier(p);
-    copy_span(recv + off * es + lo, mine + lo, hi - lo);
+    if (t <= nch) block_barrier(p);
   }
 }
 

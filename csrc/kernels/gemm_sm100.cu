@@ -34,6 +34,7 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int UMMA_K = 16;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy of the all-gather mover
+constexpr int EPI_CHUNK_BYTES = BM * 32 * 2;  // one 32-column chunk of a tile in bf16
 
 struct __align__(8) SmemCtl {
   uint64_t full[STAGES];
@@ -107,62 +108,95 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
 }
 
 // ---- all-gather mover: one thread per CTA drives bulk copies through the (otherwise unused)
-// operand ring; unit = kAgUnitRows rows of my shard, contiguous in memory.
+// operand ring; unit = kAgUnitRows rows of my shard, contiguous in memory.  Loads run two
+// pieces ahead of the stores; a piece is read from HBM once and stored to every peer.
+struct PieceIter {
+  int u;        // current unit
+  size_t o;     // byte offset inside the unit
+  bool valid;
+};
+__device__ __forceinline__ size_t unit_bytes(const GemmParams& p, int u) {
+  int rows = min(kAgUnitRows, p.rows_per_rank - u * kAgUnitRows);
+  return (size_t)rows * (size_t)p.K * 2;
+}
+__device__ __forceinline__ void piece_next(const GemmParams& p, int units, PieceIter& it) {
+  it.o += COPY_PIECE;
+  if (it.o >= unit_bytes(p, it.u)) {
+    it.o = 0;
+    it.u += p.comm_ctas;
+    it.valid = it.u < units;
+  }
+}
 __device__ void ag_mover(const GemmParams& p, char* ring, SmemCtl* ctl, int cta, uint32_t epoch) {
   const int n = p.coll.nranks, r = p.coll.rank;
   const size_t row_bytes = (size_t)p.K * 2;
   const int units = (p.rows_per_rank + kAgUnitRows - 1) / kAgUnitRows;
   const char* src = (const char*)p.a_local;
+  const size_t shard_off = (size_t)r * p.rows_per_rank * row_bytes;
   uint32_t phase_bits = 0;  // parity of copy_full[s], one bit per stage
-  int stage = 0;
-  for (int u = cta; u < units; u += p.comm_ctas) {
-    int rows = min(kAgUnitRows, p.rows_per_rank - u * kAgUnitRows);
-    size_t bytes = (size_t)rows * row_bytes;
-    size_t off0 = (size_t)u * kAgUnitRows * row_bytes;
-    size_t dst_off = (size_t)r * p.rows_per_rank * row_bytes + off0;
-    for (size_t o = 0; o < bytes; o += COPY_PIECE) {
-      uint32_t len = (uint32_t)min((size_t)COPY_PIECE, bytes - o);
-      char* buf = ring + (size_t)stage * STAGE_BYTES;
-      // the stores that last read this buffer were drained by wait_group.read below
-      mbar_expect_tx(&ctl->copy_full[stage], len);
-      bulk_g2s(buf, src + off0 + o, len, &ctl->copy_full[stage]);
-      if (!mbar_wait(&ctl->copy_full[stage], (phase_bits >> stage) & 1u, p.coll.timeout_ns, &ctl->abort)) return;
-      phase_bits ^= 1u << stage;
-      for (int k = 1; k < n; ++k) {
-        int q = (r + k) % n;
-        bulk_s2g((char*)p.ag_buf[q] + dst_off + o, buf, len);
-      }
-      if (p.copy_own) bulk_s2g((char*)p.ag_buf[r] + dst_off + o, buf, len);
-      bulk_commit();
-      stage = (stage + 1) % STAGES;
-      if (stage == 0) bulk_wait_read0();  // ring wrapped: sources must have been read
+  PieceIter ld{cta, 0, cta < units}, st = ld;
+  auto issue_load = [&](const PieceIter& it, int k) {
+    size_t ub = unit_bytes(p, it.u);
+    uint32_t len = (uint32_t)min((size_t)COPY_PIECE, ub - it.o);
+    int s = k % STAGES;
+    mbar_expect_tx(&ctl->copy_full[s], len);
+    bulk_g2s(ring + (size_t)s * STAGE_BYTES, src + (size_t)it.u * kAgUnitRows * row_bytes + it.o, len, &ctl->copy_full[s]);
+  };
+  int loaded = 0;
+  for (; loaded < 2 && ld.valid; ++loaded) {
+    issue_load(ld, loaded);
+    piece_next(p, units, ld);
+  }
+  for (int k = 0; st.valid; ++k) {
+    const int s = k % STAGES;
+    if (!mbar_wait(&ctl->copy_full[s], (phase_bits >> s) & 1u, p.coll.timeout_ns, &ctl->abort)) return;
+    phase_bits ^= 1u << s;
+    const size_t ub = unit_bytes(p, st.u);
+    const uint32_t len = (uint32_t)min((size_t)COPY_PIECE, ub - st.o);
+    const size_t dst_off = shard_off + (size_t)st.u * kAgUnitRows * row_bytes + st.o;
+    char* buf = ring + (size_t)s * STAGE_BYTES;
+    for (int q1 = 1; q1 < n; ++q1) bulk_s2g((char*)p.ag_buf[(r + q1) % n] + dst_off, buf, len);
+    if (p.copy_own) bulk_s2g((char*)p.ag_buf[r] + dst_off, buf, len);
+    bulk_commit();
+    const bool unit_done = st.o + len >= ub;
+    const int unit = st.u;
+    piece_next(p, units, st);
+    if (ld.valid) {
+      // the buffer of piece k+2 was last read by the stores of piece k-2: let all but the
+      // newest store group finish reading, then refill it
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      issue_load(ld, k + 2);
+      piece_next(p, units, ld);
     }
-    bulk_wait_all();  // this unit's bytes have been written
-    __threadfence_system();
-    for (int k = 1; k < n; ++k) {
-      int q = (r + k) % n;
-      dev::st_release_sys(&p.fflags[q]->ag_ready[r][u], epoch);
+    if (unit_done) {
+      bulk_wait_all();  // this unit's bytes have been written
+      __threadfence_system();
+      for (int q1 = 1; q1 < n; ++q1) dev::st_release_sys(&p.fflags[(r + q1) % n]->ag_ready[r][unit], epoch);
+      if (p.copy_own) dev::st_release_sys(&p.fflags[r]->ag_ready[r][unit], epoch);
     }
-    if (p.copy_own) dev::st_release_sys(&p.fflags[r]->ag_ready[r][u], epoch);
   }
 }
 
 // ---- reduce phase of GEMM -> reduce-scatter: out = sum over source slots, fixed order.
+// Partials sit tile-major: [slot][row block][column block][32-column chunk][128 rows][32 cols],
+// which is what lets the epilogue ship each 8 KB chunk with one bulk store.
 __device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas, int tiles_m, int tiles_n) {
   const int n = p.coll.nranks, r = p.coll.rank;
   const int tid = threadIdx.x;
   const FusedFlags* mine = p.fflags[r];
   const __nv_bfloat16* slots = (const __nv_bfloat16*)p.rs_buf[r];
   __nv_bfloat16* out = (__nv_bfloat16*)p.rs_out;
-  const size_t slot_elems = (size_t)p.rows_per_rank * p.N;
-  const uint32_t per_call = (uint32_t)tiles_n * 4u;  // four epilogue warps count each tile in
+  const size_t tile_elems = (size_t)BM * BN;
+  const size_t slot_elems = (size_t)tiles_m * tiles_n * tile_elems;
+  const uint32_t per_call = (uint32_t)tiles_n;  // one count per delivered tile
+  volatile int* abort = &ctl->abort;
   for (int item = cta; item < tiles_m * tiles_n; item += nctas) {
     int m_in = item % tiles_m, n_blk = item / tiles_m;
     if (tid < n) {
       uint32_t want = dev::ld_volatile(&mine->rs_expect[tid][m_in]) + per_call;
-      if (!ctl->abort && !dev::wait_flag_ge(&mine->rs_done[tid][m_in], want, p.coll.timeout_ns)) {
+      if (!*abort && !dev::wait_flag_ge(&mine->rs_done[tid][m_in], want, p.coll.timeout_ns)) {
         dev::report_error(p.coll.status, kDevGemmTimeout, r, tid, m_in, want);
-        ctl->abort = 1;
+        *abort = 1;
       }
     }
     __syncthreads();
@@ -170,20 +204,23 @@ __device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas,
     int rows = min(BM, p.rows_per_rank - row0);
     int cols = min(BN, p.N - col0);
     int vec_per_row = cols / 8;  // N % 8 == 0
+    const size_t tile_base = ((size_t)m_in * tiles_n + n_blk) * tile_elems;
     for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
       int rr = i / vec_per_row, cv = i % vec_per_row;
-      size_t e = (size_t)(row0 + rr) * p.N + col0 + cv * 8;
+      // inside a 64-byte row the four 16-byte pieces are rotated by the row number (the
+      // epilogue does that to spread its shared-memory stores over the banks)
+      size_t e_in = tile_base + (size_t)(cv / 4) * (BM * 32) + (size_t)rr * 32 + (size_t)(((cv % 4) + rr) & 3) * 8;
       float acc[8];
       uint4 raw[kMaxRanks];
 #pragma unroll
-      for (int s = 0; s < kMaxRanks; ++s)
-        if (s < n) raw[s] = *(const uint4*)(slots + (size_t)s * slot_elems + e);
+      for (int s2 = 0; s2 < kMaxRanks; ++s2)
+        if (s2 < n) raw[s2] = *(const uint4*)(slots + (size_t)s2 * slot_elems + e_in);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-      for (int s = 0; s < kMaxRanks; ++s) {
-        if (s < n) {
-          const __nv_bfloat16* h = (const __nv_bfloat16*)&raw[s];
+      for (int s2 = 0; s2 < kMaxRanks; ++s2) {
+        if (s2 < n) {
+          const __nv_bfloat16* h = (const __nv_bfloat16*)&raw[s2];
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(h[j]);
         }
@@ -191,7 +228,7 @@ __device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas,
       alignas(16) __nv_bfloat16 res[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) res[j] = __float2bfloat16_rn(acc[j]);
-      *(uint4*)(out + e) = *(const uint4*)res;
+      *(uint4*)(out + (size_t)(row0 + rr) * p.N + col0 + cv * 8) = *(const uint4*)res;
     }
     __syncthreads();
   }
@@ -202,7 +239,8 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
                           int cta, int nctas, char* smem_raw) {
   // operand ring first (1024-byte aligned for the 128-byte swizzle), control words after it
   char* ring = (char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  SmemCtl* ctl = (SmemCtl*)(ring + (size_t)STAGES * STAGE_BYTES);
+  char* epi_stage = ring + (size_t)STAGES * STAGE_BYTES;  // 2 x 8 KB, reduce-scatter epilogue
+  SmemCtl* ctl = (SmemCtl*)(epi_stage + 2 * EPI_CHUNK_BYTES);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n = p.coll.nranks, r = p.coll.rank;
   const bool fused = n > 1 && p.mode != kGemmPlain;
@@ -345,46 +383,73 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const int row_in = tl.m_in * BM + lane_grp * 32 + lane;  // row inside the shard
-      const bool row_ok = row_in < p.rows_per_rank;
-      __nv_bfloat16* dst_row;
-      int ld;
-      if (p.mode == kGemmReduceScatter && fused) {
-        // partial tile goes to the owner's slot number `r`
-        ld = p.N;
-        dst_row = (__nv_bfloat16*)p.rs_buf[tl.shard] + ((size_t)r * p.rows_per_rank + row_in) * ld;
-      } else {
-        ld = p.ldc;
-        dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * ld;
-      }
       const uint32_t t_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_grp * 32) << 16);
+      if (p.mode == kGemmReduceScatter && fused) {
+        // Partial tile -> the owner's slot number r.  Each 32-column chunk (128 rows x 64 bytes
+        // = 8 KB, contiguous at the destination) is staged in shared memory and shipped with
+        // ONE bulk store over NVLink; two staging buffers alternate.
+        const bool issuer = warp == 2 && lane == 0;
+        const size_t tile_elems = (size_t)BM * BN;
+        __nv_bfloat16* dst_tile = (__nv_bfloat16*)p.rs_buf[tl.shard] +
+                                  (((size_t)r * tiles_m + tl.m_in) * tiles_n + tl.n_blk) * tile_elems;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
-        tmem_ld_wait();
-        const int col = tl.n_blk * BN + c * 32;
-        if (row_ok) {
+        for (int c = 0; c < BN / 32; ++c) {
+          char* sbuf = epi_stage + (c & 1) * EPI_CHUNK_BYTES;
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // store c-2 has read sbuf
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
+          uint4* srow = (uint4*)(sbuf + (size_t)(lane_grp * 32 + lane) * 64);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            if (col + j * 8 < p.N) {
-              alignas(16) __nv_bfloat162 h[4];
+            alignas(16) __nv_bfloat162 h[4];
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                h[q] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]), __uint_as_float(v[j * 8 + 2 * q + 1]));
-              *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h;
+            for (int q = 0; q < 4; ++q)
+              h[q] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]), __uint_as_float(v[j * 8 + 2 * q + 1]));
+            srow[(j + lane) & 3] = *(const uint4*)h;  // rotated so a warp's stores spread over the banks
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (issuer) {
+            bulk_s2g(dst_tile + (size_t)c * (BM * 32), sbuf, EPI_CHUNK_BYTES);
+            bulk_commit();
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
+        if (issuer) {
+          bulk_wait_all();  // the whole tile has been written at the owner
+          __threadfence_system();
+          red_release_sys_add(&p.fflags[tl.shard]->rs_done[r][tl.m_in], 1u);
+        }
+      } else {
+        const int row_in = tl.m_in * BM + lane_grp * 32 + lane;  // row inside the shard
+        const bool row_ok = row_in < p.rows_per_rank;
+        __nv_bfloat16* dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
+          const int col = tl.n_blk * BN + c * 32;
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (col + j * 8 < p.N) {
+                alignas(16) __nv_bfloat162 h[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  h[q] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]), __uint_as_float(v[j * 8 + 2 * q + 1]));
+                *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h;
+              }
             }
           }
         }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
-      if (p.mode == kGemmReduceScatter && fused) {
-        // everything this warp stored for the tile is visible before the count
-        __threadfence_system();
+        tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) red_release_sys_add(&p.fflags[tl.shard]->rs_done[r][tl.m_in], 1u);
+        if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
       }
     }
   }
@@ -408,7 +473,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       if (p.mode == kGemmReduceScatter && fused) {
         FusedFlags* f = p.fflags[r];
         for (int s = 0; s < n; ++s)
-          for (int m = 0; m < tiles_m; ++m) f->rs_expect[s][m] += (uint32_t)tiles_n * 4u;
+          for (int m = 0; m < tiles_m; ++m) f->rs_expect[s][m] += (uint32_t)tiles_n;
       }
       me->opseq = proto.opseq + 1u;
       __threadfence();
@@ -468,7 +533,7 @@ Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, u
   return kSuccess;
 }
 
-size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
+size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + 2 * gemmk::EPI_CHUNK_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
 
 int gemm_default_grid(int device) {
   int sms = 0;

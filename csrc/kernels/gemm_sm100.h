@@ -36,7 +36,7 @@ struct GemmParams {
   int copy_own;             // all-gather: also place my own shard in the gathered buffer
   const void* a_local;      // all-gather: my shard, bf16 [rows_per_rank, K]
   void* ag_buf[kMaxRanks];  // all-gather: every rank's gathered-A buffer [M, K]; [rank] is mine
-  void* rs_buf[kMaxRanks];  // reduce-scatter: every rank's partial buffer [nranks][rows_per_rank][N]
+  void* rs_buf[kMaxRanks];  // reduce-scatter: every rank's partial buffer, tile-major [nranks][row blocks][col blocks][128 x 256]
   void* rs_out;             // reduce-scatter: bf16 [rows_per_rank, N]
   FusedFlags* fflags[kMaxRanks];
   CollArgs coll;            // rank, nranks, control blocks, status words, timeout

@@ -97,7 +97,15 @@ inline void block_range(size_t total_bytes, int block, int nblocks, size_t* lo, 
   *hi = h;
 }
 
-inline void copy_span(char* dst, const char* src, size_t bytes) {
+struct Lane {
+  int tid, nt;
+};
+inline Lane full_lane() { return Lane{0, 1}; }
+inline void split_lanes(bool, int, Lane* push, Lane* drain, bool* do_push, bool* do_drain) {
+  *push = *drain = full_lane();  // one thread plays both groups, one after the other
+  *do_push = *do_drain = true;
+}
+inline void copy_span(char* dst, const char* src, size_t bytes, Lane) {
   if (bytes) memmove(dst, src, bytes);
 }
 
@@ -121,7 +129,7 @@ template <typename A> inline A apply_scale(A v, float s) { return (A)((double)v 
 template <> inline float apply_scale<float>(float v, float s) { return v * s; }
 
 template <typename TI, typename TO, int OP>
-inline void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale) {
+inline void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale, Lane) {
   using A = typename Acc<TI>::type;
   for (size_t i = 0; i < n; ++i) {
     A acc = to_acc<TI>(slots[0][i]);

@@ -60,15 +60,25 @@ LaunchPlan plan_collective(const TunerInput& in) {
   if (blocks_env > 0) blocks = std::min<long>(blocks_env, in.max_blocks);
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   p.blocks = (int)blocks;
-  // Chunk: as large as the staging region allows (fewest barriers).
+  // Chunk: messages that span several chunks overlap their NVLink and HBM phases (see
+  // coll_bodies.inl), so aim for about eight chunks, but never chunks so small that the
+  // per-chunk barrier (a few microseconds) shows, nor larger than the staging region.
   const size_t H = 2 * Q;
+  auto pick = [&](size_t total_bytes, size_t min_bytes, size_t max_bytes) {
+    size_t c = total_bytes / 8;
+    if (c < min_bytes) c = min_bytes;
+    if (c > max_bytes) c = max_bytes;
+    c &= ~(size_t)4095;
+    return c ? c : (size_t)4096;
+  };
   switch (in.kind) {
     case kCollAllReduce:
-      if (p.algo == kAlgoNvls) p.chunk_elems = H / es;
+      if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 2u << 20, (H / 3) & ~(size_t)4095) / es;
       else p.chunk_elems = (slot_bytes_of(H / 2, n) / es) * (size_t)n;
       break;
     case kCollBroadcast: p.chunk_elems = Q / es; break;
-    default: p.chunk_elems = slot / es; break;
+    case kCollReduce: p.chunk_elems = slot / es; break;
+    default: p.chunk_elems = pick(in.count * es, 1u << 20, slot) / es; break;  // per-rank bytes
   }
   if (p.chunk_elems == 0) p.chunk_elems = 1;
   return p;
