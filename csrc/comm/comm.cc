@@ -107,7 +107,11 @@ Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cf
   memset(status_, 0, kStatusWords * sizeof(uint32_t));
 
   // Control segment (stateful) and staging segment (scratch).
-  AMEM_TRY(sym_alloc(round_up(sizeof(CtrlBlock) + (1u << 16), gran_), kStateful, kTagP2P, &ctrl_));
+  // The control segment is 2 MiB.  By default it stays resident through a pause: that halves
+  // the handles every rank has to export, import and map again on resume, for 2 MiB that are
+  // not returned.  AMEM_PAUSE_CONTROL=1 releases it too (saved to and restored from host memory).
+  int ctrl_cat = env_long("AMEM_PAUSE_CONTROL", 0) ? kStateful : kResident;
+  AMEM_TRY(sym_alloc(round_up(sizeof(CtrlBlock) + (1u << 16), gran_), ctrl_cat, kTagP2P, &ctrl_));
   AMEM_TRY(be_->memset_zero(ctrl_.va[rank_], ctrl_.size, dev_));
   AMEM_TRY(be_->copies_sync(dev_));
   AMEM_TRY(sym_alloc(round_up(stage, gran_), kScratch, kTagP2P, &stage_));

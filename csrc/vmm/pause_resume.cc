@@ -71,7 +71,7 @@ Status pause_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, PeerE
   {  // 1. start every host save; they run back to back on the side stream
     Phase p("amem.pause.offload", &st->offload_us);
     for (auto& a : recs) {
-      if (!is_local(a) || a.state != kMemAlloc) continue;
+      if (!is_local(a) || a.state != kMemAlloc || a.category == kResident) continue;
       bool keep = a.category == kStateful && a.tag != opt.offload_free_tag;
       if (!keep) continue;
       if (!a.shadow) AMEM_TRY(be->host_alloc(a.size, &a.shadow));
@@ -85,7 +85,7 @@ Status pause_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, PeerE
   {  // 2. let go of the peers' memory while the copies run (no data to save: the owner has it)
     Phase p("amem.pause.release_import", &st->release_import_us);
     for (auto& a : recs) {
-      if (is_local(a) || a.state != kMemAlloc) continue;
+      if (is_local(a) || a.state != kMemAlloc || a.category == kResident) continue;
       AMEM_TRY(be->unmap(a.va, a.size));
       AMEM_TRY(be->release(a.handle));
       a.handle = 0;
@@ -99,7 +99,7 @@ Status pause_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, PeerE
     Phase p("amem.pause.release_local", &st->release_local_us);
     AMEM_TRY(be->copies_sync(dev));
     for (auto& a : recs) {
-      if (!is_local(a) || (a.state != kMemAlloc && a.state != kMemOffloading)) continue;
+      if (!is_local(a) || (a.state != kMemAlloc && a.state != kMemOffloading) || a.category == kResident) continue;
       if (a.mc_handle) AMEM_TRY(be->mc_unbind(a.mc_handle, a.dev, a.mc_offset, a.size));
       AMEM_TRY(be->unmap(a.va, a.size));
       AMEM_TRY(be->release(a.handle));

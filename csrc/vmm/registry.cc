@@ -126,7 +126,7 @@ void Registry::stats(MemStats* out) {
     } else {
       out->n_local++;
       if (a.category == kScratch) out->scratch_bytes += a.size;
-      else out->stateful_bytes += a.size;
+      else out->stateful_bytes += a.size;  // saved-on-pause and resident protocol state
       if (a.mc_handle) out->multicast_bytes += a.size;
     }
     if (a.state == kMemHole) out->paused_bytes += a.size;

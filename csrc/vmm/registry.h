@@ -32,7 +32,9 @@ inline bool from_peer(int type) { return type > kLocalSymm; }
 // output lines up with its "caller_N" lines.
 enum CallerTag : int { kTagDefault = 0, kTagP2P = 1, kTagFabric = 2, kTagPosix = 3, kTagSymm = 4, kTagNvls = 5, kTagP2PPeer = 7, kTagProxy = 9, kTagSymmPeer = 10, kMaxCaller = 16 };
 
-enum Category : int { kStateful = 0, kScratch = 1 };
+// kStateful: saved to a host shadow on pause; kScratch: dropped without a copy; kResident: small
+// protocol state that stays mapped through a pause (not released, not re-imported).
+enum Category : int { kStateful = 0, kScratch = 1, kResident = 2 };
 
 struct Allocation {
   uint64_t va = 0;

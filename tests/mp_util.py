@@ -18,9 +18,15 @@ def run_ranks(fn, world, args=(), env=None, timeout=120, expect_fail=False):
     Returns the list of per-rank results (or (status, payload) pairs when expect_fail)."""
     base_env = {"AMEM_BACKEND": "mock", "GMM_LOG": os.environ.get("GMM_LOG", "2")}
     base_env.update(env or {})
-    os.environ.update(base_env)
+    saved = {k: os.environ.get(k) for k in base_env}
+    os.environ.update(base_env)   # the unique id below is made under the same settings
     from asystem_amem_b200 import get_unique_id
     uid = get_unique_id()
+    for k, v in saved.items():    # do not leak this test's settings into the next one
+        if v is None:
+            os.environ.pop(k, None)
+        else:
+            os.environ[k] = v
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_entry, args=(fn, r, world, uid, q, base_env, args)) for r in range(world)]

@@ -9,7 +9,7 @@ import pytest
 
 from mp_util import run_ranks
 
-FAST = {"AMEM_OP_TIMEOUT_MS": "1500", "AMEM_INIT_TIMEOUT_MS": "1500", "AMEM_DEVICE_TIMEOUT_MS": "700", "GMM_LOG": "0"}
+FAST = {"AMEM_PAUSE_CONTROL": "1", "AMEM_OP_TIMEOUT_MS": "1500", "AMEM_INIT_TIMEOUT_MS": "1500", "AMEM_DEVICE_TIMEOUT_MS": "700", "GMM_LOG": "0"}
 
 
 def _never_joins(rank, world, uid):

@@ -56,7 +56,7 @@ def _config1(rank, world, uid, port):
 
 def test_config1_gloo_world2_ten_cycles():
     port = 29000 + os.getpid() % 2000
-    res = run_ranks(_config1, 2, args=(port,), timeout=300)
+    res = run_ranks(_config1, 2, args=(port,), timeout=300, env={"AMEM_PAUSE_CONTROL": "1"})
     for r in res:
         assert r["close"] and r["bitwise"], r
         assert r["leak_bytes"] == 0 and r["leak_maps"] == 0, r
@@ -112,7 +112,7 @@ def _scope_and_guard(rank, world, uid):
 
 
 def test_scope_guard_and_user_memory():
-    for r in run_ranks(_scope_and_guard, 2):
+    for r in run_ranks(_scope_and_guard, 2, env={"AMEM_PAUSE_CONTROL": "1"}):
         assert all(r.values()), r
 
 
@@ -153,4 +153,34 @@ def _split_hybrid(rank, world, uid, cycles):
 
 
 def test_split_communicators_pause_together():
-    assert all(run_ranks(_split_hybrid, 4, args=(5,), env={"AMEM_STAGE_MB": "8"}))
+    assert all(run_ranks(_split_hybrid, 4, args=(5,), env={"AMEM_STAGE_MB": "8", "AMEM_PAUSE_CONTROL": "1"}))
+
+
+def _resident_control(rank, world, uid):
+    """Default mode: the 2 MiB control segment stays mapped through a pause, only staging goes."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator, backend_usage, pause_all, resume_all
+    comm = Communicator(world, rank, uid)
+    x = np.arange(4096, dtype=np.float32) * (rank + 1)
+    first = x.copy()
+    comm.all_reduce(first)
+    before = backend_usage()
+    ok = True
+    for _ in range(3):
+        pause_all()
+        during = backend_usage()
+        ok = ok and during["mappings"] == world            # my control block and the peers'
+        ok = ok and 0 < during["physical_bytes"] < before["physical_bytes"]
+        resume_all()
+        y = x.copy()
+        comm.all_reduce(y)
+        ok = ok and bool(np.array_equal(y, first))
+    st = comm.pause_resume_stats()
+    ok = ok and st["bytes_offloaded"] == 0 and st["n_release_peer"] == world - 1
+    ok = ok and backend_usage() == before
+    comm.destroy()
+    return bool(ok)
+
+
+def test_control_segment_stays_resident_by_default():
+    assert all(run_ranks(_resident_control, 3))

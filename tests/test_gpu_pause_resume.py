@@ -11,9 +11,10 @@ from gpu_util import run_emulated
 pytestmark = pytest.mark.gpu
 
 
-def test_single_rank_pause_frees_memory_and_keeps_user_data():
+def test_single_rank_pause_frees_memory_and_keeps_user_data(monkeypatch):
     from asystem_amem_b200 import Communicator, NcclError, get_unique_id, mem_alloc, mem_free, mem_stats, pause_all, resume_all
     torch.cuda.set_device(0)
+    monkeypatch.setenv("AMEM_PAUSE_CONTROL", "1")     # release the control segment as well
     comm = Communicator(1, 0, get_unique_id())
     stage = comm.info()["stage_bytes"]
     nbytes = 64 << 20
@@ -107,7 +108,7 @@ def test_process_wide_pause_with_emulated_ranks():
             f0, _ = torch.cuda.mem_get_info()
             pause_all()
             freed = torch.cuda.mem_get_info()[0] - f0
-            assert mem_stats()["live_bytes"] == 0
+            assert mem_stats()["live_bytes"] == world * world * (2 << 20)   # only the resident control blocks
             resume_all()
         barrier.wait()
         y = torch.full((4096,), float(rank + 1), device="cuda")
