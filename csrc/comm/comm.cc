@@ -87,7 +87,7 @@ Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cf
   p2p_slot_bytes_ = cfg.p2p_slot_bytes ? cfg.p2p_slot_bytes : (size_t)env_long("AMEM_P2P_SLOT_KB", device ? 64 : 8) << 10;
   if (stage < p2p_area_bytes(p2p_slot_bytes_) + (1u << 20))
     return fail(kInvalidArgument, "staging of %zu bytes is too small for the point-to-point area", stage);
-  max_blocks_ = cfg.max_blocks ? cfg.max_blocks : (int)env_long("AMEM_MAX_BLOCKS", emulate ? 8 : 64);
+  max_blocks_ = cfg.max_blocks ? cfg.max_blocks : (int)env_long("AMEM_MAX_BLOCKS", emulate ? 8 : 128);
   if (!device) max_blocks_ = 1;
   if (max_blocks_ > kMaxBlocks) max_blocks_ = kMaxBlocks;
   timeout_ns_ = (unsigned long long)env_long("AMEM_DEVICE_TIMEOUT_MS", 20000) * 1000000ull;

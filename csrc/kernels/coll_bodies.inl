@@ -33,7 +33,7 @@ AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
   Lane lp, ld;
   bool do_push, do_drain;
-  split_lanes(nch > 1, 10, &lp, &ld, &do_push, &do_drain);
+  split_lanes(nch > 1, 8, &lp, &ld, &do_push, &do_drain);
   for (uint32_t t = 0; t <= nch; ++t) {
     if (do_push && t < nch) {
       size_t off = (size_t)t * cb;
@@ -76,7 +76,7 @@ AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
   Lane lp, ld;
   bool do_push, do_drain;
-  split_lanes(nch > 1, 10, &lp, &ld, &do_push, &do_drain);
+  split_lanes(nch > 1, 8, &lp, &ld, &do_push, &do_drain);
   for (uint32_t t = 0; t <= nch; ++t) {
     if (do_push && t < nch) {
       size_t off = (size_t)t * cb;
@@ -121,7 +121,7 @@ AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems)
   const uint32_t nch = (uint32_t)((R + ce - 1) / ce);
   Lane lp, ld;
   bool do_push, do_drain;
-  split_lanes(nch > 1, 10, &lp, &ld, &do_push, &do_drain);
+  split_lanes(nch > 1, 6, &lp, &ld, &do_push, &do_drain);  // the reduce side reads n slots: it gets more warps
   for (uint32_t t = 0; t <= nch; ++t) {
     if (do_push && t < nch) {
       size_t off = (size_t)t * ce;

@@ -214,13 +214,8 @@ __device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int
   bool aligned = (((uintptr_t)out) % (VI * sizeof(TO)) == 0);
   for (int r = 0; r < nslots; ++r) aligned = aligned && (((uintptr_t)slots[r] & 15) == 0);
   size_t nvec = aligned ? n / VI : 0;
-  for (size_t i = t; i < nvec; i += nt) {
+  auto one = [&](size_t i, const uint4* raw) {
     A acc[VI];
-    uint4 raw[kMaxRanks];
-    // issue every slot's load before the first add so they are all in flight together
-#pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r)
-      if (r < nslots) raw[r] = ((const uint4*)slots[r])[i];
     {
       const TI* e = (const TI*)&raw[0];
 #pragma unroll
@@ -251,6 +246,27 @@ __device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int
 #pragma unroll
       for (int k = 0; k < VI; ++k) out[i * VI + k] = res[k];
     }
+  };
+  size_t i = t;
+  // two output vectors per thread per trip: 2 x nslots independent 16-byte loads in flight
+  for (; i + (size_t)nt < nvec; i += 2 * (size_t)nt) {
+    uint4 ra[kMaxRanks], rb[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      if (r < nslots) {
+        ra[r] = ((const uint4*)slots[r])[i];
+        rb[r] = ((const uint4*)slots[r])[i + nt];
+      }
+    }
+    one(i, ra);
+    one(i + nt, rb);
+  }
+  for (; i < nvec; i += nt) {
+    uint4 ra[kMaxRanks];
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r)
+      if (r < nslots) ra[r] = ((const uint4*)slots[r])[i];
+    one(i, ra);
   }
   for (size_t i = nvec * VI + t; i < n; i += nt) {
     A acc = to_acc<TI>(slots[0][i]);

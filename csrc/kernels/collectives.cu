@@ -122,23 +122,18 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
       char* base = a.mc_stage + hoff + (c % 3) * region + b0 * es + slo;
       const size_t nt = lr.nt;
       size_t i = lr.tid;
-      // four switch reductions in flight per thread: a round trip through the NVSwitch takes
+      // eight switch reductions in flight per thread: a round trip through the NVSwitch takes
       // microseconds, the link only fills with a lot of data outstanding
-      for (; i + 3 * nt < nvec; i += 4 * nt) {
-        uint4 v0 = Multimem<T>::ld_reduce(base + i * 16);
-        uint4 v1 = Multimem<T>::ld_reduce(base + (i + nt) * 16);
-        uint4 v2 = Multimem<T>::ld_reduce(base + (i + 2 * nt) * 16);
-        uint4 v3 = Multimem<T>::ld_reduce(base + (i + 3 * nt) * 16);
+      for (; i + 7 * nt < nvec; i += 8 * nt) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::ld_reduce(base + (i + j * nt) * 16);
         if (a.has_scale) {
-          v0 = Multimem<T>::scale(v0, a.scale);
-          v1 = Multimem<T>::scale(v1, a.scale);
-          v2 = Multimem<T>::scale(v2, a.scale);
-          v3 = Multimem<T>::scale(v3, a.scale);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
         }
-        multimem_st(base + i * 16, v0);
-        multimem_st(base + (i + nt) * 16, v1);
-        multimem_st(base + (i + 2 * nt) * 16, v2);
-        multimem_st(base + (i + 3 * nt) * 16, v3);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) multimem_st(base + (i + j * nt) * 16, v[j]);
       }
       for (; i < nvec; i += nt) {
         uint4 v = Multimem<T>::ld_reduce(base + i * 16);

@@ -67,12 +67,19 @@ __device__ __forceinline__ Tile tile_of(const GemmParams& p, int t, int tiles_m,
       o.m_in = t % tiles_m;
       o.n_blk = t / tiles_m;
     } else {
+      // Remote rows: bands of a few row blocks (all sources, all column blocks per band), so the
+      // tiles in flight share B tiles in L2 while the next band is still arriving.
       int u = t - own;
-      int per_m = (n - 1) * tiles_n;
-      o.m_in = u / per_m;
-      int v = u % per_m;
-      o.shard = (r - 1 - (v % (n - 1)) + 2 * n) % n;
-      o.n_blk = v / (n - 1);
+      const int GM2 = max(1, 16 / (n - 1));
+      const int band_tiles = GM2 * (n - 1) * tiles_n;
+      const int band = u / band_tiles;
+      const int first_m = band * GM2;
+      const int gm = min(GM2, tiles_m - first_m);
+      const int w = u - band * band_tiles;
+      o.m_in = first_m + w % gm;
+      const int rest = w / gm;
+      o.shard = (r - 1 - (rest % (n - 1)) + 2 * n) % n;
+      o.n_blk = rest / (n - 1);
     }
   } else {
     int per_shard = tiles_m * tiles_n;

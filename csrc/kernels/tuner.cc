@@ -64,21 +64,24 @@ LaunchPlan plan_collective(const TunerInput& in) {
   // coll_bodies.inl), so aim for about eight chunks, but never chunks so small that the
   // per-chunk barrier (a few microseconds) shows, nor larger than the staging region.
   const size_t H = 2 * Q;
-  auto pick = [&](size_t total_bytes, size_t min_bytes, size_t max_bytes) {
-    size_t c = total_bytes / 8;
-    if (c < min_bytes) c = min_bytes;
+  // A chunk costs one cross-rank barrier (several microseconds over NVLink): messages up to
+  // `single_bytes` go as one chunk, larger ones in about eight chunks of at least `min_bytes`.
+  auto pick = [&](size_t total_bytes, size_t single_bytes, size_t min_bytes, size_t max_bytes) {
+    size_t c = total_bytes <= single_bytes ? total_bytes : total_bytes / 8;
+    if (total_bytes > single_bytes && c < min_bytes) c = min_bytes;
     if (c > max_bytes) c = max_bytes;
-    c &= ~(size_t)4095;
+    c = (c + 4095) & ~(size_t)4095;
+    if (c > max_bytes) c = max_bytes & ~(size_t)4095;
     return c ? c : (size_t)4096;
   };
   switch (in.kind) {
     case kCollAllReduce:
-      if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 2u << 20, (H / 3) & ~(size_t)4095) / es;
+      if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 16u << 20, 8u << 20, (H / 3) & ~(size_t)4095) / es;
       else p.chunk_elems = (slot_bytes_of(H / 2, n) / es) * (size_t)n;
       break;
     case kCollBroadcast: p.chunk_elems = Q / es; break;
     case kCollReduce: p.chunk_elems = slot / es; break;
-    default: p.chunk_elems = pick(in.count * es, 1u << 20, slot) / es; break;  // per-rank bytes
+    default: p.chunk_elems = pick(in.count * es, 8u << 20, 4u << 20, slot) / es; break;  // per-rank bytes
   }
   if (p.chunk_elems == 0) p.chunk_elems = 1;
   return p;
