@@ -76,12 +76,12 @@ LaunchPlan plan_collective(const TunerInput& in) {
   };
   switch (in.kind) {
     case kCollAllReduce:
-      if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 16u << 20, 8u << 20, (H / 3) & ~(size_t)4095) / es;
+      if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, (H / 3) & ~(size_t)4095) / es;
       else p.chunk_elems = (slot_bytes_of(H / 2, n) / es) * (size_t)n;
       break;
     case kCollBroadcast: p.chunk_elems = Q / es; break;
     case kCollReduce: p.chunk_elems = slot / es; break;
-    default: p.chunk_elems = pick(in.count * es, 8u << 20, 4u << 20, slot) / es; break;  // per-rank bytes
+    default: p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, slot) / es; break;  // per-rank bytes
   }
   if (p.chunk_elems == 0) p.chunk_elems = 1;
   return p;
