@@ -90,9 +90,10 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   g.p.fflags[0] = (FusedFlags*)(ctrl[dev] + 1);
   if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);
   g.map_a_local = g.map_a;
-  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
-  int tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + kGemmBN - 1) / kGemmBN);
   int sms = gemm_default_grid(dev);
+  g.p.bn = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms);
+  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn)) != kSuccess) return R(s);
+  int tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + g.p.bn - 1) / g.p.bn);
   g.grid = tiles < sms ? tiles : sms;
   s = launch_gemm(g, stream);
   if (s == kSuccess && status_dev[dev][0]) s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_dev[dev][0]);
@@ -134,7 +135,6 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
     if ((s = make_tensor_map_bf16(&g.map_a, g.p.ag_buf[c->rank()], M, K, K, kGemmBM)) != kSuccess) return R(s);
     if ((s = make_tensor_map_bf16(&g.map_a_local, a_shard, rpr, K, K, kGemmBM)) != kSuccess) return R(s);
   }
-  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
   if (c->emulated()) {
     g.grid = emu_grid(n);
     g.p.comm_ctas = 1;
@@ -143,6 +143,8 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
     g.p.comm_ctas = n > 1 ? (int)env_long("AMEM_AG_COMM_CTAS", 16) : 0;
     if (g.p.comm_ctas > g.grid / 2) g.p.comm_ctas = g.grid / 2;
   }
+  g.p.bn = gemm_pick_bn(n * ((rpr + kGemmBM - 1) / kGemmBM), N, g.grid - g.p.comm_ctas);
+  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn)) != kSuccess) return R(s);
   return R(run_gemm(c, g, stream));
 }
 
@@ -167,6 +169,8 @@ ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int 
   g.p.K = K;
   g.p.rows_per_rank = rpr;
   g.p.rs_out = out;
+  g.grid = c->emulated() ? emu_grid(n) : gemm_default_grid(c->device());
+  g.p.bn = gemm_pick_bn(n * ((rpr + kGemmBM - 1) / kGemmBM), N, g.grid);
   if (n == 1) {
     g.p.mode = kGemmPlain;
     g.p.C = out;
@@ -175,14 +179,13 @@ ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int 
     g.p.mode = kGemmReduceScatter;
     Segment* seg = nullptr;
     // tile-major partials: every (row block, column block) occupies a full 128 x 256 tile
-    size_t tiles = (size_t)((rpr + kGemmBM - 1) / kGemmBM) * (size_t)((N + kGemmBN - 1) / kGemmBN);
-    if ((s = c->fused_segment(1, (size_t)n * tiles * kGemmBM * kGemmBN * 2, &seg)) != kSuccess) return R(s);
+    size_t tiles = (size_t)((rpr + kGemmBM - 1) / kGemmBM) * (size_t)((N + g.p.bn - 1) / g.p.bn);
+    if ((s = c->fused_segment(1, (size_t)n * tiles * kGemmBM * g.p.bn * 2, &seg)) != kSuccess) return R(s);
     for (int r = 0; r < n; ++r) g.p.rs_buf[r] = (void*)seg->va[r];
   }
   if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);
   g.map_a_local = g.map_a;
-  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, kGemmBN)) != kSuccess) return R(s);
-  g.grid = c->emulated() ? emu_grid(n) : gemm_default_grid(c->device());
+  if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn)) != kSuccess) return R(s);
   return R(run_gemm(c, g, stream));
 }
 

@@ -64,6 +64,12 @@ struct alignas(128) CtrlBlock {
   uint32_t p2p_rcvd[kMaxRanks][kP2PBlocks];       // my local count of chunks received from peer
   // small all-to-all scratch for counts (MoE routing): xchg[source rank][i]
   uint32_t xchg[kMaxRanks][256];
+  // chunk credits of the pipelined collectives, per block: cseq = chunks this block has moved so
+  // far (mine); ready[b][s] = written by rank s: its chunk number N has landed in my staging;
+  // freed[b][s] = written by rank s: it has drained my chunk number N from its staging
+  uint32_t cseq[kMaxBlocks];
+  uint32_t ready[kMaxBlocks][kMaxRanks];
+  uint32_t freed[kMaxBlocks][kMaxRanks];
 };
 
 enum DeviceError : uint32_t { kDevOk = 0, kDevBarrierTimeout = 1, kDevP2PTimeout = 2, kDevBadArgs = 3, kDevGemmTimeout = 4 };

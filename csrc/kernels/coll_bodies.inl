@@ -13,12 +13,79 @@
 // that the stores of one rank fan out over all NVLink destinations at once.
 AMEM_FN int peer_at(int rank, int n, int k, int block) { return (rank + 1 + (k - 1 + block) % (n - 1)) % n; }
 
-// All-gather, all-to-all and reduce-scatter share one skeleton.  Chunk t is PUSHED into the
-// peers' staging (NVLink-bound) while chunk t-1 is DRAINED from my own staging into the user's
-// buffer (HBM-bound): two groups of warps do the two jobs side by side and meet at one barrier
-// per chunk, so a large message moves at link speed instead of link + memory time.  Quarter
-// t % 2 of the operation's staging half holds chunk t; a quarter is rewritten only after the
-// barrier that follows its drain.
+// All-gather, all-to-all and reduce-scatter share one skeleton: every chunk is PUSHED into the
+// peers' staging (NVLink-bound) and then DRAINED from my own staging into the user's buffer
+// (HBM-bound).  A message of one chunk does push, one cross-rank barrier, drain.  A longer
+// message runs the two jobs on two groups of warps that never meet: they are coupled only by
+// per-block credits (CtrlBlock::ready / freed).  The pusher announces chunk N to each peer and
+// moves on; it only waits when it is about to overwrite quarter N % 2, for the peers' "drained
+// chunk N-2".  The drainer waits for every peer's chunk N, drains it and hands the quarter
+// back.  So the link never idles on a barrier, and the drain hides behind the next push.  The
+// operation ends when all peers have drained all of my chunks: staging is then free everywhere,
+// whatever protocol the next operation uses.
+AMEM_FN void credit_wait(Proto& p, bool want_ready, uint32_t want, Lane ln) {
+  const CollArgs& a = *p.a;
+  for (int q = ln.tid; q < a.nranks; q += ln.nt) {
+    if (q == a.rank) continue;
+    const uint32_t* f = want_ready ? &p.me->ready[p.block][q] : &p.me->freed[p.block][q];
+    if (*(volatile int*)p.abort_flag == 0 && !wait_flag_ge(f, want, a.timeout_ns)) {
+      report_error(a.status, kDevBarrierTimeout, a.rank, q, p.block, want);
+      *(volatile int*)p.abort_flag = 1;
+    }
+  }
+  lane_sync(ln);
+}
+AMEM_FN void credit_signal(Proto& p, bool is_ready, uint32_t value, Lane ln) {
+  const CollArgs& a = *p.a;
+  lane_sync(ln);  // everything the group stored (or finished reading) comes before the signal
+  for (int q = ln.tid; q < a.nranks; q += ln.nt) {
+    if (q == a.rank) continue;
+    fence_system();
+    st_release_sys(is_ready ? &a.ctrl[q]->ready[p.block][a.rank] : &a.ctrl[q]->freed[p.block][a.rank], value);
+  }
+}
+
+template <typename PushF, typename DrainF>
+AMEM_FN void run_chunks(const CollArgs& a, Proto& p, uint32_t nch, int push_sixteenths, PushF push, DrainF drain) {
+  if (nch == 0) return;
+  if (nch == 1) {
+    push(0u, full_lane());
+    block_barrier(p);
+    drain(0u, full_lane());
+    return;
+  }
+  Lane lp, ld;
+  bool do_push, do_drain;
+  split_lanes(true, push_sixteenths, &lp, &ld, &do_push, &do_drain);
+  const uint32_t base = ld_volatile(&p.me->cseq[p.block]);
+  auto push_step = [&](uint32_t t) {
+    if (t >= 2) credit_wait(p, false, base + t - 1u, lp);  // peers drained chunk t-2: its quarter is free
+    push(t, lp);
+    credit_signal(p, true, base + t + 1u, lp);
+  };
+  auto drain_step = [&](uint32_t t) {
+    credit_wait(p, true, base + t + 1u, ld);
+    drain(t, ld);
+    credit_signal(p, false, base + t + 1u, ld);
+  };
+  if (lanes_split(lp)) {
+    if (do_push) {
+      for (uint32_t t = 0; t < nch; ++t) push_step(t);
+      credit_wait(p, false, base + nch, lp);
+    } else {
+      for (uint32_t t = 0; t < nch; ++t) drain_step(t);
+    }
+  } else {  // one thread plays both groups (host executor)
+    for (uint32_t t = 0; t < nch; ++t) {
+      push_step(t);
+      drain_step(t);
+    }
+    credit_wait(p, false, base + nch, lp);
+  }
+  block_sync();
+  if (thread_index() == 0) p.me->cseq[p.block] = base + nch;
+}
+
 template <typename TI, typename TO, int OP>
 AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
@@ -31,11 +98,8 @@ AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
-  Lane lp, ld;
-  bool do_push, do_drain;
-  split_lanes(nch > 1, 8, &lp, &ld, &do_push, &do_drain);
-  for (uint32_t t = 0; t <= nch; ++t) {
-    if (do_push && t < nch) {
+  run_chunks(a, p, nch, 8,
+    [&](uint32_t t, Lane ln) {
       size_t off = (size_t)t * cb;
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
@@ -43,23 +107,21 @@ AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
       block_range(len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo, lp);
+        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo, ln);
       }
-      if (send != recv + (size_t)r * B) copy_span(recv + (size_t)r * B + off + lo, send + off + lo, hi - lo, lp);
-    }
-    if (do_drain && t >= 1) {
-      size_t off = (size_t)(t - 1) * cb;
+      if (send != recv + (size_t)r * B) copy_span(recv + (size_t)r * B + off + lo, send + off + lo, hi - lo, ln);
+    },
+    [&](uint32_t t, Lane ln) {
+      size_t off = (size_t)t * cb;
       size_t len = B - off < cb ? B - off : cb;
-      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t - 1);
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
       block_range(len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ld);
+        copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ln);
       }
-    }
-    if (t < nch) block_barrier(p);
-  }
+    });
 }
 
 template <typename TI, typename TO, int OP>
@@ -74,11 +136,8 @@ AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
-  Lane lp, ld;
-  bool do_push, do_drain;
-  split_lanes(nch > 1, 8, &lp, &ld, &do_push, &do_drain);
-  for (uint32_t t = 0; t <= nch; ++t) {
-    if (do_push && t < nch) {
+  run_chunks(a, p, nch, 8,
+    [&](uint32_t t, Lane ln) {
       size_t off = (size_t)t * cb;
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
@@ -86,23 +145,21 @@ AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
       block_range(len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + (size_t)q * B + off + lo, hi - lo, lp);
+        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + (size_t)q * B + off + lo, hi - lo, ln);
       }
-      if (send != recv) copy_span(recv + (size_t)r * B + off + lo, send + (size_t)r * B + off + lo, hi - lo, lp);
-    }
-    if (do_drain && t >= 1) {
-      size_t off = (size_t)(t - 1) * cb;
+      if (send != recv) copy_span(recv + (size_t)r * B + off + lo, send + (size_t)r * B + off + lo, hi - lo, ln);
+    },
+    [&](uint32_t t, Lane ln) {
+      size_t off = (size_t)t * cb;
       size_t len = B - off < cb ? B - off : cb;
-      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t - 1);
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
       block_range(len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ld);
+        copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ln);
       }
-    }
-    if (t < nch) block_barrier(p);
-  }
+    });
 }
 
 // Reduce-scatter with the optional fused scale and output-type cast (gradient averaging and
@@ -119,11 +176,9 @@ AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems)
   const char* send = (const char*)a.send;
   TO* recv = (TO*)a.recv;
   const uint32_t nch = (uint32_t)((R + ce - 1) / ce);
-  Lane lp, ld;
-  bool do_push, do_drain;
-  split_lanes(nch > 1, 6, &lp, &ld, &do_push, &do_drain);  // the reduce side reads n slots: it gets more warps
-  for (uint32_t t = 0; t <= nch; ++t) {
-    if (do_push && t < nch) {
+  // the reduce side reads n slots per output: it gets more warps than the push side
+  run_chunks(a, p, nch, 6,
+    [&](uint32_t t, Lane ln) {
       size_t off = (size_t)t * ce;
       size_t len = R - off < ce ? R - off : ce;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
@@ -131,23 +186,21 @@ AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems)
       block_range(len * es, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + ((size_t)q * R + off) * es + lo, hi - lo, lp);
+        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + ((size_t)q * R + off) * es + lo, hi - lo, ln);
       }
-    }
-    if (do_drain && t >= 1) {
-      size_t off = (size_t)(t - 1) * ce;
+    },
+    [&](uint32_t t, Lane ln) {
+      size_t off = (size_t)t * ce;
       size_t len = R - off < ce ? R - off : ce;
-      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t - 1);
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
       block_range(len * es, p.block, p.nblocks, &lo, &hi);
       const TI* slots[kMaxRanks];
       for (int s2 = 0; s2 < n; ++s2)
         slots[s2] = (s2 == r) ? (const TI*)(send + ((size_t)r * R + off) * es + lo)
                               : (const TI*)(a.stage[r] + qoff + (size_t)s2 * slot + lo);
-      reduce_span<TI, TO, OP>(recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, ld);
-    }
-    if (t < nch) block_barrier(p);
-  }
+      reduce_span<TI, TO, OP>(recv + off + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, ln);
+    });
 }
 
 template <typename TI, typename TO, int OP>

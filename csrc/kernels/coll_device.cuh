@@ -159,8 +159,15 @@ __device__ __forceinline__ void block_range(size_t total_bytes, int block, int n
 // "push" / "drain" group of warps when a collective overlaps its two phases.
 struct Lane {
   int tid, nt;
+  int bar;   // named barrier of the group (0 = the whole block)
 };
-__device__ __forceinline__ Lane full_lane() { return Lane{(int)threadIdx.x, (int)blockDim.x}; }
+__device__ __forceinline__ Lane full_lane() { return Lane{(int)threadIdx.x, (int)blockDim.x, 0}; }
+__device__ __forceinline__ bool lanes_split(Lane a) { return a.nt != (int)blockDim.x; }
+// Barrier among the threads of one lane only.
+__device__ __forceinline__ void lane_sync(Lane ln) {
+  if (ln.bar == 0) __syncthreads();
+  else asm volatile("bar.sync %0, %1;" ::"r"(ln.bar), "r"(ln.nt) : "memory");
+}
 
 // Splits the block's warps: the first `push_sixteenths`/16 of them push over NVLink, the rest
 // drain staging into the user's buffer.  Without overlap every thread does both in turn.
@@ -177,8 +184,8 @@ __device__ __forceinline__ void split_lanes(bool overlap, int push_sixteenths, L
   int t = threadIdx.x;
   *do_push = t < wp * 32;
   *do_drain = !*do_push;
-  *push = Lane{t, wp * 32};
-  *drain = Lane{t - wp * 32, (nwarps - wp) * 32};
+  *push = Lane{t, wp * 32, 1};
+  *drain = Lane{t - wp * 32, (nwarps - wp) * 32, 2};
 }
 
 __device__ __forceinline__ void copy_span(char* dst, const char* src, size_t bytes, Lane ln) {

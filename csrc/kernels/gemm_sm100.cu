@@ -29,8 +29,10 @@ namespace gemmk {
 
 using namespace sm100;
 
-constexpr int BM = kGemmBM, BN = kGemmBN, BK = kGemmBK, STAGES = kGemmStages;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = kGemmBM, BN_MAX = kGemmBN, BK = kGemmBK, STAGES = kGemmStages;
+// A stage always reserves room for the widest tile; the tile width itself (p.bn, a multiple of
+// 32 up to 256) is picked per problem so that the last wave of tiles is not nearly empty.
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_MAX * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int UMMA_K = 16;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy of the all-gather mover
@@ -193,6 +195,7 @@ __device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas,
   const FusedFlags* mine = p.fflags[r];
   const __nv_bfloat16* slots = (const __nv_bfloat16*)p.rs_buf[r];
   __nv_bfloat16* out = (__nv_bfloat16*)p.rs_out;
+  const int BN = p.bn;
   const size_t tile_elems = (size_t)BM * BN;
   const size_t slot_elems = (size_t)tiles_m * tiles_n * tile_elems;
   const uint32_t per_call = (uint32_t)tiles_n;  // one count per delivered tile
@@ -286,6 +289,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   if (fused && (is_mover || p.mode == kGemmReduceScatter)) dev::block_barrier(proto);
 
   const int tiles_m = (p.rows_per_rank + BM - 1) / BM;
+  const int BN = p.bn;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int shards = (p.mode == kGemmPlain || n == 1) ? 1 : n;
   const int total_tiles = tiles_m * tiles_n * shards;
@@ -322,7 +326,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         for (int kb = 0; kb < num_kb && ok; ++kb) {
           ok = mbar_wait(&ctl->empty[stage], phase ^ 1u, p.coll.timeout_ns, abort);
           if (!ok) break;
-          mbar_expect_tx(&ctl->full[stage], STAGE_BYTES);
+          mbar_expect_tx(&ctl->full[stage], (uint32_t)(A_BYTES + BN * BK * 2));
           tma_load_2d(ring + (size_t)stage * STAGE_BYTES, ma, &ctl->full[stage], kb * BK, row0);
           tma_load_2d(ring + (size_t)stage * STAGE_BYTES + A_BYTES, map_b, &ctl->full[stage], kb * BK, tl.n_blk * BN);
           issued |= 1u << stage;
@@ -356,7 +360,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         ok = mbar_wait(&ctl->tempty[buf], acc_phase ^ 1u, p.coll.timeout_ns, abort);
         if (!ok) break;
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN_MAX);
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = mbar_wait(&ctl->full[stage], phase, p.coll.timeout_ns, abort);
           if (!ok) break;
@@ -390,7 +394,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + (uint32_t)(buf * BN) + ((uint32_t)(lane_grp * 32) << 16);
+      const uint32_t t_row = tmem_base + (uint32_t)(buf * BN_MAX) + ((uint32_t)(lane_grp * 32) << 16);
       if (p.mode == kGemmReduceScatter && fused) {
         // Partial tile -> the owner's slot number r.  Each 32-column chunk (128 rows x 64 bytes
         // = 8 KB, contiguous at the destination) is staged in shared memory and shipped with
@@ -541,6 +545,21 @@ Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, u
 }
 
 size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + 2 * gemmk::EPI_CHUNK_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
+
+int gemm_pick_bn(int row_tiles, int N, int ctas) {
+  int best = kGemmBN;
+  long best_cost = -1;
+  for (int bn = kGemmBN; bn >= 128; bn -= 32) {
+    long tiles = (long)row_tiles * ((N + bn - 1) / bn);
+    long waves = (tiles + ctas - 1) / ctas;
+    long cost = waves * (bn + 16);  // + a per-tile overhead so that equal costs prefer wide tiles
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
 
 int gemm_default_grid(int device) {
   int sms = 0;

@@ -28,6 +28,7 @@ struct FusedFlags {
 
 struct GemmParams {
   int M, N, K;              // problem of this rank (M = all rows, gathered or to be scattered)
+  int bn;                   // tile width in columns: multiple of 32, <= kGemmBN (see gemm_pick_bn)
   int mode;
   void* C;                  // plain / all-gather: bf16 [M, N] row-major, leading dimension ldc
   int ldc;
@@ -58,5 +59,7 @@ Status launch_gemm(const GemmLaunch& g, cudaStream_t stream);
 // All ranks of an emulated communicator in one cooperative grid (blockIdx.y = rank).
 Status launch_gemm_emu(const GemmLaunch* ranks, int nranks, cudaStream_t stream);
 int gemm_default_grid(int device);
+// Tile width that minimises (waves of tiles) x (tile width) for `ctas` compute CTAs.
+int gemm_pick_bn(int row_tiles, int N, int ctas);
 
 }  // namespace amem

@@ -99,8 +99,11 @@ inline void block_range(size_t total_bytes, int block, int nblocks, size_t* lo, 
 
 struct Lane {
   int tid, nt;
+  int bar;
 };
-inline Lane full_lane() { return Lane{0, 1}; }
+inline Lane full_lane() { return Lane{0, 1, 0}; }
+inline bool lanes_split(Lane) { return false; }
+inline void lane_sync(Lane) {}
 inline void split_lanes(bool, int, Lane* push, Lane* drain, bool* do_push, bool* do_drain) {
   *push = *drain = full_lane();  // one thread plays both groups, one after the other
   *do_push = *do_drain = true;

@@ -9,7 +9,7 @@
 //   * code that runs where an allocation would stall or break what surrounds it.
 // It runs the same count / plan / scatter kernels as amemMoeDispatch on a one-rank
 // "communicator", but the scratch they need (per-segment expert histograms and their scans,
-// per-expert row offsets, one protocol control block and status words: about 300 KB) sits in a
+// per-expert row offsets, one protocol control block and status words: about 330 KB) sits in a
 // file-scope device array inside the library instead of in allocated memory.
 //
 // Limits and rules:

@@ -92,3 +92,35 @@ def _sendrecv_ring(rank, world, uid):
 
 def test_sendrecv_ring():
     assert all(run_ranks(_sendrecv_ring, 3))
+
+
+def _multi_chunk(rank, world, uid):
+    """Messages several times larger than a staging slot: the chunked credit protocol."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator
+    comm = Communicator(world, rank, uid)
+    n = 700_001                      # ~2.7 MiB of fp32 per rank, slots are 256 KiB here
+    mine = (np.arange(n, dtype=np.float32) % 1013) + 7 * rank
+    out = {}
+    g = np.empty(world * n, dtype=np.float32)
+    comm.all_gather(mine, g)
+    out["ag"] = bool(np.array_equal(g, np.concatenate([(np.arange(n, dtype=np.float32) % 1013) + 7 * r for r in range(world)])))
+    send = np.concatenate([mine + j for j in range(world)])
+    recv = np.empty(n, dtype=np.float32)
+    comm.reduce_scatter(send, recv)
+    exp = sum(((np.arange(n, dtype=np.float32) % 1013) + 7 * r + rank) for r in range(world))
+    out["rs"] = bool(np.array_equal(recv, exp))
+    t = np.empty(world * n, dtype=np.float32)
+    comm.all_to_all(send, t)
+    out["a2a"] = bool(np.array_equal(t, np.concatenate([(np.arange(n, dtype=np.float32) % 1013) + 7 * j + rank for j in range(world)])))
+    # and a small operation right after, on the barrier protocol
+    x = np.ones(100, dtype=np.float32)
+    comm.all_reduce(x)
+    out["ar_after"] = bool(np.all(x == world))
+    comm.destroy()
+    return out
+
+
+def test_multi_chunk_collectives():
+    for d in run_ranks(_multi_chunk, 3, env={"AMEM_STAGE_MB": "7", "AMEM_P2P_SLOT_KB": "4"}):
+        assert all(d.values()), d
