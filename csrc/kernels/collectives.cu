@@ -78,12 +78,50 @@ __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// NVLS all-reduce as a three-stage software pipeline over chunks: while one group of warps lets
-// the switch add and re-broadcast my slice of chunk t-1 (multimem.ld_reduce + multimem.st on
-// the multicast mapping, NVLink-bound), the other group copies chunk t from the user's buffer
-// into staging and chunk t-2 from staging to the user's output (HBM-bound).  One barrier per
-// stage; three staging regions rotate.  A message of one chunk degenerates to copy-in,
-// barrier, reduce, barrier, copy-out.
+// NVLS all-reduce.  Three jobs per chunk: stage the chunk into my staging (HBM), let the switch
+// add everybody's copy of my slice and broadcast the sum back into every rank's staging
+// (multimem.ld_reduce + multimem.st on the multicast mapping: NVLink), copy the reduced chunk
+// out (HBM).  A message of one chunk does them in turn with two barriers.  Longer messages
+// run the two HBM jobs on one group of warps and the switch job on another; the groups never
+// meet, they are coupled by per-block credits: "staged N" (CtrlBlock::ready) lets every rank's
+// reducer start on chunk N, "reduced N" (CtrlBlock::freed) lets every rank copy chunk N out.
+// Three staging regions rotate; region N % 3 is restaged only after chunk N-3 was copied out,
+// which (program order of the copy group) is also after everybody's reduce of it.
+template <typename T>
+__device__ __forceinline__ void nvls_reduce_slice(const CollArgs& a, Proto& p, char* region_mc, size_t len, Lane lr) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(T), vi = 16 / es;
+  size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+  size_t b0 = (size_t)r * sl, b1 = b0 + sl;
+  if (b0 > len) b0 = len;
+  if (b1 > len) b1 = len;
+  size_t slo, shi;
+  block_range((b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
+  // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
+  size_t nvec = (shi - slo + 15) / 16;
+  char* base = region_mc + b0 * es + slo;
+  const size_t nt = lr.nt;
+  size_t i = lr.tid;
+  // eight switch reductions in flight per thread: a round trip through the NVSwitch takes
+  // microseconds, the link only fills with a lot of data outstanding
+  for (; i + 7 * nt < nvec; i += 8 * nt) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::ld_reduce(base + (i + j * nt) * 16);
+    if (a.has_scale) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) multimem_st(base + (i + j * nt) * 16, v[j]);
+  }
+  for (; i < nvec; i += nt) {
+    uint4 v = Multimem<T>::ld_reduce(base + i * 16);
+    if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
+    multimem_st(base + i * 16, v);
+  }
+}
+
 template <typename T>
 __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
@@ -99,56 +137,52 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   const uint32_t nch = (uint32_t)((N + ce - 1) / ce);
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
+  auto stage_in = [&](uint32_t t, Lane ln) {
+    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce, lo, hi;
+    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    copy_span(a.stage[r] + hoff + (t % 3) * region + lo, send + off * es + lo, hi - lo, ln);
+  };
+  auto stage_out = [&](uint32_t t, Lane ln) {
+    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce, lo, hi;
+    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    copy_span(recv + off * es + lo, a.stage[r] + hoff + (t % 3) * region + lo, hi - lo, ln);
+  };
+  auto reduce = [&](uint32_t t, Lane ln) {
+    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
+    nvls_reduce_slice<T>(a, p, a.mc_stage + hoff + (t % 3) * region, len, ln);
+  };
+  if (nch == 1) {
+    stage_in(0, full_lane());
+    block_barrier(p);
+    reduce(0, full_lane());
+    block_barrier(p);
+    stage_out(0, full_lane());
+    return;
+  }
   Lane lr, lc;
   bool do_red, do_copy;
-  split_lanes(nch > 1, 8, &lr, &lc, &do_red, &do_copy);
-  for (uint32_t t = 0; t <= nch + 1; ++t) {
-    if (do_copy && t < nch) {  // stage in chunk t
-      size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce, lo, hi;
-      block_range(len * es, p.block, p.nblocks, &lo, &hi);
-      copy_span(a.stage[r] + hoff + (t % 3) * region + lo, send + off * es + lo, hi - lo, lc);
-    }
-    if (do_red && t >= 1 && t - 1 < nch) {  // switch-reduce my slice of chunk t-1, broadcast it
-      uint32_t c = t - 1;
-      size_t off = (size_t)c * ce, len = N - off < ce ? N - off : ce;
-      size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
-      size_t b0 = (size_t)r * sl, b1 = b0 + sl;
-      if (b0 > len) b0 = len;
-      if (b1 > len) b1 = len;
-      size_t slo, shi;
-      block_range((b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
-      // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
-      size_t nvec = (shi - slo + 15) / 16;
-      char* base = a.mc_stage + hoff + (c % 3) * region + b0 * es + slo;
-      const size_t nt = lr.nt;
-      size_t i = lr.tid;
-      // eight switch reductions in flight per thread: a round trip through the NVSwitch takes
-      // microseconds, the link only fills with a lot of data outstanding
-      for (; i + 7 * nt < nvec; i += 8 * nt) {
-        uint4 v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::ld_reduce(base + (i + j * nt) * 16);
-        if (a.has_scale) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) multimem_st(base + (i + j * nt) * 16, v[j]);
+  split_lanes(true, 8, &lr, &lc, &do_red, &do_copy);
+  const uint32_t base = ld_volatile(&p.me->cseq[p.block]);
+  if (do_copy) {
+    for (uint32_t t = 0; t < nch + 2; ++t) {
+      if (t >= 2) {
+        credit_wait(p, false, base + (t - 2) + 1u, lc);  // every rank has reduced chunk t-2
+        stage_out(t - 2, lc);
       }
-      for (; i < nvec; i += nt) {
-        uint4 v = Multimem<T>::ld_reduce(base + i * 16);
-        if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
-        multimem_st(base + i * 16, v);
+      if (t < nch) {
+        stage_in(t, lc);
+        credit_signal(p, true, base + t + 1u, lc);       // "staged t"
       }
     }
-    if (do_copy && t >= 2) {  // stage out chunk t-2
-      uint32_t c = t - 2;
-      size_t off = (size_t)c * ce, len = N - off < ce ? N - off : ce, lo, hi;
-      block_range(len * es, p.block, p.nblocks, &lo, &hi);
-      copy_span(recv + off * es + lo, a.stage[r] + hoff + (c % 3) * region + lo, hi - lo, lc);
+  } else {
+    for (uint32_t t = 0; t < nch; ++t) {
+      credit_wait(p, true, base + t + 1u, lr);           // every rank has staged chunk t
+      reduce(t, lr);
+      credit_signal(p, false, base + t + 1u, lr);        // "reduced t"
     }
-    if (t <= nch) block_barrier(p);
   }
+  block_sync();
+  if (thread_index() == 0) p.me->cseq[p.block] = base + nch;
 }
 
 // ------------------------------------------------------------------ kernels

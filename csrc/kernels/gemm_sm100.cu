@@ -552,7 +552,9 @@ int gemm_pick_bn(int row_tiles, int N, int ctas) {
   for (int bn = kGemmBN; bn >= 128; bn -= 32) {
     long tiles = (long)row_tiles * ((N + bn - 1) / bn);
     long waves = (tiles + ctas - 1) / ctas;
-    long cost = waves * (bn + 16);  // + a per-tile overhead so that equal costs prefer wide tiles
+    // measured: a tile's time depends only weakly on its width (the main loop is bound by
+    // filling shared memory, not by the tensor pipe), so count waves first, width second
+    long cost = waves * (bn + 600);
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best = bn;
