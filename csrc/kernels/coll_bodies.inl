@@ -23,10 +23,12 @@ AMEM_FN int peer_at(int rank, int n, int k, int block) { return (rank + 1 + (k -
 // back.  So the link never idles on a barrier, and the drain hides behind the next push.  The
 // operation ends when all peers have drained all of my chunks: staging is then free everywhere,
 // whatever protocol the next operation uses.
-AMEM_FN void credit_wait(Proto& p, bool want_ready, uint32_t want, Lane ln) {
+// `with_self`: the two groups of THIS rank also depend on each other (NVLS all-reduce), so the
+// credit is sent to, and awaited from, my own control block as well.
+AMEM_FN void credit_wait(Proto& p, bool want_ready, uint32_t want, Lane ln, bool with_self = false) {
   const CollArgs& a = *p.a;
   for (int q = ln.tid; q < a.nranks; q += ln.nt) {
-    if (q == a.rank) continue;
+    if (q == a.rank && !with_self) continue;
     const uint32_t* f = want_ready ? &p.me->ready[p.block][q] : &p.me->freed[p.block][q];
     if (*(volatile int*)p.abort_flag == 0 && !wait_flag_ge(f, want, a.timeout_ns)) {
       report_error(a.status, kDevBarrierTimeout, a.rank, q, p.block, want);
@@ -35,11 +37,11 @@ AMEM_FN void credit_wait(Proto& p, bool want_ready, uint32_t want, Lane ln) {
   }
   lane_sync(ln);
 }
-AMEM_FN void credit_signal(Proto& p, bool is_ready, uint32_t value, Lane ln) {
+AMEM_FN void credit_signal(Proto& p, bool is_ready, uint32_t value, Lane ln, bool with_self = false) {
   const CollArgs& a = *p.a;
   lane_sync(ln);  // everything the group stored (or finished reading) comes before the signal
   for (int q = ln.tid; q < a.nranks; q += ln.nt) {
-    if (q == a.rank) continue;
+    if (q == a.rank && !with_self) continue;
     fence_system();
     st_release_sys(is_ready ? &a.ctrl[q]->ready[p.block][a.rank] : &a.ctrl[q]->freed[p.block][a.rank], value);
   }

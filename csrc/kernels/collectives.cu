@@ -166,19 +166,19 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   if (do_copy) {
     for (uint32_t t = 0; t < nch + 2; ++t) {
       if (t >= 2) {
-        credit_wait(p, false, base + (t - 2) + 1u, lc);  // every rank has reduced chunk t-2
+        credit_wait(p, false, base + (t - 2) + 1u, lc, true);  // every rank (mine too) has reduced chunk t-2
         stage_out(t - 2, lc);
       }
       if (t < nch) {
         stage_in(t, lc);
-        credit_signal(p, true, base + t + 1u, lc);       // "staged t"
+        credit_signal(p, true, base + t + 1u, lc, true);  // "staged t"
       }
     }
   } else {
     for (uint32_t t = 0; t < nch; ++t) {
-      credit_wait(p, true, base + t + 1u, lr);           // every rank has staged chunk t
+      credit_wait(p, true, base + t + 1u, lr, true);     // every rank (mine too) has staged chunk t
       reduce(t, lr);
-      credit_signal(p, false, base + t + 1u, lr);        // "reduced t"
+      credit_signal(p, false, base + t + 1u, lr, true);  // "reduced t"
     }
   }
   block_sync();
