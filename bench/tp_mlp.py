@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--dim", type=int, default=8192)
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--no-pause", action="store_true", help="do not pause/resume between iterations")
     ap.add_argument("--out", default="gpurun_out/tp_mlp.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -49,6 +50,7 @@ def main():
     x_full = torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
     y_full = torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
     flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+    align = torch.zeros(8, device="cuda")
 
     def fused_ag():
         all_gather_gemm(comm, x_shard, w1, out=h)
@@ -72,6 +74,7 @@ def main():
         tot = 0.0
         for _ in range(args.iters):
             flush.zero_()
+            comm.all_reduce(align)   # ranks leave resume at different moments: line the streams up on the device
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
             fn()
@@ -86,9 +89,10 @@ def main():
         return float(t.item())
 
     res = {"n_gpus": world, "tokens": M, "dim": D, "ffn_local": Fl}
-    res["ag_gemm_fused_ms"] = timed(fused_ag, True)
+    res["paused_between_iterations"] = not args.no_pause
+    res["ag_gemm_fused_ms"] = timed(fused_ag, not args.no_pause)
     res["ag_gemm_cublas_nccl_ms"] = timed(base_ag, False)
-    res["gemm_rs_fused_ms"] = timed(fused_rs, True)
+    res["gemm_rs_fused_ms"] = timed(fused_rs, not args.no_pause)
     res["gemm_rs_cublas_nccl_ms"] = timed(base_rs, False)
     flops = 2.0 * M * Fl * D
     t_compute = flops / (peaks["bf16_tflops"] * 1e12) * 1e3

@@ -227,6 +227,9 @@ AMEM_FN void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
   reduce_span<TI, TO, OP>((TO*)a.recv + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, full_lane());
 }
 
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch);
+
 // Two-shot: reduce-scatter of the chunk into region X, then all-gather of the reduced slices
 // through region Y; both regions live in the half selected by opseq, no quarter alternation
 // is needed because each chunk ends with a barrier of its own before Y is read.
@@ -246,6 +249,19 @@ AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_el
   if (ce == 0) ce = vi * n;
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
+  {
+    // several chunks: the credit pipeline (its buffers are half as large, so re-chunk for it)
+    const size_t slot2 = slot_bytes_of(quarter_bytes(a.stage_bytes, a.p2p_slot_bytes) / 2, n);
+    size_t ce2 = chunk_elems;
+    if (ce2 > (slot2 / es) * n) ce2 = (slot2 / es) * n;
+    ce2 = ce2 / (vi * n) * (vi * n);
+    if (ce2 == 0) ce2 = vi * n;
+    const uint32_t nch2 = (uint32_t)((N + ce2 - 1) / ce2);
+    if (nch2 > 1) {
+      body_allreduce_twoshot_pipelined<TI, TO, OP>(a, p, ce2, nch2);
+      return;
+    }
+  }
   for (size_t off = 0; off < N; off += ce) {
     size_t len = N - off < ce ? N - off : ce;
     // slice length: equal parts rounded up to a whole 16-byte vector
@@ -290,6 +306,105 @@ AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_el
       copy_span(recv + (off + b0) * es + lo, a.stage[r] + yoff + (size_t)q * slot + lo, hi - lo, full_lane());
     }
   }
+}
+
+// Two-shot all-reduce for messages of several chunks, on credits.  Per chunk: (1) SCATTER my
+// copy of every slice to its owner's X region, (2) the owner REDUCEs its slice (its own
+// copy straight from the user's buffer, the others from X) and stores the result into every
+// rank's Y region and its own output, (3) every rank GATHERs the other slices from Y into its
+// output.  One group of warps does (1) and (3), the other does (2); "scattered N" (ready) and
+// "reduced N" (freed) credits, also between the two groups of one rank, couple them.  X and Y
+// are double buffered: a buffer is rewritten two chunks later, which the credit order makes
+// safe (scatter of N waits for everybody's reduce of N-2; the reduce of N waits for everybody's
+// scatter of N, which each rank issues after its gather of N-2).
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI), vi = 16 / es;
+  const size_t N = a.count;
+  const size_t Q = quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t hoff = half_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq);
+  const size_t slot = slot_bytes_of(Q / 2, n);  // X and Y each hold two buffers of n slots
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  auto xbase = [&](uint32_t t) { return hoff + (size_t)(t & 1u) * (Q / 2); };
+  auto ybase = [&](uint32_t t) { return hoff + Q + (size_t)(t & 1u) * (Q / 2); };
+  auto slice = [&](uint32_t t, int owner, size_t* off, size_t* b0, size_t* b1) {
+    *off = (size_t)t * ce;
+    size_t len = N - *off < ce ? N - *off : ce;
+    size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+    *b0 = (size_t)owner * sl;
+    *b1 = *b0 + sl;
+    if (*b0 > len) *b0 = len;
+    if (*b1 > len) *b1 = len;
+  };
+  auto scatter = [&](uint32_t t, Lane ln) {
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      size_t off, b0, b1, lo, hi;
+      slice(t, q, &off, &b0, &b1);
+      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      copy_span(a.stage[q] + xbase(t) + (size_t)r * slot + lo, send + (off + b0) * es + lo, hi - lo, ln);
+    }
+  };
+  auto reduce = [&](uint32_t t, Lane ln) {
+    size_t off, b0, b1, lo, hi;
+    slice(t, r, &off, &b0, &b1);
+    block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+    const TI* slots[kMaxRanks];
+    for (int s2 = 0; s2 < n; ++s2)
+      slots[s2] = (s2 == r) ? (const TI*)(send + (off + b0) * es + lo) : (const TI*)(a.stage[r] + xbase(t) + (size_t)s2 * slot + lo);
+    char* mine = a.stage[r] + ybase(t) + (size_t)r * slot + lo;
+    reduce_span<TI, TO, OP>((TO*)mine, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, ln);
+    lane_sync(ln);
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      copy_span(a.stage[q] + ybase(t) + (size_t)r * slot + lo, mine, hi - lo, ln);
+    }
+    copy_span(recv + (off + b0) * es + lo, mine, hi - lo, ln);
+  };
+  auto gather = [&](uint32_t t, Lane ln) {
+    for (int k = 1; k < n; ++k) {
+      int q = peer_at(r, n, k, p.block);
+      size_t off, b0, b1, lo, hi;
+      slice(t, q, &off, &b0, &b1);
+      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      copy_span(recv + (off + b0) * es + lo, a.stage[r] + ybase(t) + (size_t)q * slot + lo, hi - lo, ln);
+    }
+  };
+  Lane lr, lc;
+  bool do_red, do_copy;
+  split_lanes(true, 8, &lr, &lc, &do_red, &do_copy);
+  const uint32_t base = ld_volatile(&p.me->cseq[p.block]);
+  auto copy_step = [&](uint32_t t) {   // t runs to nch + 1
+    if (t >= 2) {
+      credit_wait(p, false, base + (t - 2) + 1u, lc, true);   // every rank reduced chunk t-2
+      gather(t - 2, lc);
+    }
+    if (t < nch) {
+      scatter(t, lc);
+      credit_signal(p, true, base + t + 1u, lc, true);        // "scattered t"
+    }
+  };
+  auto reduce_step = [&](uint32_t t) {
+    credit_wait(p, true, base + t + 1u, lr, true);
+    reduce(t, lr);
+    credit_signal(p, false, base + t + 1u, lr, true);          // "reduced t"
+  };
+  if (lanes_split(lr)) {
+    if (do_copy) {
+      for (uint32_t t = 0; t < nch + 2; ++t) copy_step(t);
+    } else {
+      for (uint32_t t = 0; t < nch; ++t) reduce_step(t);
+    }
+  } else {  // one thread plays both groups (host executor)
+    for (uint32_t t = 0; t < nch + 2; ++t) {
+      copy_step(t);
+      if (t < nch) reduce_step(t);
+    }
+  }
+  block_sync();
+  if (thread_index() == 0) p.me->cseq[p.block] = base + nch;
 }
 
 template <typename TI, typename TO, int OP>

@@ -196,13 +196,14 @@ __device__ __forceinline__ void copy_span(char* dst, const char* src, size_t byt
     const uint4* s = (const uint4*)src;
     uint4* d = (uint4*)dst;
     size_t i = t;
-    // four independent 16-byte loads in flight per thread
-    for (; i + 3 * (size_t)nt < nvec; i += 4 * (size_t)nt) {
-      uint4 v0 = s[i], v1 = s[i + nt], v2 = s[i + 2 * (size_t)nt], v3 = s[i + 3 * (size_t)nt];
-      d[i] = v0;
-      d[i + nt] = v1;
-      d[i + 2 * (size_t)nt] = v2;
-      d[i + 3 * (size_t)nt] = v3;
+    // eight independent 16-byte loads in flight per thread: with only part of the block's warps
+    // on a copy (the collectives split their warps), HBM latency needs that much to be covered
+    for (; i + 7 * (size_t)nt < nvec; i += 8 * (size_t)nt) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = s[i + (size_t)j * nt];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d[i + (size_t)j * nt] = v[j];
     }
     for (; i < nvec; i += nt) d[i] = s[i];
     for (size_t b = nvec * 16 + t; b < bytes; b += nt) dst[b] = src[b];

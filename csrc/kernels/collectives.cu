@@ -161,7 +161,8 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   }
   Lane lr, lc;
   bool do_red, do_copy;
-  split_lanes(true, 8, &lr, &lc, &do_red, &do_copy);
+  // the switch job needs few instructions, the two HBM copies need many loads in flight
+  split_lanes(true, 4, &lr, &lc, &do_red, &do_copy);
   const uint32_t base = ld_volatile(&p.me->cseq[p.block]);
   if (do_copy) {
     for (uint32_t t = 0; t < nch + 2; ++t) {

@@ -79,7 +79,7 @@ LaunchPlan plan_collective(const TunerInput& in) {
   switch (in.kind) {
     case kCollAllReduce:
       if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, (H / 3) & ~(size_t)4095) / es;
-      else p.chunk_elems = (slot_bytes_of(H / 2, n) / es) * (size_t)n;
+      else p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, (slot_bytes_of(H / 2, n)) * (size_t)n) / es;
       break;
     case kCollBroadcast: p.chunk_elems = Q / es; break;
     case kCollReduce: p.chunk_elems = slot / es; break;
