@@ -31,6 +31,8 @@ void Comm::fill_args(CollArgs* a) const {
   a->status = status_;
   a->timeout_ns = timeout_ns_;
   a->p2p_max_lanes = emu_ ? 2 : kP2PBlocks;
+  static const long nvls_split = env_long("AMEM_NVLS_SPLIT", 4);
+  a->nvls_split = (int)nvls_split;
   a->scale = 1.0f;
 }
 

@@ -95,6 +95,7 @@ struct CollArgs {
   // send/recv lists for grouped point-to-point (kind == kCollSendRecv)
   int n_p2p;
   int p2p_max_lanes;       // blocks one transfer may use (<= kP2PBlocks; small on emulated comms)
+  int nvls_split;          // sixteenths of a block's warps on the switch job of the pipelined NVLS all-reduce (0 = 4)
   struct P2P {
     int peer;
     int is_send;

@@ -107,9 +107,15 @@ AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
       block_range(len, p.block, p.nblocks, &lo, &hi);
-      for (int k = 1; k < n; ++k) {
-        int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo, ln);
+      char* mc = (a.algo == kAlgoNvls && a.mc_stage) ? a.mc_stage + qoff + (size_t)r * slot + lo : nullptr;
+      if (mc_copy_ok(mc, send + off + lo, hi - lo)) {
+        // NVLS all-gather: one multicast store lands my piece in every rank's staging slot
+        copy_span_mc(mc, send + off + lo, hi - lo, ln);
+      } else {
+        for (int k = 1; k < n; ++k) {
+          int q = peer_at(r, n, k, p.block);
+          copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + off + lo, hi - lo, ln);
+        }
       }
       if (send != recv + (size_t)r * B) copy_span(recv + (size_t)r * B + off + lo, send + off + lo, hi - lo, ln);
     },

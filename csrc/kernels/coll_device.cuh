@@ -212,6 +212,28 @@ __device__ __forceinline__ void copy_span(char* dst, const char* src, size_t byt
   }
 }
 
+// Copy into the multicast mapping: ONE store per 16 bytes that the NVSwitch replicates into
+// every rank's memory (multimem.st), instead of one store per peer.  16-byte aligned spans only.
+__device__ __forceinline__ bool mc_copy_ok(const char* dst_mc, const char* src, size_t bytes) {
+  return dst_mc != nullptr && ((((uintptr_t)dst_mc | (uintptr_t)src) & 15) == 0) && (bytes % 16 == 0);
+}
+__device__ __forceinline__ void copy_span_mc(char* dst_mc, const char* src, size_t bytes, Lane ln) {
+  const uint4* s = (const uint4*)src;
+  size_t nvec = bytes / 16, nt = ln.nt, i = ln.tid;
+  for (; i + 7 * nt < nvec; i += 8 * nt) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = s[i + j * nt];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst_mc + (i + j * nt) * 16), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
+  }
+  for (; i < nvec; i += nt) {
+    uint4 v = s[i];
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst_mc + i * 16), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+  }
+}
+
 // out[i] = cast(scale * OP_r(slot_r[i]))  for i in [0, n); reduction order is rank 0..nslots-1,
 // accumulated in Acc<TI> (fp32 for 16-bit floats) and rounded once.
 template <typename TI, typename TO, int OP>

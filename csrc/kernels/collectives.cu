@@ -87,7 +87,7 @@ __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
 // reducer start on chunk N, "reduced N" (CtrlBlock::freed) lets every rank copy chunk N out.
 // Three staging regions rotate; region N % 3 is restaged only after chunk N-3 was copied out,
 // which (program order of the copy group) is also after everybody's reduce of it.
-template <typename T>
+template <typename T, int U>
 __device__ __forceinline__ void nvls_reduce_slice(const CollArgs& a, Proto& p, char* region_mc, size_t len, Lane lr) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(T), vi = 16 / es;
@@ -102,23 +102,62 @@ __device__ __forceinline__ void nvls_reduce_slice(const CollArgs& a, Proto& p, c
   char* base = region_mc + b0 * es + slo;
   const size_t nt = lr.nt;
   size_t i = lr.tid;
-  // eight switch reductions in flight per thread: a round trip through the NVSwitch takes
-  // microseconds, the link only fills with a lot of data outstanding
-  for (; i + 7 * nt < nvec; i += 8 * nt) {
-    uint4 v[8];
+  // U switch reductions in flight per thread: a round trip through the NVSwitch takes
+  // microseconds, the link only fills with megabytes outstanding per GPU
+  for (; i + (U - 1) * nt < nvec; i += U * nt) {
+    uint4 v[U];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::ld_reduce(base + (i + j * nt) * 16);
+    for (int j = 0; j < U; ++j) v[j] = Multimem<T>::ld_reduce(base + (i + j * nt) * 16);
     if (a.has_scale) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
+      for (int j = 0; j < U; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) multimem_st(base + (i + j * nt) * 16, v[j]);
+    for (int j = 0; j < U; ++j) multimem_st(base + (i + j * nt) * 16, v[j]);
   }
   for (; i < nvec; i += nt) {
     uint4 v = Multimem<T>::ld_reduce(base + i * 16);
     if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
     multimem_st(base + i * 16, v);
+  }
+}
+
+// Copy of one chunk (`len` elements) between the user's buffer and my staging, split over the
+// blocks the same way nvls_reduce_slice splits the switch job: block b moves its share of EVERY
+// rank's slice.  Then block b of a reducer depends on block b of every rank and on nothing else,
+// which is what the per-block barriers and credits promise.
+template <typename T>
+__device__ __forceinline__ void nvls_copy_sliced(char* dst, const char* src, size_t len, const CollArgs& a, const Proto& p, Lane ln) {
+  const int n = a.nranks;
+  const size_t es = sizeof(T), vi = 16 / es;
+  const size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+  int nfull = sl ? (int)(len / sl) : 0;
+  if (nfull > n) nfull = n;
+  size_t lo, hi;
+  block_range(sl * es, p.block, p.nblocks, &lo, &hi);
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    // the full slices together: one 16-byte load per slice in flight per thread
+    const size_t nvec = (hi - lo) / 16, stride = sl * es / 16, nt = ln.nt;
+    const uint4* s4 = (const uint4*)(src + lo);
+    uint4* d4 = (uint4*)(dst + lo);
+    for (size_t i = ln.tid; i < nvec; i += nt) {
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < nfull) v[q] = s4[(size_t)q * stride + i];
+#pragma unroll
+      for (int q = 0; q < kMaxRanks; ++q)
+        if (q < nfull) d4[(size_t)q * stride + i] = v[q];
+    }
+  } else {
+    for (int q = 0; q < nfull; ++q) copy_span(dst + (size_t)q * sl * es + lo, src + (size_t)q * sl * es + lo, hi - lo, ln);
+  }
+  for (int q = nfull; q < n; ++q) {  // the ragged end: at most one short slice, the rest empty
+    size_t b0 = (size_t)q * sl, b1 = b0 + sl;
+    if (b0 > len) b0 = len;
+    if (b1 > len) b1 = len;
+    block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+    copy_span(dst + b0 * es + lo, src + b0 * es + lo, hi - lo, ln);
   }
 }
 
@@ -138,18 +177,20 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   auto stage_in = [&](uint32_t t, Lane ln) {
-    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce, lo, hi;
-    block_range(len * es, p.block, p.nblocks, &lo, &hi);
-    copy_span(a.stage[r] + hoff + (t % 3) * region + lo, send + off * es + lo, hi - lo, ln);
+    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
+    nvls_copy_sliced<T>(a.stage[r] + hoff + (t % 3) * region, send + off * es, len, a, p, ln);
   };
   auto stage_out = [&](uint32_t t, Lane ln) {
-    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce, lo, hi;
-    block_range(len * es, p.block, p.nblocks, &lo, &hi);
-    copy_span(recv + off * es + lo, a.stage[r] + hoff + (t % 3) * region + lo, hi - lo, ln);
+    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
+    nvls_copy_sliced<T>(recv + off * es, a.stage[r] + hoff + (t % 3) * region, len, a, p, ln);
   };
   auto reduce = [&](uint32_t t, Lane ln) {
     size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
-    nvls_reduce_slice<T>(a, p, a.mc_stage + hoff + (t % 3) * region, len, ln);
+    nvls_reduce_slice<T, 8>(a, p, a.mc_stage + hoff + (t % 3) * region, len, ln);
+  };
+  auto reduce_deep = [&](uint32_t t, Lane ln) {  // few warps: twice the loads in flight each
+    size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
+    nvls_reduce_slice<T, 16>(a, p, a.mc_stage + hoff + (t % 3) * region, len, ln);
   };
   if (nch == 1) {
     stage_in(0, full_lane());
@@ -162,7 +203,7 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   Lane lr, lc;
   bool do_red, do_copy;
   // the switch job needs few instructions, the two HBM copies need many loads in flight
-  split_lanes(true, 4, &lr, &lc, &do_red, &do_copy);
+  split_lanes(true, a.nvls_split > 0 ? a.nvls_split : 4, &lr, &lc, &do_red, &do_copy);
   const uint32_t base = ld_volatile(&p.me->cseq[p.block]);
   if (do_copy) {
     for (uint32_t t = 0; t < nch + 2; ++t) {
@@ -178,7 +219,7 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   } else {
     for (uint32_t t = 0; t < nch; ++t) {
       credit_wait(p, true, base + t + 1u, lr, true);     // every rank (mine too) has staged chunk t
-      reduce(t, lr);
+      reduce_deep(t, lr);
       credit_signal(p, false, base + t + 1u, lr, true);  // "reduced t"
     }
   }

@@ -108,6 +108,8 @@ inline void split_lanes(bool, int, Lane* push, Lane* drain, bool* do_push, bool*
   *push = *drain = full_lane();  // one thread plays both groups, one after the other
   *do_push = *do_drain = true;
 }
+inline bool mc_copy_ok(const char*, const char*, size_t) { return false; }  // no multicast on the host
+inline void copy_span_mc(char*, const char*, size_t, Lane) {}
 inline void copy_span(char* dst, const char* src, size_t bytes, Lane) {
   if (bytes) memmove(dst, src, bytes);
 }

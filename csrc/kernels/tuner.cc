@@ -52,6 +52,12 @@ LaunchPlan plan_collective(const TunerInput& in) {
     }
     p.algo = want;
   }
+  // All-gather may push through the multicast mapping (multimem.st: one store instead of n-1);
+  // opt-in with AMEM_AG_NVLS=1 or AMEM_ALGO=nvls until it has been measured to win.
+  if (in.kind == kCollAllGather && in.nvls && n > 2) {
+    static const long ag_nvls = env_long("AMEM_AG_NVLS", 0);
+    if (ag_nvls || env_algo() == kAlgoNvls || in.forced_algo == kAlgoNvls) p.algo = kAlgoNvls;
+  }
   // Grid: one block per 32 KiB of work up to the communicator's cap; latency-bound sizes use
   // few blocks because every block waits on its own set of peer flags.
   size_t per_block = 32 << 10;
