@@ -235,6 +235,46 @@ class Communicator:
                                       _stream_handle(stream, send)), "ncclAlltoAll")
         return recv
 
+    def all_to_all_v(self, send, recv, send_counts, recv_counts, send_displs=None, recv_displs=None, stream=None):
+        """Variable-size all-to-all (element counts / displacements per peer, MPI_Alltoallv
+        style): one grouped launch of sends and receives -- the form in which NCCL applications
+        write it (ncclGroupStart + ncclSend/ncclRecv per peer + ncclGroupEnd); this rank's own
+        block is a local copy.  Counts must match pairwise: send_counts[j] here equals
+        recv_counts[me] on rank j."""
+        n, me = self.nranks, self.rank
+        assert len(send_counts) == n and len(recv_counts) == n and send.dtype == recv.dtype
+        def displs(counts, given):
+            if given is not None:
+                return list(given)
+            out, acc = [], 0
+            for c in counts:
+                out.append(acc)
+                acc += int(c)
+            return out
+        sd, rd = displs(send_counts, send_displs), displs(recv_counts, recv_displs)
+        if int(send_counts[me]) != int(recv_counts[me]):
+            raise ValueError("all_to_all_v: this rank's own send and receive counts differ")
+        es, dt, st = send.itemsize if hasattr(send, "itemsize") else send.element_size(), _dtype_code(send), _stream_handle(stream, send)
+        sp, rp = _ptr(send), _ptr(recv)
+        if send_counts[me]:
+            flat_s, flat_r = send.reshape(-1), recv.reshape(-1)
+            c = int(send_counts[me])
+            if hasattr(flat_r, "copy_"):
+                flat_r[rd[me]:rd[me] + c].copy_(flat_s[sd[me]:sd[me] + c])
+            else:
+                flat_r[rd[me]:rd[me] + c] = flat_s[sd[me]:sd[me] + c]
+        group_start()
+        try:
+            for k in range(1, n):
+                to, frm = (me + k) % n, (me - k) % n
+                if send_counts[to]:
+                    B.check(self.lib.ncclSend(sp + sd[to] * es, int(send_counts[to]), dt, to, self._h, st), "ncclSend")
+                if recv_counts[frm]:
+                    B.check(self.lib.ncclRecv(rp + rd[frm] * es, int(recv_counts[frm]), dt, frm, self._h, st), "ncclRecv")
+        finally:
+            group_end()
+        return recv
+
     def send(self, tensor, peer: int, stream=None):
         B.check(self.lib.ncclSend(_ptr(tensor), _numel(tensor), _dtype_code(tensor), peer, self._h, _stream_handle(stream, tensor)), "ncclSend")
 

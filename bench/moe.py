@@ -123,7 +123,8 @@ def main():
     res["combine_frac_of_770"] = res["combine_link_gbs"] / 770.0
 
     # all communicators paused and resumed together
-    first = layer(x).clone()
+    with torch.no_grad():
+        first = layer(x).clone()
     torch.cuda.synchronize()
     dist.barrier(group=gloo)
     used0 = torch.cuda.mem_get_info()[0]
@@ -133,7 +134,8 @@ def main():
         freed = torch.cuda.mem_get_info()[0] - used0
         resume_all()
         if c % 10 == 9 or c == args.cycles - 1:
-            out = layer(x)
+            with torch.no_grad():
+                out = layer(x)
             torch.cuda.synchronize()
             same = same and torch.equal(out, first)
         drift = max(drift, abs(torch.cuda.mem_get_info()[0] - used0))

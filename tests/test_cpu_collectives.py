@@ -124,3 +124,27 @@ def _multi_chunk(rank, world, uid):
 def test_multi_chunk_collectives():
     for d in run_ranks(_multi_chunk, 3, env={"AMEM_STAGE_MB": "7", "AMEM_P2P_SLOT_KB": "4"}):
         assert all(d.values()), d
+
+
+def _alltoallv(rank, world, uid):
+    import numpy as np
+    from asystem_amem_b200 import Communicator
+    comm = Communicator(world, rank, uid)
+    # rank i sends (i + 2 * j + 1) * 1000 + 3 elements to rank j, except nothing from 0 to 1
+    cnt = lambda i, j: 0 if (i, j) == (0, 1) else (i + 2 * j + 1) * 1000 + 3  # noqa: E731
+    sc = [cnt(rank, j) for j in range(world)]
+    rc = [cnt(j, rank) for j in range(world)]
+    send = np.concatenate([np.full(sc[j], 100.0 * rank + j, dtype=np.float32) for j in range(world)])
+    recv = np.full(sum(rc), -1.0, dtype=np.float32)
+    ok = True
+    for _ in range(2):
+        comm.all_to_all_v(send, recv, sc, rc)
+        exp = np.concatenate([np.full(rc[j], 100.0 * j + rank, dtype=np.float32) for j in range(world)])
+        ok = ok and bool(np.array_equal(recv, exp))
+        recv[:] = -1.0
+    comm.destroy()
+    return ok
+
+
+def test_all_to_all_v():
+    assert all(run_ranks(_alltoallv, 3))

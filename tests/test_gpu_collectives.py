@@ -172,6 +172,23 @@ def test_sendrecv_ring_and_pairs(world):
     assert all(run_emulated(world, fn))
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_all_to_all_v(world):
+    cnt = lambda i, j: 0 if (i, j) == (0, 1) else (i + 2 * j + 1) * 1001  # noqa: E731
+
+    def fn(rank, world, comm, stream):
+        sc = [cnt(rank, j) for j in range(world)]
+        rc = [cnt(j, rank) for j in range(world)]
+        send = torch.cat([torch.full((sc[j],), 100.0 * rank + j, device="cuda", dtype=torch.bfloat16) for j in range(world)])
+        recv = torch.full((sum(rc),), -1.0, device="cuda", dtype=torch.bfloat16)
+        comm.all_to_all_v(send, recv, sc, rc)
+        stream.synchronize()
+        exp = torch.cat([torch.full((rc[j],), 100.0 * j + rank, dtype=torch.bfloat16) for j in range(world)])
+        return torch.equal(recv.cpu(), exp)
+
+    assert all(run_emulated(world, fn))
+
+
 def test_unaligned_and_tiny_sizes():
     """Every size 1..130 elements and buffers at odd element offsets (no 16-byte alignment)."""
     world = 4

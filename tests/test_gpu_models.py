@@ -72,8 +72,9 @@ def test_moe_layer_matches_dense_reference():
 
     def fn(rank, world, comm, stream):
         layer = MoELayer(comm, dim, ffn, E, k, tokens_per_rank=T, capacity_factor=float(world), seed=7)
-        out1 = layer(xs[rank].cuda())
-        out2 = layer(xs[rank].cuda())
+        with torch.no_grad():
+            out1 = layer(xs[rank].cuda())
+            out2 = layer(xs[rank].cuda())
         stream.synchronize()
         return out1.cpu(), out2.cpu(), layer.router.detach().cpu(), layer.w13.detach().cpu(), layer.w2.detach().cpu()
 
