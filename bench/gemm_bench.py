@@ -2,8 +2,10 @@
 """Single-GPU throughput of the tcgen05 GEMM against cuBLAS (torch.matmul) on the tensor-parallel
 MLP shapes (Llama-3-70B, TP=8: d=8192, ffn/8=3584, 8192 tokens).  CUDA-event timing, L2 flushed
 between iterations, fraction of the measured cuBLAS peak from MEASURED_PEAKS.json."""
+import argparse
 import json
 import os
+import statistics
 import sys
 
 import torch
@@ -12,45 +14,65 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from asystem_amem_b200.ops import gemm_bf16  # noqa: E402
 
 
-def time_fn(fn, iters=10, warmup=3):
+def time_interleaved(fns, iters=30, warmup=3):
+    """Times several implementations of one problem turn by turn (so that clock and power state
+    hit them alike); returns {name: (median_ms, best_ms)}."""
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     for _ in range(warmup):
-        fn()
+        for fn in fns.values():
+            fn()
     torch.cuda.synchronize()
-    best, total = 1e9, 0.0
+    times = {k: [] for k in fns}
     for _ in range(iters):
-        flush.zero_()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        fn()
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e)
-        best = min(best, ms)
-        total += ms
-    return best, total / iters
+        for name, fn in fns.items():
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            fn()
+            e.record()
+            torch.cuda.synchronize()
+            times[name].append(s.elapsed_time(e))
+    return {k: (statistics.median(v), min(v)) for k, v in times.items()}
 
 
 def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default="gpurun_out/gemm.jsonl")
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--shapes", default="8192x3584x8192,8192x8192x3584,8192x8192x8192,4096x4096x4096,1024x3584x8192,2048x2048x2048")
+    args = ap.parse_args()
     peaks = {}
     p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
     if os.path.exists(p):
         peaks = json.load(open(p))
     peak = peaks.get("bf16_tflops", 1590.0)
-    shapes = [(8192, 3584, 8192), (8192, 8192, 3584), (8192, 8192, 8192), (4096, 4096, 4096), (1024, 3584, 8192)]
-    rows = []
-    for M, N, K in shapes:
-        a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
-        b = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
-        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        ours_best, ours_mean = time_fn(lambda: gemm_bf16(a, b, out))
-        ref_best, ref_mean = time_fn(lambda: torch.matmul(a, b.t(), out=out))
-        fl = 2.0 * M * N * K
-        rows.append({"M": M, "N": N, "K": K, "amem_ms": round(ours_best, 4), "cublas_ms": round(ref_best, 4),
-                     "amem_tflops": round(fl / ours_best / 1e9, 1), "cublas_tflops": round(fl / ref_best / 1e9, 1),
-                     "frac_of_measured_peak": round(fl / ours_best / 1e9 / peak, 3),
-                     "vs_cublas": round(ref_best / ours_best, 3)})
-        print(json.dumps(rows[-1]), flush=True)
+    shapes = [tuple(int(v) for v in sh.split("x")) for sh in args.shapes.split(",")]
+    os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+    with open(args.out, "w") as f:
+        for M, N, K in shapes:
+            a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+            b = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+            def ours(split):
+                def run():
+                    os.environ["AMEM_GEMM_SPLITK"] = split
+                    gemm_bf16(a, b, out)
+                return run
+
+            t = time_interleaved({"amem": ours("1"), "amem_nosplit": ours("0"), "cublas": lambda: torch.matmul(a, b.t(), out=out)},
+                                 iters=args.iters)
+            os.environ["AMEM_GEMM_SPLITK"] = "1"
+            fl = 2.0 * M * N * K
+            med, best = t["amem"]
+            row = {"M": M, "N": N, "K": K, "amem_ms": round(med, 4), "amem_best_ms": round(best, 4),
+                   "amem_no_tail_split_ms": round(t["amem_nosplit"][0], 4),
+                   "cublas_ms": round(t["cublas"][0], 4), "cublas_best_ms": round(t["cublas"][1], 4),
+                   "amem_tflops": round(fl / med / 1e9, 1), "cublas_tflops": round(fl / t["cublas"][0] / 1e9, 1),
+                   "frac_of_measured_peak": round(fl / med / 1e9 / peak, 3), "vs_cublas": round(t["cublas"][0] / med, 3),
+                   "timing": "median of %d, L2 flushed before every launch, implementations interleaved" % args.iters}
+            print(json.dumps(row), flush=True)
+            f.write(json.dumps(row) + "\n")
 
 
 if __name__ == "__main__":

@@ -52,6 +52,37 @@ int emu_grid(int nranks) {
 
 }  // namespace
 
+namespace {
+struct SplitKWs {
+  float* partials = nullptr;
+  uint32_t* counters = nullptr;
+};
+// One workspace per (device, stream); null when none exists and none can be made right now.
+SplitKWs* splitk_workspace(int dev, cudaStream_t stream, int ctas) {
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, SplitKWs> all;
+  std::lock_guard<std::mutex> lk(mu);
+  auto key = std::make_pair(dev, stream);
+  auto it = all.find(key);
+  if (it != all.end()) return it->second.partials ? &it->second : nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return nullptr;  // not recorded: a later launch outside the capture may allocate
+  }
+  SplitKWs w;
+  size_t ctr_bytes = gemm_splitk_ctr_words(ctas) * sizeof(uint32_t);
+  if (cudaMalloc((void**)&w.partials, gemm_splitk_ws_bytes(ctas)) != cudaSuccess ||
+      cudaMalloc((void**)&w.counters, ctr_bytes) != cudaSuccess || cudaMemset(w.counters, 0, ctr_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    if (w.partials) cudaFree(w.partials);
+    w = SplitKWs();  // remembered as "no workspace": the GEMM runs unsplit on this stream
+  }
+  auto ins = all.emplace(key, w);
+  return ins.first->second.partials ? &ins.first->second : nullptr;
+}
+}  // namespace
+
 extern "C" {
 
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
@@ -91,10 +122,23 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);
   g.map_a_local = g.map_a;
   int sms = gemm_default_grid(dev);
-  g.p.bn = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms);
+  // Split-K of the last wave needs a workspace (fp32 partial tiles + counters), kept per
+  // (device, stream) so that launches on different streams never share one.  It is allocated on
+  // the first launch of a stream; a stream that is being captured gets no split unless it
+  // already has one (allocation is not allowed there).  AMEM_GEMM_SPLITK=0 turns the split off.
+  const long splitk_on = env_long("AMEM_GEMM_SPLITK", 1);  // read per call: benches flip it
+  SplitKWs* ws = splitk_on ? splitk_workspace(dev, stream, sms) : nullptr;
+  int slices = 1;
+  const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
+  g.p.bn = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms, ws ? k_blocks : 0, &slices);
   if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn)) != kSuccess) return R(s);
   int tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + g.p.bn - 1) / g.p.bn);
-  g.grid = tiles < sms ? tiles : sms;
+  g.grid = (tiles < sms && slices <= 1) ? tiles : sms;
+  if (ws && slices > 1) {
+    g.p.sk_slices = slices;
+    g.p.sk_ws = ws->partials;
+    g.p.sk_ctr = ws->counters;
+  }
   s = launch_gemm(g, stream);
   if (s == kSuccess && status_dev[dev][0]) s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_dev[dev][0]);
   return R(s);

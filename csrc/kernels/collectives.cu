@@ -9,19 +9,10 @@
 // (blockIdx.y = rank): kernels of different ranks wait on one another, so they must never be
 // separate launches on the same device.  This is what lets the single-GPU test-suite cover
 // the multi-rank protocol.
-#include <cooperative_groups.h>
-
-#include "../core/log.h"
-#include "../core/status.h"
-#include "coll_device.cuh"
-#include "dispatch.h"
-#include "launch.h"
+#include "coll_kernels.cuh"
 
 namespace amem {
 namespace dev {
-#define AMEM_FN __device__ __forceinline__
-#include "coll_bodies.inl"
-#undef AMEM_FN
 
 // ------------------------------------------------------------------ NVLS all-reduce
 template <typename T> struct Multimem;
@@ -228,18 +219,6 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
 }
 
 // ------------------------------------------------------------------ kernels
-template <typename TI, typename TO, int OP, bool RED>
-__global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {
-  __shared__ int s_abort;
-  run_body<TI, TO, OP, RED>(a, blockIdx.x, gridDim.x, &s_abort, chunk_elems);
-}
-
-template <typename TI, typename TO, int OP, bool RED>
-__global__ void __launch_bounds__(512) coll_kernel_emu(const CollArgs* __restrict__ all, size_t chunk_elems) {
-  __shared__ int s_abort;
-  run_body<TI, TO, OP, RED>(all[blockIdx.y], blockIdx.x, gridDim.x, &s_abort, chunk_elems);
-}
-
 template <typename T>
 __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {
   __shared__ int s_abort;
@@ -281,6 +260,20 @@ static Status check_launch(const char* what) {
   return kSuccess;
 }
 
+// The reducing kernels live in one translation unit per group of element types.
+static Status launch_reduce(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream, const CollArgs* dev_all, int nranks, bool* ok) {
+  typedef Status (*PartFn)(const CollArgs&, const LaunchPlan&, cudaStream_t, const CollArgs*, int, bool*);
+  static const PartFn parts[] = {launch_reduce_part_bf16, launch_reduce_part_f32, launch_reduce_part_f16, launch_reduce_part_i32,
+                                 launch_reduce_part_i64,  launch_reduce_part_i8,  launch_reduce_part_f64};
+  for (PartFn fn : parts) {
+    bool handled = false;
+    Status st = fn(a, plan, stream, dev_all, nranks, &handled);
+    if (handled) return st;
+  }
+  *ok = false;
+  return kSuccess;
+}
+
 int sendrecv_blocks(const CollArgs& a) {
   int total = 0;
   for (int e = 0; e < a.n_p2p; ++e) total += p2p_lanes(a.p2p[e].bytes, a.p2p_slot_bytes, a.p2p_max_lanes);
@@ -305,24 +298,13 @@ Status launch_collective(const CollArgs& a, const LaunchPlan& plan, cudaStream_t
   }
   bool reducing = a.kind == kCollAllReduce || a.kind == kCollReduceScatter || a.kind == kCollReduce;
   if (reducing) {
-#define DEV_CALL(TI, TO, OP) dev::coll_kernel<TI, TO, OP, true><<<grid, block, 0, stream>>>(a, plan.chunk_elems)
-    AMEM_DISPATCH_REDUCE(a.dtype, a.out_dtype, a.redop, DEV_CALL);
-#undef DEV_CALL
+    Status st = launch_reduce(a, plan, stream, nullptr, 0, &ok);
+    if (st != kSuccess) return st;
   } else {
     dev::coll_kernel<unsigned char, unsigned char, kSum, false><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
   }
   if (!ok) return fail(kInvalidArgument, "unsupported datatype %d -> %d with operator %d", a.dtype, a.out_dtype, a.redop);
   return check_launch("collective");
-}
-
-template <typename K>
-static Status coop_launch(K kernel, dim3 grid, dim3 block, void** params, cudaStream_t stream, const char* what) {
-  cudaError_t e = cudaLaunchCooperativeKernel((const void*)kernel, grid, block, params, 0, stream);
-  if (e != cudaSuccess) {
-    cudaGetLastError();
-    return fail(kCudaError, "%s cooperative launch (%u x %u blocks) failed: %s", what, grid.x, grid.y, cudaGetErrorString(e));
-  }
-  return kSuccess;
 }
 
 Status launch_collective_emu(const CollArgs* dev_all, const CollArgs& a, int nranks, const LaunchPlan& plan, cudaStream_t stream) {
@@ -340,9 +322,7 @@ Status launch_collective_emu(const CollArgs* dev_all, const CollArgs& a, int nra
   Status st = kSuccess;
   bool reducing = a.kind == kCollAllReduce || a.kind == kCollReduceScatter || a.kind == kCollReduce;
   if (reducing) {
-#define EMU_CALL(TI, TO, OP) st = coop_launch(dev::coll_kernel_emu<TI, TO, OP, true>, grid, block, params, stream, "collective(emu)")
-    AMEM_DISPATCH_REDUCE(a.dtype, a.out_dtype, a.redop, EMU_CALL);
-#undef EMU_CALL
+    st = launch_reduce(a, plan, stream, dev_all, nranks, &ok);
   } else {
     st = coop_launch(dev::coll_kernel_emu<unsigned char, unsigned char, kSum, false>, grid, block, params, stream, "collective(emu)");
   }

@@ -16,6 +16,7 @@
 // accumulators so the epilogue of tile i overlaps the main loop of tile i+1.  TMA loads never
 // use cluster multicast and only ever read this GPU's own memory; peers are reached with plain
 // or bulk stores.  Every wait is bounded and ends in an error status, not a hang.
+#include <algorithm>
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 
@@ -37,6 +38,10 @@ constexpr int UMMA_K = 16;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy of the all-gather mover
 constexpr int EPI_CHUNK_BYTES = BM * 32 * 2;  // one 32-column chunk of a tile in bf16
+// A parked (split-K) accumulator: BN/4 column groups x (rows of every band padded to an odd
+// count) x 4 floats; bands x padded rows <= BM + 2 * slices <= BM + 64.
+constexpr int SK_MAX_SLICES = 32;
+constexpr size_t SK_SLOT_FLOATS = (size_t)(BN_MAX / 4) * (BM + 2 * SK_MAX_SLICES) * 4;
 
 struct __align__(8) SmemCtl {
   uint64_t full[STAGES];
@@ -54,6 +59,34 @@ struct Tile {
   int m_in;       // row-block index inside the shard
   int n_blk;
 };
+
+// One unit of work of a compute CTA: a whole tile, or (tail split) a range of K blocks of one.
+struct Work {
+  int t, kb0, kb1;
+  int slice;   // -1: whole tile
+};
+// CTA g of G runs `full_waves` whole tiles (t = g, g + G, ...) and then at most one item of the
+// last wave: a whole tile when that wave is not split, else slice g % S of tail tile g / S.
+__device__ __forceinline__ int work_count(int g, int G, int total_tiles, int S) {
+  const int full = total_tiles / G, rem = total_tiles - full * G;
+  return full + ((S > 1 ? g < rem * S : g < rem) ? 1 : 0);
+}
+__device__ __forceinline__ Work work_of(int i, int g, int G, int total_tiles, int S, int num_kb) {
+  const int full = total_tiles / G;
+  Work w;
+  if (i < full || S <= 1) {
+    w.t = g + i * G;
+    w.kb0 = 0;
+    w.kb1 = num_kb;
+    w.slice = -1;
+  } else {
+    w.t = full * G + g / S;
+    w.slice = g % S;
+    w.kb0 = (int)((long)w.slice * num_kb / S);
+    w.kb1 = (int)((long)(w.slice + 1) * num_kb / S);
+  }
+  return w;
+}
 
 // Tile order.  plain: row blocks fastest (CTAs that run together share the B tile in L2).
 // all-gather: the local shard first, then row block by row block across the source ranks
@@ -296,6 +329,8 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   const int num_kb = (p.K + BK - 1) / BK;
   const int g = cta - comm_ctas, G = nctas - comm_ctas;  // compute CTA index / count
   const uint32_t idesc = make_idesc_bf16(BM, BN);
+  const int S = (p.mode == kGemmPlain && p.sk_slices > 1 && p.sk_ws && p.sk_ctr) ? p.sk_slices : 1;
+  const int n_items = is_mover ? 0 : work_count(g, G, total_tiles, S);
 
   if (is_mover) {
     if (threadIdx.x == 0) ag_mover(p, ring, ctl, cta, epoch);
@@ -305,8 +340,9 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       int stage = 0;
       uint32_t phase = 0, issued = 0, issued_phase = 0;
       bool ok = true;
-      for (int t = g; t < total_tiles && ok; t += G) {
-        Tile tl = tile_of(p, t, tiles_m, tiles_n);
+      for (int i = 0; i < n_items && ok; ++i) {
+        const Work wk = work_of(i, g, G, total_tiles, S, num_kb);
+        Tile tl = tile_of(p, wk.t, tiles_m, tiles_n);
         const bool remote = p.mode == kGemmAllGather && fused && tl.shard != r;
         if (remote) {
           // wait for every 32-row unit this 128-row tile covers
@@ -323,7 +359,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         }
         const CUtensorMap* ma = (p.mode == kGemmAllGather && fused && !remote) ? map_a_local : map_a;
         int row0 = tl.m_in * BM + ((p.mode == kGemmAllGather && fused && !remote) ? 0 : tl.shard * p.rows_per_rank);
-        for (int kb = 0; kb < num_kb && ok; ++kb) {
+        for (int kb = wk.kb0; kb < wk.kb1 && ok; ++kb) {
           ok = mbar_wait(&ctl->empty[stage], phase ^ 1u, p.coll.timeout_ns, abort);
           if (!ok) break;
           mbar_expect_tx(&ctl->full[stage], (uint32_t)(A_BYTES + BN * BK * 2));
@@ -354,14 +390,15 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = g; t < total_tiles && ok; t += G, ++it) {
+      for (; it < n_items && ok; ++it) {
+        const Work wk = work_of(it, g, G, total_tiles, S, num_kb);
         const int buf = it & 1;
         const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
         ok = mbar_wait(&ctl->tempty[buf], acc_phase ^ 1u, p.coll.timeout_ns, abort);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN_MAX);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
           ok = mbar_wait(&ctl->full[stage], phase, p.coll.timeout_ns, abort);
           if (!ok) break;
           tc_fence_after_sync();
@@ -370,7 +407,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             // 16 bf16 = 32 bytes further along K inside the 128-byte swizzled row
-            tc_mma_f16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) ? 1u : 0u);
+            tc_mma_f16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.kb0 || kk) ? 1u : 0u);
           }
           tc_commit(&ctl->empty[stage]);  // frees the stage when these MMAs have read it
           if (++stage == STAGES) {
@@ -386,8 +423,9 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
     const int lane_grp = warp % 4;  // TMEM lanes [32 * lane_grp, +32) belong to this warp
     int it = 0;
     bool ok = true;
-    for (int t = g; t < total_tiles && ok; t += G, ++it) {
-      Tile tl = tile_of(p, t, tiles_m, tiles_n);
+    for (; it < n_items && ok; ++it) {
+      const Work wk = work_of(it, g, G, total_tiles, S, num_kb);
+      Tile tl = tile_of(p, wk.t, tiles_m, tiles_n);
       const int buf = it & 1;
       const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
       ok = mbar_wait(&ctl->tfull[buf], acc_phase, p.coll.timeout_ns, abort);
@@ -434,6 +472,93 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           bulk_wait_all();  // the whole tile has been written at the owner
           __threadfence_system();
           red_release_sys_add(&p.fflags[tl.shard]->rs_done[r][tl.m_in], 1u);
+        }
+      } else if (wk.slice >= 0) {
+        // Slice of a tail tile: park the fp32 accumulator, meet the tile's other slices, then
+        // sum one band of its rows over all slices (in slice order) and store that band.
+        // A parked tile is laid out [band][4-column group][row in band, padded to an odd
+        // count][4 floats]: a band of one slice is one contiguous piece, fetched with a single
+        // bulk copy into the (now idle) operand ring, so every slice's band is in flight at
+        // once; the odd row count keeps the shared-memory reads that follow free of conflicts.
+        const int j = wk.t - (total_tiles / G) * G;
+        const size_t part_elems = SK_SLOT_FLOATS;  // one parked tile, padding included
+        const int groups = BN / 4;
+        const int rows_per = (BM + S - 1) / S, rows_pad = rows_per | 1;
+        const size_t band_vecs = (size_t)groups * rows_pad;
+        float4* mine = (float4*)(p.sk_ws + ((size_t)j * S + wk.slice) * part_elems);
+        const int row = lane_grp * 32 + lane;
+        float4* my_row = mine + (size_t)(row / rows_per) * band_vecs + (row % rows_per);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            my_row[(size_t)(c * 8 + q) * rows_pad] =
+                make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        uint32_t* ctr = p.sk_ctr + 2 * j;
+        const int r0 = wk.slice * rows_per, r1 = min(BM, r0 + rows_per);
+        const uint32_t band_bytes = (uint32_t)(band_vecs * sizeof(float4));
+        if (warp == 2 && lane == 0) {
+          atomicAdd(ctr, 1u);
+          if (*abort || !dev::wait_flag_ge(ctr, (uint32_t)S, p.coll.timeout_ns)) {
+            dev::report_error(p.coll.status, kDevGemmTimeout, r, wk.slice, j, 0xdead0003u);
+            *abort = 1;
+          }
+          __threadfence();
+          if (!*abort && r1 > r0) {
+            // every MMA of this CTA has completed (the accumulator was read above) and the
+            // producer has nothing in flight: the ring is free
+            fence_proxy_async();
+            mbar_expect_tx(&ctl->copy_full[0], band_bytes * (uint32_t)S);
+            for (int s2 = 0; s2 < S; ++s2) {
+              const char* src = (const char*)(p.sk_ws + ((size_t)j * S + s2) * part_elems + (size_t)wk.slice * band_vecs * 4);
+              // pieces of at most 32 KB: one copy of more than 64 KB delivered wrong bytes at
+              // both ends of its destination
+              for (uint32_t o = 0; o < band_bytes; o += COPY_PIECE)
+                bulk_g2s(ring + (size_t)s2 * band_bytes + o, src + o, min((uint32_t)COPY_PIECE, band_bytes - o), &ctl->copy_full[0]);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!*abort && r1 > r0) {
+          bool got = mbar_wait(&ctl->copy_full[0], 0u, p.coll.timeout_ns, abort);
+          if (got) {
+            const float4* sm = (const float4*)ring;
+            const int total = (r1 - r0) * groups;
+            for (int e = row; e < total; e += 128) {
+              const int rr = e / groups, c4 = e % groups;
+              const float4* sp = sm + (size_t)c4 * rows_pad + rr;
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int s2 = 0; s2 < S; ++s2) {
+                const float4 x = sp[(size_t)s2 * band_vecs];
+                acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+              }
+              const int grow = tl.m_in * BM + r0 + rr, gcol = tl.n_blk * BN + c4 * 4;
+              if (grow < p.rows_per_rank && gcol < p.N) {
+                alignas(8) __nv_bfloat162 h[2];
+                h[0] = __floats2bfloat162_rn(acc.x, acc.y);
+                h[1] = __floats2bfloat162_rn(acc.z, acc.w);
+                *(uint2*)((__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + grow) * p.ldc + gcol) = *(const uint2*)h;
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          __threadfence();
+          if (atomicAdd(ctr + 1, 1u) == (uint32_t)S - 1u) {  // last reader: leave the counters at zero
+            ctr[0] = 0;
+            ctr[1] = 0;
+            __threadfence();
+          }
         }
       } else {
         const int row_in = tl.m_in * BM + lane_grp * 32 + lane;  // row inside the shard
@@ -546,20 +671,45 @@ Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, u
 
 size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + 2 * gemmk::EPI_CHUNK_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
 
-int gemm_pick_bn(int row_tiles, int N, int ctas) {
-  int best = kGemmBN;
-  long best_cost = -1;
+static double splitk_fixup_blocks() {
+  const long v = env_long("AMEM_GEMM_SPLITK_COST", 24);  // in K blocks of main loop (measured: 20-35)
+  return (double)v;
+}
+
+int gemm_tail_slices(long tiles, int ctas, int k_blocks) {
+  long rem = tiles % ctas;
+  if (rem == 0 || k_blocks <= 0) return 1;
+  long s = std::min<long>(ctas / rem, k_blocks / 8);
+  if (s > gemmk::SK_MAX_SLICES) s = gemmk::SK_MAX_SLICES;
+  if (s < 2) return 1;
+  // the fix-up (park the accumulator, wait, re-read a band of every slice) costs about as much
+  // as two dozen K blocks of main loop; split only when the shortened wave plus that clearly
+  // wins (with two or three slices it measured no better than the unsplit wave)
+  double tail = 1.0 / (double)s + splitk_fixup_blocks() / (double)k_blocks;
+  return tail < 0.75 ? (int)s : 1;
+}
+
+size_t gemm_splitk_ws_bytes(int ctas) { return (size_t)ctas * gemmk::SK_SLOT_FLOATS * sizeof(float); }
+size_t gemm_splitk_ctr_words(int ctas) { return (size_t)2 * ctas; }
+
+int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks, int* slices) {
+  int best = kGemmBN, best_s = 1;
+  double best_cost = -1;
   for (int bn = kGemmBN; bn >= 128; bn -= 32) {
     long tiles = (long)row_tiles * ((N + bn - 1) / bn);
-    long waves = (tiles + ctas - 1) / ctas;
+    long full = tiles / ctas, rem = tiles % ctas;
+    int s = gemm_tail_slices(tiles, ctas, k_blocks);
+    double tail = rem == 0 ? 0.0 : (s > 1 ? 1.0 / s + splitk_fixup_blocks() / k_blocks : 1.0);
     // measured: a tile's time depends only weakly on its width (the main loop is bound by
     // filling shared memory, not by the tensor pipe), so count waves first, width second
-    long cost = waves * (bn + 600);
+    double cost = ((double)full + tail) * (bn + 600);
     if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best = bn;
+      best_s = s;
     }
   }
+  if (slices) *slices = best_s;
   return best;
 }
 

@@ -40,6 +40,12 @@ struct GemmParams {
   void* rs_buf[kMaxRanks];  // reduce-scatter: every rank's partial buffer, tile-major [nranks][row blocks][col blocks][128 x 256]
   void* rs_out;             // reduce-scatter: bf16 [rows_per_rank, N]
   FusedFlags* fflags[kMaxRanks];
+  // Split-K of the last, partly filled wave of tiles (plain mode): each of its tiles is cut in
+  // sk_slices ranges of K that run on different CTAs; partial accumulators meet in sk_ws
+  // (fp32, [tile][slice][32-column chunk][128 rows][32]) and are summed in slice order.
+  int sk_slices;            // 0 or 1: off
+  float* sk_ws;
+  uint32_t* sk_ctr;         // two counters per tail tile (arrived, finished), zero between launches
   CollArgs coll;            // rank, nranks, control blocks, status words, timeout
 };
 
@@ -59,7 +65,14 @@ Status launch_gemm(const GemmLaunch& g, cudaStream_t stream);
 // All ranks of an emulated communicator in one cooperative grid (blockIdx.y = rank).
 Status launch_gemm_emu(const GemmLaunch* ranks, int nranks, cudaStream_t stream);
 int gemm_default_grid(int device);
-// Tile width that minimises (waves of tiles) x (tile width) for `ctas` compute CTAs.
-int gemm_pick_bn(int row_tiles, int N, int ctas);
+// Tile width that minimises (waves of tiles) x (tile width) for `ctas` compute CTAs.  With
+// `k_blocks` > 0 the last wave may be split along K (see GemmParams::sk_slices): its cost is
+// then 1/slices of a wave plus the fix-up, and *slices receives the split to use (1 = none).
+int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks = 0, int* slices = nullptr);
+// Slices of the tail split for a given tiling, 1 when splitting does not pay.
+int gemm_tail_slices(long tiles, int ctas, int k_blocks);
+// Bytes of split-K workspace / number of counters that a launch on `ctas` CTAs may touch.
+size_t gemm_splitk_ws_bytes(int ctas);
+size_t gemm_splitk_ctr_words(int ctas);
 
 }  // namespace amem

@@ -54,7 +54,7 @@ LaunchPlan plan_collective(const TunerInput& in) {
   }
   // All-gather may push through the multicast mapping (multimem.st: one store instead of n-1);
   // opt-in with AMEM_AG_NVLS=1 or AMEM_ALGO=nvls until it has been measured to win.
-  if (in.kind == kCollAllGather && in.nvls && n > 2) {
+  if (in.kind == kCollAllGather && in.nvls && n > 1) {
     static const long ag_nvls = env_long("AMEM_AG_NVLS", 0);
     if (ag_nvls || env_algo() == kAlgoNvls || in.forced_algo == kAlgoNvls) p.algo = kAlgoNvls;
   }

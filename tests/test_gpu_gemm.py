@@ -28,6 +28,26 @@ def test_gemm_bf16_matches_fp32_reference(M, N, K):
         torch.testing.assert_close(out.float(), ref.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 512, 4096), (1000, 264, 8192), (1000, 264, 2048), (4096, 4096, 4096), (8192, 3584, 8192), (520, 776, 4096)])
+def test_gemm_split_k_tail(M, N, K):
+    """Shapes whose last wave of tiles is cut along K: partial accumulators meet in the
+    workspace, the sum is taken in slice order, so repeated calls agree bit for bit, on the
+    same stream and on a second one (which gets a workspace of its own)."""
+    from asystem_amem_b200.ops import gemm_bf16
+    a, b = _rand((M, K), 3).cuda(), _rand((N, K), 4, 0.05).cuda()
+    outs = [gemm_bf16(a, b) for _ in range(3)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        outs.append(gemm_bf16(a, b))
+    torch.cuda.synchronize()
+    ref = a.float() @ b.float().t()
+    tol = 2e-2 * ref.abs().max().item() + 1e-2
+    for out in outs:
+        assert (out.float() - ref).abs().max().item() <= tol
+        assert torch.equal(out, outs[0])
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("m_local,N,K", [(128, 256, 256), (200, 520, 328), (512, 1024, 1024)])
 def test_all_gather_gemm(world, m_local, N, K):
