@@ -173,14 +173,15 @@ def main() -> None:
         t1 = time.perf_counter()
         pause()
         t2 = time.perf_counter()
-        free1 = torch.cuda.mem_get_info()[0]
+        free1 = torch.cuda.mem_get_info()[0]                     # instrumentation, outside both timed windows
+        t2b = time.perf_counter()
         resume()
         t3 = time.perf_counter()
         collective()
         host_out.copy_(y[:16].float(), non_blocking=True)        # D2H read of the result
         torch.cuda.synchronize()
         t4 = time.perf_counter()
-        return (t2 - t1) * 1e3, (t3 - t2) * 1e3, ev[0].elapsed_time(ev[1]), free1 - free0, (t4 - t0) * 1e3
+        return (t2 - t1) * 1e3, (t3 - t2b) * 1e3, ev[0].elapsed_time(ev[1]), free1 - free0, (t4 - t0) * 1e3
 
     for _ in range(args.warmup):
         step(False)

@@ -3,6 +3,8 @@
 #include <unistd.h>
 
 #include <cstring>
+#include <string>
+#include <thread>
 #include <vector>
 
 #include "../core/log.h"
@@ -30,6 +32,39 @@ struct Phase {
 };
 
 bool is_local(const Allocation& a) { return !from_peer(a.type); }
+
+// Runs fn(0) .. fn(n-1), one thread per index (the calling thread takes index 0).  The driver
+// calls that pause and resume make per peer (unmap, release, import, map, set-access) are
+// independent of one another, and with eight ranks they are most of the latency.
+// AMEM_PR_THREADS=0 runs them in turn.
+template <typename F>
+void parallel_each(size_t n, F fn) {
+  static const long on = env_long("AMEM_PR_THREADS", 1);
+  if (n <= 1 || !on) {
+    for (size_t i = 0; i < n; ++i) fn(i);
+    return;
+  }
+  std::vector<std::thread> th;
+  th.reserve(n - 1);
+  for (size_t i = 1; i < n; ++i) th.emplace_back([&fn, i] { fn(i); });
+  fn(0);
+  for (auto& t : th) t.join();
+}
+
+// Result of one per-peer job; the error text lives in a thread-local slot, so it is carried
+// back to the calling thread by hand.
+struct JobResult {
+  Status st = kSuccess;
+  std::string err;
+};
+Status first_error(const std::vector<JobResult>& res) {
+  for (const auto& r : res)
+    if (r.st != kSuccess) {
+      last_error_slot() = r.err;
+      return r.st;
+    }
+  return kSuccess;
+}
 
 // Undo what one resume attempt built, so the scope is back in the PAUSED state.
 void rollback_locals(Registry& reg, VmmBackend* be, std::vector<Allocation>& made) {
@@ -84,16 +119,27 @@ Status pause_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, PeerE
   }
   {  // 2. let go of the peers' memory while the copies run (no data to save: the owner has it)
     Phase p("amem.pause.release_import", &st->release_import_us);
-    for (auto& a : recs) {
-      if (is_local(a) || a.state != kMemAlloc || a.category == kResident) continue;
-      AMEM_TRY(be->unmap(a.va, a.size));
-      AMEM_TRY(be->release(a.handle));
+    std::vector<Allocation*> peers;
+    for (auto& a : recs)
+      if (!is_local(a) && a.state == kMemAlloc && a.category != kResident) peers.push_back(&a);
+    std::vector<JobResult> res(peers.size());
+    parallel_each(peers.size(), [&](size_t i) {
+      Allocation& a = *peers[i];
+      Status s = be->unmap(a.va, a.size);
+      if (s == kSuccess) s = be->release(a.handle);
+      res[i].st = s;
+      if (s != kSuccess) res[i].err = last_error_slot();
+    });
+    for (size_t i = 0; i < peers.size(); ++i) {
+      if (res[i].st != kSuccess) continue;
+      Allocation& a = *peers[i];
       a.handle = 0;
       a.state = kMemHole;
       reg.update(a);
       st->bytes_released_peer += a.size;
       st->n_release_peer++;
     }
+    AMEM_TRY(first_error(res));
   }
   {  // 3. saves done -> drop the local physical memory, keep the addresses
     Phase p("amem.pause.release_local", &st->release_local_us);
@@ -207,30 +253,53 @@ Status resume_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, Peer
     }
     {  // 3b. ... then all receives, mapping each peer's memory where it used to be
       Phase p("amem.resume.import", &st->import_us);
+      // the descriptors first, in record order (the peers sent them in that order) ...
+      std::vector<Allocation*> holes;
+      std::vector<int> fds;
       for (auto& a : recs) {
         if (is_local(a) || a.state != kMemHole) continue;
         uint32_t sym = 0;
         uint64_t sz = 0;
         int fd = -1;
-        AMEM_TRY(px->recv_fd(a.exporter_rank, &sym, &sz, &fd));
-        if (sym != a.sym_id || sz != a.size) {
+        Status s = px->recv_fd(a.exporter_rank, &sym, &sz, &fd);
+        if (s == kSuccess && (sym != a.sym_id || sz != a.size)) {
           if (fd >= 0) close(fd);
-          return fail(kInternalError, "resume: expected segment %u (%zu B) from rank %d, got %u (%llu B)", a.sym_id,
-                      a.size, a.exporter_rank, sym, (unsigned long long)sz);
+          fd = -1;
+          s = fail(kInternalError, "resume: expected segment %u (%zu B) from rank %d, got %u (%llu B)", a.sym_id, a.size,
+                   a.exporter_rank, sym, (unsigned long long)sz);
         }
-        uint64_t h = 0;
-        Status s = be->import_fd(fd, a.size, &h);
-        close(fd);
-        AMEM_TRY(s);
-        s = be->map(a.va, a.size, h, a.dev);
         if (s != kSuccess) {
-          be->release(h);
+          for (int f : fds) close(f);
           return s;
         }
-        a.handle = h;
-        a.state = kMemAlloc;
-        reg.update(a);
+        holes.push_back(&a);
+        fds.push_back(fd);
       }
+      // ... then every peer's memory goes back where it used to be, side by side
+      std::vector<JobResult> res(holes.size());
+      parallel_each(holes.size(), [&](size_t i) {
+        Allocation& a = *holes[i];
+        uint64_t h = 0;
+        Status s = be->import_fd(fds[i], a.size, &h);
+        close(fds[i]);
+        if (s == kSuccess) {
+          s = be->map(a.va, a.size, h, a.dev);
+          if (s != kSuccess) {
+            std::string keep = last_error_slot();
+            be->release(h);
+            last_error_slot() = keep;
+          }
+        }
+        res[i].st = s;
+        if (s != kSuccess) res[i].err = last_error_slot();
+        else a.handle = h;
+      });
+      for (size_t i = 0; i < holes.size(); ++i) {
+        if (res[i].st != kSuccess) continue;
+        holes[i]->state = kMemAlloc;
+        reg.update(*holes[i]);
+      }
+      AMEM_TRY(first_error(res));
     }
   }
   {  // 4. contents are back
