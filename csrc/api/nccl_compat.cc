@@ -355,6 +355,15 @@ ncclResult_t ncclGroupStart(void) {
   return R(Comm::group_start());
 }
 ncclResult_t ncclGroupEnd(void) { return R(Comm::group_end()); }
+ncclResult_t ncclGroupSimulateEnd(ncclSimInfo_t* simInfo) {
+  if (simInfo && (simInfo->size != sizeof(ncclSimInfo_t) || simInfo->magic != 0x74685283u))
+    return R(fail(kInvalidArgument, "ncclGroupSimulateEnd: simInfo was not set up with NCCL_SIM_INFO_INITIALIZER"));
+  float us = 0.f;
+  Status st = Comm::group_simulate_end(&us);
+  if (st == kSuccess && simInfo) simInfo->estimatedTime = us;
+  return R(st);
+}
+void ncclResetDebugInit(void) { log_level_ref().store((int)env_long("GMM_LOG", kInfo)); }
 
 // ---- AMem -----------------------------------------------------------------------------
 ncclResult_t ncclPause(ncclComm_t* comm) {

@@ -73,6 +73,7 @@ class Comm {
   Status p2p(bool is_send, const void* src, void* dst, size_t bytes, int peer, cudaStream_t stream);
   static Status group_start();
   static Status group_end();
+  static Status group_simulate_end(float* est_us);
 
   // Fills kernel arguments for fused kernels built on top of the communicator.
   void fill_args(CollArgs* a) const;

@@ -182,6 +182,28 @@ Status Comm::group_end() {
   return first;
 }
 
+// Closes the group without launching anything: the queued point-to-point operations are
+// dropped and their total is priced with the measured peer-copy rate (ncclGroupSimulateEnd).
+Status Comm::group_simulate_end(float* est_us) {
+  if (t_group_depth <= 0) return fail(kInvalidUsage, "ncclGroupSimulateEnd without ncclGroupStart");
+  if (--t_group_depth > 0) {
+    if (est_us) *est_us = 0.f;
+    return kSuccess;
+  }
+  std::vector<Comm*> comms;
+  comms.swap(t_group_comms);
+  double us = 0;
+  for (Comm* c : comms) {
+    size_t out_bytes = 0, in_bytes = 0;
+    for (auto& e : c->pending_) (e.is_send ? out_bytes : in_bytes) += e.bytes;
+    c->pending_.clear();
+    // launch + flag latency, then the busier direction at ~770 GB/s per direction
+    us += 8.0 + (double)std::max(out_bytes, in_bytes) / 770e3;
+  }
+  if (est_us) *est_us = (float)us;
+  return kSuccess;
+}
+
 Status Comm::p2p(bool is_send, const void* src, void* dst, size_t bytes, int peer, cudaStream_t stream) {
   AMEM_TRY(check_usable(is_send ? "ncclSend" : "ncclRecv"));
   if (peer < 0 || peer >= nranks_) return fail(kInvalidArgument, "peer %d out of range", peer);

@@ -139,6 +139,20 @@ ncclResult_t ncclRecv(void* recvbuff, size_t count, ncclDataType_t datatype, int
 ncclResult_t ncclGroupStart(void);
 ncclResult_t ncclGroupEnd(void);
 
+/* Filled by ncclGroupSimulateEnd: the group is closed without being launched and its duration
+ * (microseconds) is estimated. */
+typedef struct ncclSimInfo_v22200 {
+  size_t size;
+  unsigned int magic;
+  unsigned int version;
+  float estimatedTime;
+} ncclSimInfo_t;
+#define NCCL_UNDEF_FLOAT -1.0f
+#define NCCL_SIM_INFO_INITIALIZER { sizeof(ncclSimInfo_t), 0x74685283, NCCL_VERSION_CODE, NCCL_UNDEF_FLOAT }
+ncclResult_t ncclGroupSimulateEnd(ncclSimInfo_t* simInfo);
+/* Re-reads the logging environment (GMM_LOG). */
+void ncclResetDebugInit(void);
+
 /* ---- AMem: pause / resume ------------------------------------------------------------ */
 /* comm == NULL (or *comm == NULL): every communicator of the process plus ncclMemAlloc
  * memory.  Otherwise only that communicator.  Synchronous; every rank of the communicator

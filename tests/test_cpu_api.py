@@ -41,6 +41,21 @@ def _api(rank, world, uid):
     st = mem_stats()
     out["stats"] = (st["n_local"] == 2 and st["n_imported"] == 2 * (world - 1) and st["scratch_bytes"] > st["stateful_bytes"] > 0
                     and st["bytes_by_tag"][1] > 0 and st["bytes_by_tag"][7] > 0 and st["group_id"] == 170)
+    # a simulated group: nothing is sent, the estimate is positive, the next real group works
+    class SimInfo(ctypes.Structure):
+        _fields_ = [("size", ctypes.c_size_t), ("magic", ctypes.c_uint), ("version", ctypes.c_uint), ("estimatedTime", ctypes.c_float)]
+    sim = SimInfo(ctypes.sizeof(SimInfo), 0x74685283, 22705, -1.0)
+    buf = np.zeros(1 << 16, dtype=np.float32)
+    lib.ncclGroupStart()
+    lib.ncclSend(buf.ctypes.data, buf.size, B.DTYPES["float32"], (rank + 1) % world, comm._h, None)
+    lib.ncclRecv(buf.ctypes.data, buf.size, B.DTYPES["float32"], (rank - 1) % world, comm._h, None)
+    lib.ncclGroupSimulateEnd.argtypes = [ctypes.POINTER(SimInfo)]
+    out["simulate"] = lib.ncclGroupSimulateEnd(ctypes.byref(sim)) == 0 and sim.estimatedTime > 0
+    out["simulate_bad_struct"] = lib.ncclGroupSimulateEnd(ctypes.byref(SimInfo(1, 2, 3, 0.0))) == 4
+    y = np.full(10, float(rank), dtype=np.float32)
+    assert lib.ncclAllReduce(y.ctypes.data, y.ctypes.data, 10, B.DTYPES["float32"], 0, comm._h, None) == 0
+    out["after_simulate"] = bool(np.all(y == sum(range(world))))
+    lib.ncclResetDebugInit()
     bad = np.zeros(4, dtype=np.float32)
     out["bad_root"] = lib.ncclBroadcast(bad.ctypes.data, bad.ctypes.data, 4, B.DTYPES["float32"], world + 3, comm._h, None) == 4
     comm.destroy()
