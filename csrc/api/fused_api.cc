@@ -119,8 +119,6 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   g.p.coll.status = status_dev[dev];
   g.p.coll.timeout_ns = 5ull * 1000000000ull;
   g.p.fflags[0] = (FusedFlags*)(ctrl[dev] + 1);
-  if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, kGemmBM)) != kSuccess) return R(s);
-  g.map_a_local = g.map_a;
   int sms = gemm_default_grid(dev);
   // Split-K of the last wave needs a workspace (fp32 partial tiles + counters), kept per
   // (device, stream) so that launches on different streams never share one.  It is allocated on
@@ -128,11 +126,24 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   // already has one (allocation is not allowed there).  AMEM_GEMM_SPLITK=0 turns the split off.
   const long splitk_on = env_long("AMEM_GEMM_SPLITK", 1);  // read per call: benches flip it
   SplitKWs* ws = splitk_on ? splitk_workspace(dev, stream, sms) : nullptr;
-  int slices = 1;
   const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
-  g.p.bn = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms, ws ? k_blocks : 0, &slices);
+  // Tile height: 256-row tiles feed two accumulators from one B tile (less shared-memory fill
+  // per FLOP, the limit of the 128-row main loop) but their epilogue is not hidden behind the
+  // next tile, so they pay only with a long K.  AMEM_GEMM_TALL = 0 / 1 forces, -1 decides.
+  const long tall_env = env_long("AMEM_GEMM_TALL", -1);
+  int slices = 1, slices_tall = 1;
+  const int bn_flat = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms, ws ? k_blocks : 0, &slices);
+  const int bn_tall = gemm_pick_bn((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, sms, ws ? k_blocks : 0, &slices_tall);
+  bool tall = tall_env >= 0 ? tall_env != 0 : gemm_tall_pays(M, N, k_blocks, sms, bn_flat, slices, bn_tall, slices_tall);
+  if (M <= kGemmBM) tall = false;
+  g.p.tall = tall ? 1 : 0;
+  g.p.bn = tall ? bn_tall : bn_flat;
+  if (tall) slices = slices_tall;
+  const int tile_rows = tall ? 2 * kGemmBM : kGemmBM;
+  if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, tile_rows)) != kSuccess) return R(s);
+  g.map_a_local = g.map_a;
   if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn)) != kSuccess) return R(s);
-  int tiles = ((M + kGemmBM - 1) / kGemmBM) * ((N + g.p.bn - 1) / g.p.bn);
+  int tiles = ((M + tile_rows - 1) / tile_rows) * ((N + g.p.bn - 1) / g.p.bn);
   g.grid = (tiles < sms && slices <= 1) ? tiles : sms;
   if (ws && slices > 1) {
     g.p.sk_slices = slices;

@@ -3,6 +3,7 @@
 // element-type traits.  Everything here is plain sm_100a CUDA C++ with inline PTX for the
 // memory-model sensitive accesses; no library device code is used.
 #pragma once
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -237,14 +238,15 @@ __device__ __forceinline__ void copy_span_mc(char* dst_mc, const char* src, size
 // out[i] = cast(scale * OP_r(slot_r[i]))  for i in [0, n); reduction order is rank 0..nslots-1,
 // accumulated in Acc<TI> (fp32 for 16-bit floats) and rounded once.
 template <typename TI, typename TO, int OP>
-__device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale, Lane ln) {
+__device__ __noinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale, Lane ln) {
   using A = typename Acc<TI>::type;
   constexpr int VI = 16 / sizeof(TI);
   int t = ln.tid, nt = ln.nt;
   bool aligned = (((uintptr_t)out) % (VI * sizeof(TO)) == 0);
   for (int r = 0; r < nslots; ++r) aligned = aligned && (((uintptr_t)slots[r] & 15) == 0);
   size_t nvec = aligned ? n / VI : 0;
-  auto one = [&](size_t i, const uint4* raw) {
+  auto one = [&](size_t i, const uint4* raw, auto nmax) {  // nmax: length of raw[], a compile-time constant
+    constexpr int NM = decltype(nmax)::value;
     A acc[VI];
     {
       const TI* e = (const TI*)&raw[0];
@@ -252,7 +254,7 @@ __device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int
       for (int k = 0; k < VI; ++k) acc[k] = to_acc<TI>(e[k]);
     }
 #pragma unroll
-    for (int r = 1; r < kMaxRanks; ++r) {
+    for (int r = 1; r < NM; ++r) {
       if (r < nslots) {
         const TI* e = (const TI*)&raw[r];
 #pragma unroll
@@ -278,25 +280,28 @@ __device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int
     }
   };
   size_t i = t;
-  // two output vectors per thread per trip: 2 x nslots independent 16-byte loads in flight
-  for (; i + (size_t)nt < nvec; i += 2 * (size_t)nt) {
-    uint4 ra[kMaxRanks], rb[kMaxRanks];
+  // up to four ranks: two output vectors per thread per trip, so that eight independent 16-byte
+  // loads are in flight either way (with more ranks a second vector would not fit the registers)
+  if (nslots <= kMaxRanks / 2) {
+    for (; i + (size_t)nt < nvec; i += 2 * (size_t)nt) {
+      uint4 ra[kMaxRanks / 2], rb[kMaxRanks / 2];
 #pragma unroll
-    for (int r = 0; r < kMaxRanks; ++r) {
-      if (r < nslots) {
-        ra[r] = ((const uint4*)slots[r])[i];
-        rb[r] = ((const uint4*)slots[r])[i + nt];
+      for (int r = 0; r < kMaxRanks / 2; ++r) {
+        if (r < nslots) {
+          ra[r] = ((const uint4*)slots[r])[i];
+          rb[r] = ((const uint4*)slots[r])[i + nt];
+        }
       }
+      one(i, ra, std::integral_constant<int, kMaxRanks / 2>());
+      one(i + nt, rb, std::integral_constant<int, kMaxRanks / 2>());
     }
-    one(i, ra);
-    one(i + nt, rb);
   }
   for (; i < nvec; i += nt) {
     uint4 ra[kMaxRanks];
 #pragma unroll
     for (int r = 0; r < kMaxRanks; ++r)
       if (r < nslots) ra[r] = ((const uint4*)slots[r])[i];
-    one(i, ra);
+    one(i, ra, std::integral_constant<int, kMaxRanks>());
   }
   for (size_t i = nvec * VI + t; i < n; i += nt) {
     A acc = to_acc<TI>(slots[0][i]);

@@ -321,7 +321,14 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   // have left the previous launch (it signals this barrier only after starting this one).
   if (fused && (is_mover || p.mode == kGemmReduceScatter)) dev::block_barrier(proto);
 
-  const int tiles_m = (p.rows_per_rank + BM - 1) / BM;
+  // Tall tiles (plain mode only): MT = 2 accumulators of 128 rows share one B tile; the ring
+  // then holds 3 stages of 64 KB (A 32 KB + B 32 KB) instead of 4 of 48 KB.
+  const int MT = (p.mode == kGemmPlain && p.tall) ? 2 : 1;
+  const int TM = BM * MT;                                   // rows of a tile
+  const int n_stages = MT == 2 ? 3 : STAGES;
+  const int a_bytes = A_BYTES * MT;
+  const size_t stage_bytes = MT == 2 ? (size_t)(2 * A_BYTES + B_BYTES) : (size_t)STAGE_BYTES;
+  const int tiles_m = (p.rows_per_rank + TM - 1) / TM;
   const int BN = p.bn;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int shards = (p.mode == kGemmPlain || n == 1) ? 1 : n;
@@ -358,16 +365,16 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           fence_proxy_async();  // peers' stores -> my TMA reads
         }
         const CUtensorMap* ma = (p.mode == kGemmAllGather && fused && !remote) ? map_a_local : map_a;
-        int row0 = tl.m_in * BM + ((p.mode == kGemmAllGather && fused && !remote) ? 0 : tl.shard * p.rows_per_rank);
+        int row0 = tl.m_in * TM + ((p.mode == kGemmAllGather && fused && !remote) ? 0 : tl.shard * p.rows_per_rank);
         for (int kb = wk.kb0; kb < wk.kb1 && ok; ++kb) {
           ok = mbar_wait(&ctl->empty[stage], phase ^ 1u, p.coll.timeout_ns, abort);
           if (!ok) break;
-          mbar_expect_tx(&ctl->full[stage], (uint32_t)(A_BYTES + BN * BK * 2));
-          tma_load_2d(ring + (size_t)stage * STAGE_BYTES, ma, &ctl->full[stage], kb * BK, row0);
-          tma_load_2d(ring + (size_t)stage * STAGE_BYTES + A_BYTES, map_b, &ctl->full[stage], kb * BK, tl.n_blk * BN);
+          mbar_expect_tx(&ctl->full[stage], (uint32_t)(a_bytes + BN * BK * 2));
+          tma_load_2d(ring + (size_t)stage * stage_bytes, ma, &ctl->full[stage], kb * BK, row0);  // box of TM rows
+          tma_load_2d(ring + (size_t)stage * stage_bytes + a_bytes, map_b, &ctl->full[stage], kb * BK, tl.n_blk * BN);
           issued |= 1u << stage;
           issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
-          if (++stage == STAGES) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -392,8 +399,9 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       bool ok = true;
       for (; it < n_items && ok; ++it) {
         const Work wk = work_of(it, g, G, total_tiles, S, num_kb);
-        const int buf = it & 1;
-        const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+        // one accumulator per tile and two buffers in turn, or (tall) both used by one tile
+        const int buf = MT == 2 ? 0 : (it & 1);
+        const uint32_t acc_phase = MT == 2 ? ((uint32_t)it & 1u) : ((uint32_t)(it >> 1) & 1u);
         ok = mbar_wait(&ctl->tempty[buf], acc_phase ^ 1u, p.coll.timeout_ns, abort);
         if (!ok) break;
         tc_fence_after_sync();
@@ -402,15 +410,18 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           ok = mbar_wait(&ctl->full[stage], phase, p.coll.timeout_ns, abort);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint64_t da = make_smem_desc_sw128(ring + (size_t)stage * STAGE_BYTES);
-          const uint64_t db = make_smem_desc_sw128(ring + (size_t)stage * STAGE_BYTES + A_BYTES);
+          const uint64_t da = make_smem_desc_sw128(ring + (size_t)stage * stage_bytes);
+          const uint64_t da2 = make_smem_desc_sw128(ring + (size_t)stage * stage_bytes + A_BYTES);
+          const uint64_t db = make_smem_desc_sw128(ring + (size_t)stage * stage_bytes + a_bytes);
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             // 16 bf16 = 32 bytes further along K inside the 128-byte swizzled row
-            tc_mma_f16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb > wk.kb0 || kk) ? 1u : 0u);
+            const uint32_t acc = (kb > wk.kb0 || kk) ? 1u : 0u;
+            tc_mma_f16(d_tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, acc);
+            if (MT == 2) tc_mma_f16(d_tmem + (uint32_t)BN_MAX, da2 + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, acc);
           }
           tc_commit(&ctl->empty[stage]);  // frees the stage when these MMAs have read it
-          if (++stage == STAGES) {
+          if (++stage == n_stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -426,8 +437,8 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
     for (; it < n_items && ok; ++it) {
       const Work wk = work_of(it, g, G, total_tiles, S, num_kb);
       Tile tl = tile_of(p, wk.t, tiles_m, tiles_n);
-      const int buf = it & 1;
-      const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+      const int buf = MT == 2 ? 0 : (it & 1);
+      const uint32_t acc_phase = MT == 2 ? ((uint32_t)it & 1u) : ((uint32_t)(it >> 1) & 1u);
       ok = mbar_wait(&ctl->tfull[buf], acc_phase, p.coll.timeout_ns, abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -476,27 +487,30 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       } else if (wk.slice >= 0) {
         // Slice of a tail tile: park the fp32 accumulator, meet the tile's other slices, then
         // sum one band of its rows over all slices (in slice order) and store that band.
-        // A parked tile is laid out [band][4-column group][row in band, padded to an odd
-        // count][4 floats]: a band of one slice is one contiguous piece, fetched with a single
-        // bulk copy into the (now idle) operand ring, so every slice's band is in flight at
-        // once; the odd row count keeps the shared-memory reads that follow free of conflicts.
+        // A parked accumulator (one per 128-row half of the tile) is laid out [band][4-column
+        // group][row in band, padded to an odd count][4 floats]: a band of one slice is one
+        // contiguous piece, fetched with bulk copies into the (now idle) operand ring, so every
+        // slice's band is in flight at once; the odd row count keeps the shared-memory reads that
+        // follow free of bank conflicts.
         const int j = wk.t - (total_tiles / G) * G;
-        const size_t part_elems = SK_SLOT_FLOATS;  // one parked tile, padding included
+        const size_t part_elems = SK_SLOT_FLOATS;  // one parked accumulator, padding included
         const int groups = BN / 4;
         const int rows_per = (BM + S - 1) / S, rows_pad = rows_per | 1;
         const size_t band_vecs = (size_t)groups * rows_pad;
-        float4* mine = (float4*)(p.sk_ws + ((size_t)j * S + wk.slice) * part_elems);
         const int row = lane_grp * 32 + lane;
-        float4* my_row = mine + (size_t)(row / rows_per) * band_vecs + (row % rows_per);
+        for (int h = 0; h < MT; ++h) {
+          float4* mine = (float4*)(p.sk_ws + (((size_t)j * S + wk.slice) * MT + h) * part_elems);
+          float4* my_row = mine + (size_t)(row / rows_per) * band_vecs + (row % rows_per);
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
-          tmem_ld_wait();
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_row + (uint32_t)(h * BN_MAX + c * 32), v);
+            tmem_ld_wait();
 #pragma unroll
-          for (int q = 0; q < 8; ++q)
-            my_row[(size_t)(c * 8 + q) * rows_pad] =
-                make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            for (int q = 0; q < 8; ++q)
+              my_row[(size_t)(c * 8 + q) * rows_pad] =
+                  make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+          }
         }
         tc_fence_before_sync();
         __syncwarp();
@@ -513,24 +527,20 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
             *abort = 1;
           }
           __threadfence();
-          if (!*abort && r1 > r0) {
-            // every MMA of this CTA has completed (the accumulator was read above) and the
-            // producer has nothing in flight: the ring is free
+        }
+        for (int h = 0; h < MT; ++h) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // the ring is free: MMAs done (h = 0), sums of the first half done (h = 1)
+          if (warp == 2 && lane == 0 && !*abort && r1 > r0) {
             fence_proxy_async();
             mbar_expect_tx(&ctl->copy_full[0], band_bytes * (uint32_t)S);
             for (int s2 = 0; s2 < S; ++s2) {
-              const char* src = (const char*)(p.sk_ws + ((size_t)j * S + s2) * part_elems + (size_t)wk.slice * band_vecs * 4);
-              // pieces of at most 32 KB: one copy of more than 64 KB delivered wrong bytes at
-              // both ends of its destination
+              const char* src = (const char*)(p.sk_ws + (((size_t)j * S + s2) * MT + h) * part_elems + (size_t)wk.slice * band_vecs * 4);
               for (uint32_t o = 0; o < band_bytes; o += COPY_PIECE)
                 bulk_g2s(ring + (size_t)s2 * band_bytes + o, src + o, min((uint32_t)COPY_PIECE, band_bytes - o), &ctl->copy_full[0]);
             }
           }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (!*abort && r1 > r0) {
-          bool got = mbar_wait(&ctl->copy_full[0], 0u, p.coll.timeout_ns, abort);
-          if (got) {
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (!*abort && r1 > r0 && mbar_wait(&ctl->copy_full[0], (uint32_t)h & 1u, p.coll.timeout_ns, abort)) {
             const float4* sm = (const float4*)ring;
             const int total = (r1 - r0) * groups;
             for (int e = row; e < total; e += 128) {
@@ -541,12 +551,12 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
                 const float4 x = sp[(size_t)s2 * band_vecs];
                 acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
               }
-              const int grow = tl.m_in * BM + r0 + rr, gcol = tl.n_blk * BN + c4 * 4;
+              const int grow = tl.m_in * TM + h * BM + r0 + rr, gcol = tl.n_blk * BN + c4 * 4;
               if (grow < p.rows_per_rank && gcol < p.N) {
-                alignas(8) __nv_bfloat162 h[2];
-                h[0] = __floats2bfloat162_rn(acc.x, acc.y);
-                h[1] = __floats2bfloat162_rn(acc.z, acc.w);
-                *(uint2*)((__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + grow) * p.ldc + gcol) = *(const uint2*)h;
+                alignas(8) __nv_bfloat162 hh[2];
+                hh[0] = __floats2bfloat162_rn(acc.x, acc.y);
+                hh[1] = __floats2bfloat162_rn(acc.z, acc.w);
+                *(uint2*)((__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + grow) * p.ldc + gcol) = *(const uint2*)hh;
               }
             }
           }
@@ -561,24 +571,26 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           }
         }
       } else {
-        const int row_in = tl.m_in * BM + lane_grp * 32 + lane;  // row inside the shard
-        const bool row_ok = row_in < p.rows_per_rank;
-        __nv_bfloat16* dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * p.ldc;
+        for (int h = 0; h < MT; ++h) {
+          const int row_in = tl.m_in * TM + h * BM + lane_grp * 32 + lane;  // row inside the shard
+          const bool row_ok = row_in < p.rows_per_rank;
+          __nv_bfloat16* dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * p.ldc;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);
-          tmem_ld_wait();
-          const int col = tl.n_blk * BN + c * 32;
-          if (row_ok) {
+          for (int c = 0; c < BN / 32; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(t_row + (uint32_t)(h * BN_MAX + c * 32), v);
+            tmem_ld_wait();
+            const int col = tl.n_blk * BN + c * 32;
+            if (row_ok) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              if (col + j * 8 < p.N) {
-                alignas(16) __nv_bfloat162 h[4];
+              for (int j = 0; j < 4; ++j) {
+                if (col + j * 8 < p.N) {
+                  alignas(16) __nv_bfloat162 h2[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  h[q] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]), __uint_as_float(v[j * 8 + 2 * q + 1]));
-                *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h;
+                  for (int q = 0; q < 4; ++q)
+                    h2[q] = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2 * q]), __uint_as_float(v[j * 8 + 2 * q + 1]));
+                  *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h2;
+                }
               }
             }
           }
@@ -689,7 +701,7 @@ int gemm_tail_slices(long tiles, int ctas, int k_blocks) {
   return tail < 0.75 ? (int)s : 1;
 }
 
-size_t gemm_splitk_ws_bytes(int ctas) { return (size_t)ctas * gemmk::SK_SLOT_FLOATS * sizeof(float); }
+size_t gemm_splitk_ws_bytes(int ctas) { return (size_t)ctas * 2 * gemmk::SK_SLOT_FLOATS * sizeof(float); }  // two halves of a tall tile
 size_t gemm_splitk_ctr_words(int ctas) { return (size_t)2 * ctas; }
 
 int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks, int* slices) {
@@ -711,6 +723,23 @@ int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks, int* slices) {
   }
   if (slices) *slices = best_s;
   return best;
+}
+
+// Cost of a tiling in units of "one K block of a 128-row tile's main loop": waves x (K blocks
+// + exposed epilogue), with the partly filled last wave priced as in gemm_pick_bn.
+static double tiling_cost(int row_tiles, int N, int bn, int slices, int k_blocks, int ctas, double per_block, double epilogue) {
+  long tiles = (long)row_tiles * ((N + bn - 1) / bn);
+  long full = tiles / ctas, rem = tiles % ctas;
+  double tail = rem == 0 ? 0.0 : (slices > 1 ? 1.0 / slices + splitk_fixup_blocks() / k_blocks : 1.0);
+  return ((double)full + tail) * ((double)k_blocks * per_block + epilogue);
+}
+
+bool gemm_tall_pays(int M, int N, int k_blocks, int ctas, int bn_flat, int slices_flat, int bn_tall, int slices_tall) {
+  // a tall tile does twice the work per K block in 1.5x the time of a flat one (its main loop is
+  // bound by the tensor pipe, the flat one by filling shared memory) and exposes its epilogue
+  const double flat = tiling_cost((M + kGemmBM - 1) / kGemmBM, N, bn_flat, slices_flat, k_blocks, ctas, 1.0, 0.0);
+  const double tall = tiling_cost((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, bn_tall, slices_tall, k_blocks, ctas, 1.5, 12.0);
+  return tall < flat;
 }
 
 int gemm_default_grid(int device) {

@@ -29,6 +29,8 @@ struct FusedFlags {
 struct GemmParams {
   int M, N, K;              // problem of this rank (M = all rows, gathered or to be scattered)
   int bn;                   // tile width in columns: multiple of 32, <= kGemmBN (see gemm_pick_bn)
+  int tall;                 // plain mode: 1 = tiles of 256 rows (two accumulators side by side in TMEM, one B tile
+                            // feeds both: a third less shared-memory fill per FLOP; the epilogue is then not overlapped)
   int mode;
   void* C;                  // plain / all-gather: bf16 [M, N] row-major, leading dimension ldc
   int ldc;
@@ -69,6 +71,8 @@ int gemm_default_grid(int device);
 // `k_blocks` > 0 the last wave may be split along K (see GemmParams::sk_slices): its cost is
 // then 1/slices of a wave plus the fix-up, and *slices receives the split to use (1 = none).
 int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks = 0, int* slices = nullptr);
+// Whether 256-row tiles (GemmParams::tall) are expected to beat 128-row tiles for this problem.
+bool gemm_tall_pays(int M, int N, int k_blocks, int ctas, int bn_flat, int slices_flat, int bn_tall, int slices_tall);
 // Slices of the tail split for a given tiling, 1 when splitting does not pay.
 int gemm_tail_slices(long tiles, int ctas, int k_blocks);
 // Bytes of split-K workspace / number of counters that a launch on `ctas` CTAs may touch.

@@ -27,6 +27,8 @@ class VmmBackend {
   virtual Status granularity(int dev, size_t* out) = 0;
   virtual Status mem_info(int dev, size_t* free_bytes, size_t* total_bytes) = 0;
   virtual Status device_sync(int dev) = 0;
+  // Called once by a helper thread before it makes memory-management calls for device `dev`.
+  virtual Status thread_init(int dev) { (void)dev; return kSuccess; }
 
   // Virtual address ranges.  A reserved range stays reserved across pause/resume.
   virtual Status reserve(size_t size, size_t align, uint64_t* va) = 0;

@@ -169,6 +169,10 @@ class CudaBackend : public VmmBackend {
     RT(e, "cudaMemGetInfo");
     return kSuccess;
   }
+  Status thread_init(int dev) override {
+    RT(cudaSetDevice(dev), "cudaSetDevice");  // binds the device's primary context to this thread
+    return kSuccess;
+  }
   Status device_sync(int dev) override {
     int cur = 0;
     RT(cudaGetDevice(&cur), "cudaGetDevice");

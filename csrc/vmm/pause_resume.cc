@@ -125,7 +125,8 @@ Status pause_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, PeerE
     std::vector<JobResult> res(peers.size());
     parallel_each(peers.size(), [&](size_t i) {
       Allocation& a = *peers[i];
-      Status s = be->unmap(a.va, a.size);
+      Status s = i ? be->thread_init(dev) : kSuccess;
+      if (s == kSuccess) s = be->unmap(a.va, a.size);
       if (s == kSuccess) s = be->release(a.handle);
       res[i].st = s;
       if (s != kSuccess) res[i].err = last_error_slot();
@@ -280,7 +281,8 @@ Status resume_scope(Registry& reg, VmmBackend* be, uint64_t owner, int dev, Peer
       parallel_each(holes.size(), [&](size_t i) {
         Allocation& a = *holes[i];
         uint64_t h = 0;
-        Status s = be->import_fd(fds[i], a.size, &h);
+        Status s = i ? be->thread_init(dev) : kSuccess;
+        if (s == kSuccess) s = be->import_fd(fds[i], a.size, &h);
         close(fds[i]);
         if (s == kSuccess) {
           s = be->map(a.va, a.size, h, a.dev);

@@ -12,8 +12,18 @@ def _rand(shape, seed, scale=1.0):
     return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16)
 
 
+@pytest.fixture(params=["0", "1"], ids=["tiles128", "tiles256"])
+def tile_height(request):
+    """Forces the 128-row or the 256-row tile form of the plain GEMM (the library reads the
+    variable at every call); without it the library picks by its cost model."""
+    import os
+    os.environ["AMEM_GEMM_TALL"] = request.param
+    yield request.param
+    os.environ.pop("AMEM_GEMM_TALL", None)
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (256, 512, 1024), (1000, 264, 328), (4096, 4096, 4096), (77, 8, 8)])
-def test_gemm_bf16_matches_fp32_reference(M, N, K):
+def test_gemm_bf16_matches_fp32_reference(M, N, K, tile_height):
     from asystem_amem_b200.ops import gemm_bf16
     a, b = _rand((M, K), 1).cuda(), _rand((N, K), 2).cuda()
     out = gemm_bf16(a, b)
@@ -29,7 +39,7 @@ def test_gemm_bf16_matches_fp32_reference(M, N, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 512, 4096), (1000, 264, 8192), (1000, 264, 2048), (4096, 4096, 4096), (8192, 3584, 8192), (520, 776, 4096)])
-def test_gemm_split_k_tail(M, N, K):
+def test_gemm_split_k_tail(M, N, K, tile_height):
     """Shapes whose last wave of tiles is cut along K: partial accumulators meet in the
     workspace, the sum is taken in slice order, so repeated calls agree bit for bit, on the
     same stream and on a second one (which gets a workspace of its own)."""
