@@ -130,7 +130,7 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   // Tile height: 256-row tiles feed two accumulators from one B tile (less shared-memory fill
   // per FLOP, the limit of the 128-row main loop) but their epilogue is not hidden behind the
   // next tile, so they pay only with a long K.  AMEM_GEMM_TALL = 0 / 1 forces, -1 decides.
-  const long tall_env = env_long("AMEM_GEMM_TALL", 0);  // off until its cost model has been calibrated
+  const long tall_env = env_long("AMEM_GEMM_TALL", -1);
   int slices = 1, slices_tall = 1;
   const int bn_flat = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms, ws ? k_blocks : 0, &slices);
   const int bn_tall = gemm_pick_bn((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, sms, ws ? k_blocks : 0, &slices_tall);

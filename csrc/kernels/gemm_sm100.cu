@@ -278,6 +278,7 @@ __device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas,
 }
 
 // ---- the kernel body, shared by the one-rank-per-GPU kernel and the emulation kernel -------
+template <int MT>  // accumulators (128-row halves) per tile: 1, or 2 for the tall tiles of the plain mode
 __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const CUtensorMap* map_a_local, const CUtensorMap* map_b,
                           int cta, int nctas, char* smem_raw) {
   // operand ring first (1024-byte aligned for the 128-byte swizzle), control words after it
@@ -323,11 +324,10 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
 
   // Tall tiles (plain mode only): MT = 2 accumulators of 128 rows share one B tile; the ring
   // then holds 3 stages of 64 KB (A 32 KB + B 32 KB) instead of 4 of 48 KB.
-  const int MT = (p.mode == kGemmPlain && p.tall) ? 2 : 1;
-  const int TM = BM * MT;                                   // rows of a tile
-  const int n_stages = MT == 2 ? 3 : STAGES;
-  const int a_bytes = A_BYTES * MT;
-  const size_t stage_bytes = MT == 2 ? (size_t)(2 * A_BYTES + B_BYTES) : (size_t)STAGE_BYTES;
+  constexpr int TM = BM * MT;                                   // rows of a tile
+  constexpr int n_stages = MT == 2 ? 3 : STAGES;
+  constexpr int a_bytes = A_BYTES * MT;
+  constexpr size_t stage_bytes = MT == 2 ? (size_t)(2 * A_BYTES + B_BYTES) : (size_t)STAGE_BYTES;
   const int tiles_m = (p.rows_per_rank + TM - 1) / TM;
   const int BN = p.bn;
   const int tiles_n = (p.N + BN - 1) / BN;
@@ -629,11 +629,12 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   }
 }
 
+template <int MT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
             const __grid_constant__ CUtensorMap map_a_local, const __grid_constant__ CUtensorMap map_b) {
   extern __shared__ char smem_raw[];
-  gemm_body(p, &map_a, &map_a_local, &map_b, blockIdx.x, gridDim.x, smem_raw);
+  gemm_body<MT>(p, &map_a, &map_a_local, &map_b, blockIdx.x, gridDim.x, smem_raw);
 }
 
 struct EmuGemmParams {
@@ -642,7 +643,7 @@ struct EmuGemmParams {
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel_emu(const __grid_constant__ EmuGemmParams all) {
   extern __shared__ char smem_raw[];
   const GemmLaunch& g = all.rank[blockIdx.y];
-  gemm_body(g.p, &g.map_a, &g.map_a_local, &g.map_b, blockIdx.x, gridDim.x, smem_raw);
+  gemm_body<1>(g.p, &g.map_a, &g.map_a_local, &g.map_b, blockIdx.x, gridDim.x, smem_raw);
 }
 
 }  // namespace gemmk
@@ -735,10 +736,11 @@ static double tiling_cost(int row_tiles, int N, int bn, int slices, int k_blocks
 }
 
 bool gemm_tall_pays(int M, int N, int k_blocks, int ctas, int bn_flat, int slices_flat, int bn_tall, int slices_tall) {
-  // a tall tile does twice the work per K block in 1.5x the time of a flat one (its main loop is
-  // bound by the tensor pipe, the flat one by filling shared memory) and exposes its epilogue
+  // measured (8192^3 and 4096^3, both forms in one run): a tall tile does twice the work per K
+  // block in about 1.65x the time of a flat one (its main loop is bound by the tensor pipe, the
+  // flat one by filling shared memory) and exposes an epilogue worth about 17 flat K blocks
   const double flat = tiling_cost((M + kGemmBM - 1) / kGemmBM, N, bn_flat, slices_flat, k_blocks, ctas, 1.0, 0.0);
-  const double tall = tiling_cost((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, bn_tall, slices_tall, k_blocks, ctas, 1.5, 12.0);
+  const double tall = tiling_cost((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, bn_tall, slices_tall, k_blocks, ctas, 1.65, 17.0);
   return tall < flat;
 }
 
@@ -755,9 +757,12 @@ static Status prepare_kernel(const void* fn) {
 }
 
 Status launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
-  static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel);
-  if (ready != kSuccess) return ready;
-  gemmk::gemm_kernel<<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
+  static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel<1>);
+  static Status ready_tall = prepare_kernel((const void*)gemmk::gemm_kernel<2>);
+  const bool tall = g.p.mode == kGemmPlain && g.p.tall;
+  if ((tall ? ready_tall : ready) != kSuccess) return tall ? ready_tall : ready;
+  if (tall) gemmk::gemm_kernel<2><<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
+  else gemmk::gemm_kernel<1><<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(kCudaError, "gemm launch failed: %s", cudaGetErrorString(e));
   return kSuccess;
