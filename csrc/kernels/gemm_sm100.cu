@@ -298,7 +298,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&ctl->tfull[b], 1);
-      mbar_init(&ctl->tempty[b], 4);
+      mbar_init(&ctl->tempty[b], 4 * MT);  // one arrival per epilogue warp
     }
     ctl->abort = 0;
     mbar_fence_init();
@@ -432,6 +432,9 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int lane_grp = warp % 4;  // TMEM lanes [32 * lane_grp, +32) belong to this warp
+    // tall tiles: eight epilogue warps, warps 2-5 drain the first accumulator, 6-9 the second
+    const int my_h = MT == 2 ? (warp - 2) / 4 : 0;
+    constexpr int EPI_THREADS = 128 * MT;
     int it = 0;
     bool ok = true;
     for (; it < n_items && ok; ++it) {
@@ -498,7 +501,8 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         const int rows_per = (BM + S - 1) / S, rows_pad = rows_per | 1;
         const size_t band_vecs = (size_t)groups * rows_pad;
         const int row = lane_grp * 32 + lane;
-        for (int h = 0; h < MT; ++h) {
+        {
+          const int h = my_h;
           float4* mine = (float4*)(p.sk_ws + (((size_t)j * S + wk.slice) * MT + h) * part_elems);
           float4* my_row = mine + (size_t)(row / rows_per) * band_vecs + (row % rows_per);
 #pragma unroll 1
@@ -516,7 +520,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         uint32_t* ctr = p.sk_ctr + 2 * j;
         const int r0 = wk.slice * rows_per, r1 = min(BM, r0 + rows_per);
         const uint32_t band_bytes = (uint32_t)(band_vecs * sizeof(float4));
@@ -529,7 +533,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           __threadfence();
         }
         for (int h = 0; h < MT; ++h) {
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // the ring is free: MMAs done (h = 0), sums of the first half done (h = 1)
+          asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // the ring is free: MMAs done (h = 0), sums of the first half done (h = 1)
           if (warp == 2 && lane == 0 && !*abort && r1 > r0) {
             fence_proxy_async();
             mbar_expect_tx(&ctl->copy_full[0], band_bytes * (uint32_t)S);
@@ -539,11 +543,11 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
                 bulk_g2s(ring + (size_t)s2 * band_bytes + o, src + o, min((uint32_t)COPY_PIECE, band_bytes - o), &ctl->copy_full[0]);
             }
           }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
+          asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
           if (!*abort && r1 > r0 && mbar_wait(&ctl->copy_full[0], (uint32_t)h & 1u, p.coll.timeout_ns, abort)) {
             const float4* sm = (const float4*)ring;
             const int total = (r1 - r0) * groups;
-            for (int e = row; e < total; e += 128) {
+            for (int e = my_h * 128 + row; e < total; e += EPI_THREADS) {
               const int rr = e / groups, c4 = e % groups;
               const float4* sp = sm + (size_t)c4 * rows_pad + rr;
               float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -561,7 +565,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
             }
           }
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
         if (warp == 2 && lane == 0) {
           __threadfence();
           if (atomicAdd(ctr + 1, 1u) == (uint32_t)S - 1u) {  // last reader: leave the counters at zero
@@ -571,15 +575,14 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           }
         }
       } else {
-        for (int h = 0; h < MT; ++h) {
+        {
+          const int h = my_h;
           const int row_in = tl.m_in * TM + h * BM + lane_grp * 32 + lane;  // row inside the shard
           const bool row_ok = row_in < p.rows_per_rank;
           __nv_bfloat16* dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * p.ldc;
-#pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(t_row + (uint32_t)(h * BN_MAX + c * 32), v);
-            tmem_ld_wait();
+          // two register buffers: the TMEM load of the next 32 columns is in flight while the
+          // current ones are converted and stored
+          auto store_chunk = [&](const uint32_t* v, int c) {
             const int col = tl.n_blk * BN + c * 32;
             if (row_ok) {
 #pragma unroll
@@ -592,6 +595,21 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
                   *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h2;
                 }
               }
+            }
+          };
+          const uint32_t t_half = t_row + (uint32_t)(h * BN_MAX);
+          const int nchunks = BN / 32;
+          uint32_t va[32], vb[32];
+          tmem_ld_32x32(t_half, va);
+#pragma unroll 1
+          for (int c = 0; c < nchunks; c += 2) {
+            tmem_ld_wait();
+            if (c + 1 < nchunks) tmem_ld_32x32(t_half + (uint32_t)((c + 1) * 32), vb);
+            store_chunk(va, c);
+            if (c + 1 < nchunks) {
+              tmem_ld_wait();
+              if (c + 2 < nchunks) tmem_ld_32x32(t_half + (uint32_t)((c + 2) * 32), va);
+              store_chunk(vb, c + 1);
             }
           }
         }
@@ -630,7 +648,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
 }
 
 template <int MT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(64 + 128 * MT, 1)  // TMA warp, MMA warp, 4 * MT epilogue warps
 gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
             const __grid_constant__ CUtensorMap map_a_local, const __grid_constant__ CUtensorMap map_b) {
   extern __shared__ char smem_raw[];
@@ -761,7 +779,7 @@ Status launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   static Status ready_tall = prepare_kernel((const void*)gemmk::gemm_kernel<2>);
   const bool tall = g.p.mode == kGemmPlain && g.p.tall;
   if ((tall ? ready_tall : ready) != kSuccess) return tall ? ready_tall : ready;
-  if (tall) gemmk::gemm_kernel<2><<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
+  if (tall) gemmk::gemm_kernel<2><<<g.grid, 64 + 128 * 2, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
   else gemmk::gemm_kernel<1><<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(kCudaError, "gemm launch failed: %s", cudaGetErrorString(e));
