@@ -126,6 +126,7 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "amemMoeDispatch": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "amemMoeCombine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "amemGemmBf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "amemGemmPlan": [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],
         "amemAllGatherGemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
         "amemGemmReduceScatter": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     }

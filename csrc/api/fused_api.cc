@@ -81,9 +81,44 @@ SplitKWs* splitk_workspace(int dev, cudaStream_t stream, int ctas) {
   auto ins = all.emplace(key, w);
   return ins.first->second.partials ? &ins.first->second : nullptr;
 }
+
+// Tiling of the plain GEMM for one problem: tile width, tile height, split of the last wave.
+struct GemmPlan {
+  int bn, tall, slices;
+};
+GemmPlan plan_gemm(int M, int N, int K, int sms, bool can_split) {
+  const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
+  // Tile height: 256-row tiles feed two accumulators from one B tile (less shared-memory fill
+  // per FLOP, the limit of the 128-row main loop) but their epilogue is not hidden behind the
+  // next tile, so they pay only with a long K.  AMEM_GEMM_TALL = 0 / 1 forces, -1 decides.
+  const long tall_env = env_long("AMEM_GEMM_TALL", -1);
+  int slices = 1, slices_tall = 1;
+  const int bn_flat = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms, can_split ? k_blocks : 0, &slices);
+  const int bn_tall = gemm_pick_bn((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, sms, can_split ? k_blocks : 0, &slices_tall);
+  bool tall = tall_env >= 0 ? tall_env != 0 : gemm_tall_pays(M, N, k_blocks, sms, bn_flat, slices, bn_tall, slices_tall);
+  if (M <= kGemmBM) tall = false;
+  GemmPlan p;
+  p.tall = tall ? 1 : 0;
+  p.bn = tall ? bn_tall : bn_flat;
+  p.slices = tall ? slices_tall : slices;
+  return p;
+}
 }  // namespace
 
 extern "C" {
+
+// The tiling amemGemmBf16 would use on a GPU with `sms` SMs (no GPU needed: planning is host
+// arithmetic).  Outputs may be null.
+ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices) {
+  Status s = check_shape(M, N, K);
+  if (s != kSuccess) return R(s);
+  if (sms <= 0) return R(fail(kInvalidArgument, "amemGemmPlan: sms must be positive"));
+  GemmPlan p = plan_gemm(M, N, K, sms, env_long("AMEM_GEMM_SPLITK", 1) != 0);
+  if (tile_rows) *tile_rows = p.tall ? 2 * kGemmBM : kGemmBM;
+  if (tile_cols) *tile_cols = p.bn;
+  if (tail_slices) *tail_slices = p.slices;
+  return ncclSuccess;
+}
 
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
   Status s = check_shape(M, N, K);
@@ -126,19 +161,11 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   // already has one (allocation is not allowed there).  AMEM_GEMM_SPLITK=0 turns the split off.
   const long splitk_on = env_long("AMEM_GEMM_SPLITK", 1);  // read per call: benches flip it
   SplitKWs* ws = splitk_on ? splitk_workspace(dev, stream, sms) : nullptr;
-  const int k_blocks = (K + kGemmBK - 1) / kGemmBK;
-  // Tile height: 256-row tiles feed two accumulators from one B tile (less shared-memory fill
-  // per FLOP, the limit of the 128-row main loop) but their epilogue is not hidden behind the
-  // next tile, so they pay only with a long K.  AMEM_GEMM_TALL = 0 / 1 forces, -1 decides.
-  const long tall_env = env_long("AMEM_GEMM_TALL", -1);
-  int slices = 1, slices_tall = 1;
-  const int bn_flat = gemm_pick_bn((M + kGemmBM - 1) / kGemmBM, N, sms, ws ? k_blocks : 0, &slices);
-  const int bn_tall = gemm_pick_bn((M + 2 * kGemmBM - 1) / (2 * kGemmBM), N, sms, ws ? k_blocks : 0, &slices_tall);
-  bool tall = tall_env >= 0 ? tall_env != 0 : gemm_tall_pays(M, N, k_blocks, sms, bn_flat, slices, bn_tall, slices_tall);
-  if (M <= kGemmBM) tall = false;
-  g.p.tall = tall ? 1 : 0;
-  g.p.bn = tall ? bn_tall : bn_flat;
-  if (tall) slices = slices_tall;
+  GemmPlan plan = plan_gemm(M, N, K, sms, ws != nullptr);
+  const bool tall = plan.tall != 0;
+  int slices = plan.slices;
+  g.p.tall = plan.tall;
+  g.p.bn = plan.bn;
   const int tile_rows = tall ? 2 * kGemmBM : kGemmBM;
   if ((s = make_tensor_map_bf16(&g.map_a, A, M, K, K, tile_rows)) != kSuccess) return R(s);
   g.map_a_local = g.map_a;

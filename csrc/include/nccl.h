@@ -203,6 +203,9 @@ ncclResult_t amemAllReduceAlgo(const void* sendbuff, void* recvbuff, size_t coun
  * row-major with K contiguous, the layout of activations and of Linear weights).  N and K must
  * be multiples of 8. */
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream);
+/* The tiling amemGemmBf16 picks for a problem on a GPU with `sms` SMs: tile rows (128 or 256), tile
+ * columns, K-slices of the last wave (1 = not split).  Host arithmetic only; outputs may be NULL. */
+ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices);
 /* One kernel: C[M,N] = allgather_rows(a_shard)[M,K] * B[N,K]^T.  a_shard holds this rank's
  * M/nranks rows; the transfer of the other ranks' rows overlaps the tensor-core work. */
 ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int M, int N, int K, ncclComm_t comm, cudaStream_t stream);

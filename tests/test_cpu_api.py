@@ -95,3 +95,38 @@ def test_comm_init_all_in_one_process():
     th = [threading.Thread(target=lambda i=i: lib.ncclCommDestroy(comms[i])) for i in range(n)]
     [t.start() for t in th]
     [t.join(60) for t in th]
+
+
+def test_gemm_planner_picks_tile_form_and_tail_split():
+    """The GEMM's tiling is host arithmetic: checked here for the shapes it was calibrated on
+    (148 SMs), without a GPU."""
+    os.environ["AMEM_BACKEND"] = "mock"
+    from asystem_amem_b200 import bindings as B
+    lib = B.load_library()
+
+    def plan(M, N, K, **env):
+        old = {k: os.environ.get(k) for k in env}
+        os.environ.update({k: str(v) for k, v in env.items()})
+        try:
+            r, c, s = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+            assert lib.amemGemmPlan(M, N, K, 148, ctypes.byref(r), ctypes.byref(c), ctypes.byref(s)) == 0
+            return r.value, c.value, s.value
+        finally:
+            for k, v in old.items():
+                os.environ.pop(k, None) if v is None else os.environ.__setitem__(k, v)
+
+    # tensor-parallel MLP shape: 256-row tiles, 448 tiles = 3 waves + 4 tiles cut into K-slices
+    rows, cols, slices = plan(8192, 3584, 8192)
+    assert (rows, cols) == (256, 256) and 4 <= slices <= 32
+    # forced 128-row tiles: 896 tiles = 6 waves + 8 tiles; min(148 // 8, 128 K blocks // 8) = 16 slices
+    assert plan(8192, 3584, 8192, AMEM_GEMM_TALL=0) == (128, 256, 16)
+    assert plan(8192, 3584, 8192, AMEM_GEMM_TALL=0, AMEM_GEMM_SPLITK=0)[2] == 1
+    # short K or few tiles: the exposed epilogue of the tall form does not pay
+    assert plan(2048, 2048, 2048)[0] == 128
+    assert plan(1024, 3584, 8192)[0] == 128
+    assert plan(64, 512, 4096)[0] == 128          # a single row block can never be tall
+    # tile width stays a multiple of 32 in [128, 256]; bad shapes are refused
+    for shape in [(4096, 4096, 4096), (1000, 264, 8192), (8192, 8192, 3584)]:
+        rows, cols, slices = plan(*shape)
+        assert rows in (128, 256) and 128 <= cols <= 256 and cols % 32 == 0 and 1 <= slices <= 32
+    assert lib.amemGemmPlan(128, 100, 64, 148, None, None, None) == 4   # N not a multiple of 8
