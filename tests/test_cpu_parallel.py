@@ -1,5 +1,6 @@
 """CPU (mock backend) tests of the parallel wrappers: sharded data parallel training on a tiny
 Llama decoder with a pause/resume between steps, and the pipeline-parallel forward schedule."""
+import pytest
 import torch
 
 from mp_util import run_ranks
@@ -105,3 +106,25 @@ def test_pipeline_forward_schedule():
     assert res[0] is None and res[1] is None
     # stage s computes 2x + s
     assert res[2] == [((2 * (i + 1) + 0) * 2 + 1) * 2 + 2 for i in range(3)]
+
+
+def _context_parallel(rank, world, uid, causal):
+    import torch
+    from asystem_amem_b200 import Communicator
+    from asystem_amem_b200.parallel.cp import _attend, ring_attention, ulysses_attention
+    comm = Communicator(world, rank, uid)
+    s_local, heads, dim = 24, 2 * world, 16
+    g = torch.Generator().manual_seed(3)
+    full = [torch.randn(world * s_local, heads, dim, generator=g) for _ in range(3)]
+    mine = [t[rank * s_local:(rank + 1) * s_local].contiguous() for t in full]
+    ref = _attend(*full, causal)[0][rank * s_local:(rank + 1) * s_local]
+    out_u = ulysses_attention(comm, *mine, causal=causal)
+    out_r = ring_attention(comm, *mine, causal=causal)
+    comm.destroy()
+    return float((out_u - ref).abs().max()), float((out_r - ref).abs().max())
+
+
+@pytest.mark.parametrize("world,causal", [(2, False), (3, True)])
+def test_context_parallel_attention_matches_full_attention(world, causal):
+    for err_ulysses, err_ring in run_ranks(_context_parallel, world, args=(causal,), timeout=300):
+        assert err_ulysses < 1e-5 and err_ring < 1e-5, (err_ulysses, err_ring)

@@ -96,3 +96,26 @@ def test_moe_layer_matches_dense_reference():
                 ref[t] += w[t, j] * (a @ w2[e].to(torch.bfloat16).t()).float()[0]
         torch.testing.assert_close(o1.float(), ref, rtol=5e-2, atol=2e-2)
         assert torch.equal(o1, o2)
+
+
+@pytest.mark.parametrize("world,causal", [(2, True), (4, False)])
+def test_context_parallel_attention_on_gpu(world, causal):
+    """Ulysses (all-to-all) and ring (send/recv) attention over sequence shards against attention
+    over the whole sequence, fp32."""
+    from asystem_amem_b200.parallel.cp import _attend, ring_attention, ulysses_attention
+    s_local, heads, dim = 64, 8, 32
+    g = torch.Generator().manual_seed(9)
+    full = [torch.randn(world * s_local, heads, dim, generator=g) for _ in range(3)]
+    ref = _attend(*full, causal)[0]
+
+    def fn(rank, world, comm, stream):
+        mine = [t[rank * s_local:(rank + 1) * s_local].contiguous().cuda() for t in full]
+        out_u = ulysses_attention(comm, *mine, causal=causal)
+        out_r = ring_attention(comm, *mine, causal=causal)
+        stream.synchronize()
+        return out_u.cpu(), out_r.cpu()
+
+    for rank, (out_u, out_r) in enumerate(run_emulated(world, fn)):
+        sl = slice(rank * s_local, (rank + 1) * s_local)
+        torch.testing.assert_close(out_u, ref[sl], rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(out_r, ref[sl], rtol=1e-4, atol=1e-4)
