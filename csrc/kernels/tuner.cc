@@ -84,7 +84,19 @@ LaunchPlan plan_collective(const TunerInput& in) {
   };
   switch (in.kind) {
     case kCollAllReduce:
-      if (p.algo == kAlgoNvls) p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, (H / 3) & ~(size_t)4095) / es;
+      if (p.algo == kAlgoNvls) {
+        // A message above 32 MiB goes in AMEM_NVLS_CHUNKS chunks (default 8) of at least
+        // AMEM_NVLS_CHUNK_MB (default 16): more, smaller chunks fill the three-stage pipeline
+        // sooner, but each chunk costs two rounds of credits.
+        static const long parts = std::max<long>(1, env_long("AMEM_NVLS_CHUNKS", 8));
+        static const long min_mb = std::max<long>(1, env_long("AMEM_NVLS_CHUNK_MB", 16));
+        const size_t total = in.count * es, lo = (size_t)min_mb << 20, cap = (H / 3) & ~(size_t)4095;
+        size_t c = total <= ((size_t)32 << 20) ? total : std::max(lo, total / (size_t)parts);
+        c = std::min(c, cap);
+        c = (c + 4095) & ~(size_t)4095;
+        if (c > cap) c = cap;
+        p.chunk_elems = std::max<size_t>(c, 4096) / es;
+      }
       else p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, (slot_bytes_of(H / 2, n)) * (size_t)n) / es;
       break;
     case kCollBroadcast: p.chunk_elems = Q / es; break;
