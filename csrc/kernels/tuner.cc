@@ -2,6 +2,7 @@
 // everything.  The thresholds were set from bus-bandwidth sweeps on 8 x B200 over NVSwitch;
 // AMEM_ALGO (oneshot|twoshot|nvls), AMEM_ONESHOT_MAX_KB and AMEM_BLOCKS override them.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "../core/log.h"
@@ -42,7 +43,10 @@ LaunchPlan plan_collective(const TunerInput& in) {
     // 1.7x the NVLS rate there, so NVLS is only picked by default from three ranks up.
     bool nvls_ok = in.nvls && n > 1 && (in.redop == kSum || in.redop == kAvg) &&
                    (in.dtype == kF32 || in.dtype == kBF16 || in.dtype == kF16);
-    size_t one_max = std::min(slot, (size_t)oneshot_kb << 10);
+    // Between two GPUs one-shot moves exactly the bytes two-shot does, with one barrier instead
+    // of two: measured faster up to 16 MiB (1 MiB: 27.6 vs 39.1 us; 8 MiB: 43.0 vs 52.6 us).
+    static const bool oneshot_set = getenv("AMEM_ONESHOT_MAX_KB") != nullptr;
+    size_t one_max = std::min(slot, (n == 2 && !oneshot_set) ? ((size_t)16 << 20) : ((size_t)oneshot_kb << 10));
     if (want == kAlgoNvls && !nvls_ok) want = kAlgoAuto;
     if (want == kAlgoOneShot && in.count * es > slot) want = kAlgoAuto;
     if (want == kAlgoAuto) {
@@ -72,10 +76,17 @@ LaunchPlan plan_collective(const TunerInput& in) {
   // coll_bodies.inl), so aim for about eight chunks, but never chunks so small that the
   // per-chunk barrier (a few microseconds) shows, nor larger than the staging region.
   const size_t H = 2 * Q;
-  // A chunk costs one cross-rank barrier (several microseconds over NVLink): messages up to
-  // `single_bytes` go as one chunk, larger ones in about eight chunks of at least `min_bytes`.
+  // A chunk of the credit pipeline costs about 12 us over its share of the transfer (measured
+  // between two GPUs: the two warp groups each run at half the block's memory parallelism), so
+  // chunks are as large as staging allows: messages up to `single_bytes` go as one chunk, larger
+  // ones in about eight chunks of at least `min_bytes`, never more than `max_bytes`.
+  // AMEM_SINGLE_MB / AMEM_CHUNK_MB / AMEM_CHUNKS override the three numbers (experiments).
+  static const long env_single_mb = env_long("AMEM_SINGLE_MB", 0), env_min_mb = env_long("AMEM_CHUNK_MB", 0);
+  static const long env_parts = std::max<long>(1, env_long("AMEM_CHUNKS", 8));
   auto pick = [&](size_t total_bytes, size_t single_bytes, size_t min_bytes, size_t max_bytes) {
-    size_t c = total_bytes <= single_bytes ? total_bytes : total_bytes / 8;
+    if (env_single_mb > 0) single_bytes = (size_t)env_single_mb << 20;
+    if (env_min_mb > 0) min_bytes = (size_t)env_min_mb << 20;
+    size_t c = total_bytes <= single_bytes ? total_bytes : total_bytes / (size_t)env_parts;
     if (total_bytes > single_bytes && c < min_bytes) c = min_bytes;
     if (c > max_bytes) c = max_bytes;
     c = (c + 4095) & ~(size_t)4095;
@@ -97,11 +108,11 @@ LaunchPlan plan_collective(const TunerInput& in) {
         if (c > cap) c = cap;
         p.chunk_elems = std::max<size_t>(c, 4096) / es;
       }
-      else p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, (slot_bytes_of(H / 2, n)) * (size_t)n) / es;
+      else p.chunk_elems = pick(in.count * es, 64u << 20, 32u << 20, (slot_bytes_of(H / 2, n)) * (size_t)n) / es;
       break;
     case kCollBroadcast: p.chunk_elems = Q / es; break;
     case kCollReduce: p.chunk_elems = slot / es; break;
-    default: p.chunk_elems = pick(in.count * es, 32u << 20, 16u << 20, slot) / es; break;  // per-rank bytes
+    default: p.chunk_elems = pick(in.count * es, 64u << 20, 32u << 20, slot) / es; break;  // per-rank bytes
   }
   if (p.chunk_elems == 0) p.chunk_elems = 1;
   return p;
