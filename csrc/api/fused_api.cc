@@ -123,22 +123,29 @@ ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* til
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
   Status s = check_shape(M, N, K);
   if (s != kSuccess) return R(s);
-  static thread_local uint32_t dummy_status[kStatusWords];
-  // A communicator-free launch still needs protocol words (epoch, operation counter): a small
-  // private control block per device.
+  // A communicator-free launch still needs protocol words (epoch, operation counter) and status
+  // words the host can read: one small block of each per device, made on first use.
+  static std::mutex init_mu;
   static CtrlBlock* ctrl[64] = {nullptr};
+  static uint32_t* status_dev[64] = {nullptr};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!ctrl[dev]) {
-    if (cudaMalloc((void**)&ctrl[dev], sizeof(CtrlBlock) + sizeof(FusedFlags)) != cudaSuccess) return ncclUnhandledCudaError;
-    cudaMemset(ctrl[dev], 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
+  if (dev < 0 || dev >= 64) return R(fail(kInvalidArgument, "device ordinal %d out of range", dev));
+  {
+    std::lock_guard<std::mutex> lk(init_mu);
+    if (!ctrl[dev]) {
+      CtrlBlock* c = nullptr;
+      if (cudaMalloc((void**)&c, sizeof(CtrlBlock) + sizeof(FusedFlags)) != cudaSuccess) return ncclUnhandledCudaError;
+      cudaMemset(c, 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
+      ctrl[dev] = c;
+    }
+    if (!status_dev[dev]) {
+      uint32_t* st = nullptr;
+      if (cudaHostAlloc((void**)&st, kStatusWords * 4, cudaHostAllocMapped) != cudaSuccess) return ncclUnhandledCudaError;
+      memset(st, 0, kStatusWords * 4);
+      status_dev[dev] = st;
+    }
   }
-  static uint32_t* status_dev[64] = {nullptr};
-  if (!status_dev[dev]) {
-    if (cudaHostAlloc((void**)&status_dev[dev], kStatusWords * 4, cudaHostAllocMapped) != cudaSuccess) return ncclUnhandledCudaError;
-    memset(status_dev[dev], 0, kStatusWords * 4);
-  }
-  (void)dummy_status;
   GemmLaunch g;
   memset(&g, 0, sizeof(g));
   g.p.M = M;
@@ -178,7 +185,11 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
     g.p.sk_ctr = ws->counters;
   }
   s = launch_gemm(g, stream);
-  if (s == kSuccess && status_dev[dev][0]) s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_dev[dev][0]);
+  if (s == kSuccess && status_dev[dev][0]) {
+    // an earlier launch gave up on a wait: its split-K counters may be left mid-count
+    if (ws) cudaMemsetAsync(ws->counters, 0, gemm_splitk_ctr_words(sms) * sizeof(uint32_t), stream);
+    s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_dev[dev][0]);
+  }
   return R(s);
 }
 
