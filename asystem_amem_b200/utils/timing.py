@@ -63,33 +63,84 @@ def load_measured_peaks(root: str | None = None) -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons every 200 ms while a timed region runs."""
+    """Samples SM clocks and clock-event reasons while a timed region runs (read-only queries).
+
+    NVML is initialised in the constructor, i.e. BEFORE the timed region: starting a fresh
+    ``nvidia-smi`` process per sample (which initialises the management library every time) was
+    measured to stall the memory-management calls of the benchmark itself (one cuMemUnmap of 940 ms
+    in a region that otherwise takes 2 ms).  In-process NVML queries take microseconds; the
+    ``nvidia-smi`` loop is kept as a fallback when the Python binding is missing."""
 
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int = 0):
-        self.index, self.samples, self._stop = index, [], threading.Event()
+    def __init__(self, index: int = 0, period_s: float | None = 0.05):
+        """``period_s=None``: no background thread, the caller takes samples with ``sample_now()``
+        at moments of its choosing (management-library queries contend with the driver's
+        memory-management calls: polled at 50 Hz from two ranks they stretched a 13 ms
+        pause + resume to 87 ms, so a latency benchmark samples between those calls, not across)."""
+        self.index, self.samples, self._stop, self.period_s = index, [], threading.Event(), period_s
+        self._nvml = self._handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index(index))
+            self._nvml = pynvml
+        except Exception:  # noqa: BLE001
+            self._nvml = self._handle = None
         self._t = threading.Thread(target=self._run, daemon=True)
+
+    @staticmethod
+    def _physical_index(index: int) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+        parts = [p for p in vis.split(",") if p.strip()]
+        if parts and index < len(parts) and parts[index].strip().isdigit():
+            return int(parts[index])
+        return index
+
+    def _sample_nvml(self):
+        n, h = self._nvml, self._handle
+        sm = n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+        try:
+            mask = n.nvmlDeviceGetCurrentClocksEventReasons(h)
+        except Exception:  # noqa: BLE001
+            mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+        flag = lambda bit: "Active" if mask & bit else "Not Active"  # noqa: E731
+        return [str(sm), str(mx), flag(n.nvmlClocksEventReasonHwSlowdown), flag(n.nvmlClocksEventReasonHwThermalSlowdown),
+                flag(n.nvmlClocksEventReasonSwThermalSlowdown), flag(n.nvmlClocksEventReasonSwPowerCap)]
+
+    def sample_now(self) -> None:
+        """One synchronous sample (no-op without the Python binding)."""
+        if self._nvml is not None:
+            try:
+                self.samples.append(self._sample_nvml())
+            except Exception:  # noqa: BLE001
+                pass
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([f.strip() for f in out.split(",")])
+                if self._nvml is not None:
+                    self.samples.append(self._sample_nvml())
+                else:
+                    out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                         capture_output=True, text=True, timeout=5).stdout.strip()
+                    if out:
+                        self.samples.append([f.strip() for f in out.split(",")])
             except Exception:  # noqa: BLE001
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(self.period_s if self._nvml is not None else 0.2)
 
     def __enter__(self):
-        self._t.start()
+        if self.period_s is not None:
+            self._t.start()
         return self
 
     def __exit__(self, *a):
         self._stop.set()
-        self._t.join(timeout=6)
+        if self._t.is_alive():
+            self._t.join(timeout=6)
 
     def summary(self) -> dict:
         def num(s):

@@ -35,42 +35,7 @@ if ROOT not in sys.path:
 PUBLISHED_MS = 1000.0  # the reference's published steady-state figure: "< 1 second" per offload+reload
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index, self.samples, self._stop = index, [], threading.Event()
-        self._t = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i", str(self.index)],
-                                     capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([f.strip() for f in out.split(",")])
-            except Exception:  # noqa: BLE001
-                pass
-            self._stop.wait(0.2)
-
-    def __enter__(self):
-        self._t.start()
-        return self
-
-    def __exit__(self, *a):
-        self._stop.set()
-        self._t.join(timeout=6)
-
-    def summary(self) -> dict:
-        sm = [float(s[0]) for s in self.samples if s and s[0].replace(".", "").isdigit()]
-        mx = [float(s[1]) for s in self.samples if len(s) > 1 and s[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for s in self.samples for i in range(4) if len(s) >= 6 and s[2 + i].lower().startswith("active")})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+from asystem_amem_b200.utils.timing import ClockSampler  # noqa: E402  (in-process NVML, initialised before the timed region)
 
 
 def reference_arm(args) -> None:
@@ -168,6 +133,8 @@ def main() -> None:
         ev[0].record()
         collective()
         ev[1].record()
+        if record:
+            sampler.sample_now()                                 # the kernel is still running: clocks under load
         torch.cuda.synchronize()
         free0 = torch.cuda.mem_get_info()[0]
         t1 = time.perf_counter()
@@ -183,6 +150,9 @@ def main() -> None:
         t4 = time.perf_counter()
         return (t2 - t1) * 1e3, (t3 - t2b) * 1e3, ev[0].elapsed_time(ev[1]), free1 - free0, (t4 - t0) * 1e3
 
+    # NVML comes up here, before any timed step; clocks are read once per step while the timed
+    # all-reduce runs on the GPU (never across ncclPause / ncclResume, which such queries slow down)
+    sampler = ClockSampler(local, period_s=None)
     for _ in range(args.warmup):
         step(False)
     if args.impl == "amem":
@@ -190,7 +160,7 @@ def main() -> None:
     rows = []
     torch.cuda.synchronize()
     host_barrier()
-    with ClockSampler(local) as clocks:
+    with sampler as clocks:
         t_begin = time.perf_counter()
         for _ in range(args.steps):
             rows.append(step(True))
