@@ -94,6 +94,7 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "ncclCommAbort": [c_void_p],
         "ncclCommFinalize": [c_void_p],
         "ncclCommSplit": [c_void_p, c_int, c_int, P(c_void_p), c_void_p],
+        "ncclCommShrink": [c_void_p, P(c_int), c_int, P(c_void_p), c_void_p, c_int],
         "ncclCommGetAsyncError": [c_void_p, P(c_int)],
         "ncclCommCount": [c_void_p, P(c_int)],
         "ncclCommCuDevice": [c_void_p, P(c_int)],

@@ -161,6 +161,17 @@ class Communicator:
         self.lib.ncclCommUserRank(h, ctypes.byref(r))
         return Communicator(n.value, r.value, b"", _handle=h.value)
 
+    def shrink(self, exclude) -> "Communicator":
+        """A new communicator over the ranks of this one that are not in ``exclude``
+        (ncclCommShrink).  Only the surviving ranks call it; the excluded ones may be gone."""
+        ex = (ctypes.c_int * max(1, len(exclude)))(*exclude)
+        h = ctypes.c_void_p()
+        B.check(self.lib.ncclCommShrink(self._h, ex, len(exclude), ctypes.byref(h), None, 0), "ncclCommShrink")
+        n, r = ctypes.c_int(), ctypes.c_int()
+        self.lib.ncclCommCount(h, ctypes.byref(n))
+        self.lib.ncclCommUserRank(h, ctypes.byref(r))
+        return Communicator(n.value, r.value, b"", _handle=h.value)
+
     @property
     def handle(self) -> int:
         return self._h.value

@@ -183,9 +183,15 @@ ncclResult_t ncclCommInitRankScalable(ncclComm_t* newcomm, int nranks, int myran
   return ncclCommInitRankConfig(newcomm, nranks, commIds[0], myrank, config);
 }
 
-ncclResult_t ncclCommShrink(ncclComm_t, int*, int, ncclComm_t* newcomm, ncclConfig_t*, int) {
-  if (newcomm) *newcomm = nullptr;
-  return R(fail(kInvalidUsage, "ncclCommShrink is not supported: create a new communicator over the surviving ranks"));
+// The surviving ranks of `comm` (all but excludeRanksList) form a new communicator; the parent is
+// left as it is (shrinkFlags is accepted for source compatibility: there is no in-flight
+// network state to abort, a parent with a lost rank is simply destroyed or aborted afterwards).
+ncclResult_t ncclCommShrink(ncclComm_t comm, int* excludeRanksList, int excludeRanksCount, ncclComm_t* newcomm, ncclConfig_t* config, int) {
+  if (!comm || !newcomm) return ncclInvalidArgument;
+  Comm* c = nullptr;
+  Status s = C(comm)->shrink(excludeRanksList, excludeRanksCount, config_from(config), &c);
+  *newcomm = reinterpret_cast<ncclComm_t>(c);
+  return R(s);
 }
 
 ncclResult_t ncclRedOpCreatePreMulSum(ncclRedOp_t* op, void* scalar, ncclDataType_t datatype, ncclScalarResidence_t residence, ncclComm_t) {

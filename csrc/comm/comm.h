@@ -47,6 +47,9 @@ class Comm {
   static Status create(const UniqueId& id, int nranks, int rank, const CommConfig& cfg, VmmBackend* be, Comm** out);
   // Collective over the parent.  color < 0 yields *out == nullptr.
   Status split(int color, int key, const CommConfig& cfg, Comm** out);
+  // New communicator over the ranks of this one that are NOT in `exclude` (ncclCommShrink); only
+  // the surviving ranks call it, the excluded ones may be gone.
+  Status shrink(const int* exclude, int n_exclude, const CommConfig& cfg, Comm** out);
   Status destroy();
   void abort();
 

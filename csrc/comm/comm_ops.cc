@@ -287,6 +287,32 @@ Status Comm::split(int color, int key, const CommConfig& cfg, Comm** out) {
   return Comm::create(all[leader].id, (int)members.size(), new_rank, cfg, be_, out);
 }
 
+Status Comm::shrink(const int* exclude, int n_exclude, const CommConfig& cfg, Comm** out) {
+  *out = nullptr;
+  if (n_exclude < 0 || (n_exclude > 0 && !exclude)) return fail(kInvalidArgument, "ncclCommShrink: bad exclusion list");
+  std::vector<bool> gone(nranks_, false);
+  for (int i = 0; i < n_exclude; ++i) {
+    if (exclude[i] < 0 || exclude[i] >= nranks_) return fail(kInvalidArgument, "ncclCommShrink: rank %d is not in this communicator", exclude[i]);
+    gone[exclude[i]] = true;
+  }
+  if (gone[rank_]) return fail(kInvalidArgument, "ncclCommShrink: the calling rank %d is in the exclusion list", rank_);
+  std::vector<int> alive;
+  for (int r = 0; r < nranks_; ++r)
+    if (!gone[r]) alive.push_back(r);
+  // The lowest surviving rank proposes the id of the child and tells every other survivor over
+  // the pairwise sockets; excluded ranks are never contacted (they may have died).
+  UniqueId id;
+  const int leader = alive[0];
+  if (rank_ == leader) {
+    AMEM_TRY(make_unique_id(&id));
+    for (size_t i = 1; i < alive.size(); ++i) AMEM_TRY(mesh_->send_blob(alive[i], &id, sizeof(id)));
+  } else {
+    AMEM_TRY(mesh_->recv_blob(leader, &id, sizeof(id)));
+  }
+  int new_rank = (int)(std::find(alive.begin(), alive.end(), rank_) - alive.begin());
+  return Comm::create(id, (int)alive.size(), new_rank, cfg, be_, out);
+}
+
 Status Comm::pause(PauseResumeStats* st) {
   std::lock_guard<std::mutex> g(mu_);
   if (paused_) return kSuccess;

@@ -189,6 +189,27 @@ Status Mesh::recv_fd(int from, uint32_t* sym_id, uint64_t* size, int* fd) {
   return kSuccess;
 }
 
+Status Mesh::send_blob(int to, const void* data, size_t len) {
+  if (len > 16384) return fail(kInvalidArgument, "control-plane messages are limited to 16 KiB");
+  if (to < 0 || to >= nranks_ || to == rank_) return fail(kInvalidArgument, "send_blob: bad peer %d", to);
+  std::lock_guard<std::mutex> g(mu_);
+  Deadline dl = Deadline::after_ms(op_timeout_ms_);
+  AMEM_TRY(send_frame(to, kOpBlob, (uint32_t)len, 0, -1));
+  if (len) AMEM_TRY(uds_send(socks_[to], data, len, -1, dl));
+  return kSuccess;
+}
+
+Status Mesh::recv_blob(int from, void* data, size_t len) {
+  if (from < 0 || from >= nranks_ || from == rank_) return fail(kInvalidArgument, "recv_blob: bad peer %d", from);
+  std::lock_guard<std::mutex> g(mu_);
+  Deadline dl = Deadline::after_ms(op_timeout_ms_);
+  Frame f;
+  AMEM_TRY(recv_frame(from, kOpBlob, &f, nullptr));
+  if (f.arg != len) return fail(kInternalError, "rank %d sent %u bytes, expected %zu", from, f.arg, len);
+  if (len) AMEM_TRY(uds_recv(socks_[from], data, len, nullptr, dl));
+  return kSuccess;
+}
+
 Status Mesh::allgather(const void* mine, size_t len, void* all) {
   if (len > 16384) return fail(kInvalidArgument, "control-plane all-gather is limited to 16 KiB per rank");
   std::lock_guard<std::mutex> g(mu_);

@@ -49,6 +49,9 @@ class Mesh : public PeerExchange {
 
   // Every rank contributes `len` bytes (at most 16 KiB); `all` receives nranks * len.
   Status allgather(const void* mine, size_t len, void* all);
+  // One message of `len` bytes (at most 16 KiB) to / from a single peer; nobody else takes part.
+  Status send_blob(int to, const void* data, size_t len);
+  Status recv_blob(int from, void* data, size_t len);
   // Closes every socket; peers see end-of-file on their next receive (ncclCommAbort).
   void shutdown_all();
 

@@ -34,10 +34,12 @@ def _api(rank, world, uid):
     lib.ncclRedOpDestroy.argtypes = [ctypes.c_int, ctypes.c_void_p]
     assert lib.ncclRedOpDestroy(op.value, comm._h) == 0
     out["destroyed_op_refused"] = lib.ncclAllReduce(x.ctypes.data, x.ctypes.data, 1000, B.DTYPES["float32"], op.value, comm._h, None) == 4
-    # unsupported / compatibility calls
-    lib.ncclCommShrink.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_int]
+    # a shrink that names the caller itself, or a rank that does not exist, is refused
+    lib.ncclCommShrink.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_int]
     nc = ctypes.c_void_p()
-    out["shrink"] = lib.ncclCommShrink(comm._h, None, 0, ctypes.byref(nc), None, 0) == 5
+    me, bogus = (ctypes.c_int * 1)(rank), (ctypes.c_int * 1)(world + 5)
+    out["shrink"] = (lib.ncclCommShrink(comm._h, me, 1, ctypes.byref(nc), None, 0) == 4 and
+                     lib.ncclCommShrink(comm._h, bogus, 1, ctypes.byref(nc), None, 0) == 4 and not nc.value)
     st = mem_stats()
     out["stats"] = (st["n_local"] == 2 and st["n_imported"] == 2 * (world - 1) and st["scratch_bytes"] > st["stateful_bytes"] > 0
                     and st["bytes_by_tag"][1] > 0 and st["bytes_by_tag"][7] > 0 and st["group_id"] == 170)

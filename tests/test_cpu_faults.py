@@ -129,3 +129,33 @@ def _peer_skips_collective(rank, world, uid):
 def test_bounded_wait_runs_out_when_a_peer_skips_a_collective():
     res = run_ranks(_peer_skips_collective, 2, env=FAST)
     assert res[0] == (3, 3), res  # ncclInternalError, also visible through ncclCommGetAsyncError
+
+
+def _shrink_after_loss(rank, world, uid):
+    """Rank 2 leaves between steps (host-side failure, nothing in flight); the survivors build a
+    smaller communicator out of the old one and carry on, pause / resume included."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator
+    comm = Communicator(world, rank, uid)
+    x = np.full(1000, float(rank + 1), dtype=np.float32)
+    comm.all_reduce(x)
+    ok = bool(np.all(x == 6.0))
+    if rank == 2:
+        return ok                                     # gone: never calls shrink, never destroys
+    small = comm.shrink([2])
+    ok = ok and small.nranks == 2 and small.rank == rank
+    y = np.full(1000, float(rank + 1), dtype=np.float32)
+    small.all_reduce(y)
+    ok = ok and bool(np.all(y == 3.0))
+    small.pause()
+    small.resume()
+    y[:] = float(rank + 1)
+    small.all_reduce(y)
+    ok = ok and bool(np.all(y == 3.0))
+    small.destroy()
+    comm.abort()
+    return ok
+
+
+def test_survivors_shrink_the_communicator():
+    assert all(run_ranks(_shrink_after_loss, 3, env=FAST))
