@@ -14,6 +14,7 @@
 #include "../comm/comm.h"
 #include "../core/log.h"
 #include "../include/nccl.h"
+#include "../kernels/launch.h"
 #include "../ipc/uds.h"
 
 using namespace amem;
@@ -421,6 +422,30 @@ ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* sta
   if (emulated) *emulated = C(comm)->emulated() ? 1 : 0;
   if (nvls) *nvls = C(comm)->nvls() ? 1 : 0;
   if (stage_bytes) *stage_bytes = C(comm)->stage_segment().size;
+  return ncclSuccess;
+}
+// The variant, grid and chunk the library would use for one collective on a communicator of
+// `nranks` GPUs with the default staging (host arithmetic only; no communicator needed).
+// kind: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 broadcast, 4 reduce, 5 all-to-all;
+// count has the meaning of the matching NCCL call.  algo out: 1 one-shot, 2 two-shot, 3 NVLS, 0 n/a.
+ncclResult_t amemTunerPlan(int kind, size_t count, ncclDataType_t dtype, int nranks, int nvls, size_t stage_bytes, int* algo,
+                           int* blocks, size_t* chunk_elems) {
+  if (kind < 0 || kind > kCollAllToAll || nranks < 1 || nranks > kMaxRanks || dtype_size(dtype) == 0) return ncclInvalidArgument;
+  TunerInput ti;
+  ti.kind = kind;
+  ti.count = count;
+  ti.dtype = dtype;
+  ti.redop = kSum;
+  ti.nranks = nranks;
+  ti.stage_bytes = stage_bytes ? stage_bytes : ((size_t)288 << 20);
+  ti.p2p_slot_bytes = (size_t)64 << 10;
+  ti.nvls = nvls != 0;
+  ti.max_blocks = 128;
+  ti.forced_algo = kAlgoAuto;
+  LaunchPlan p = plan_collective(ti);
+  if (algo) *algo = p.algo;
+  if (blocks) *blocks = p.blocks;
+  if (chunk_elems) *chunk_elems = p.chunk_elems;
   return ncclSuccess;
 }
 ncclResult_t amemInject(const char* what, int nth, int param) {

@@ -205,6 +205,11 @@ ncclResult_t amemAllReduceAlgo(const void* sendbuff, void* recvbuff, size_t coun
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream);
 /* The tiling amemGemmBf16 picks for a problem on a GPU with `sms` SMs: tile rows (128 or 256), tile
  * columns, K-slices of the last wave (1 = not split).  Host arithmetic only; outputs may be NULL. */
+/* Variant (1 one-shot, 2 two-shot, 3 NVLS, 0 n/a), grid and chunk the library picks for a collective
+ * (kind: 0 all-reduce, 1 all-gather, 2 reduce-scatter, 3 broadcast, 4 reduce, 5 all-to-all) on `nranks`
+ * GPUs; stage_bytes 0 = default staging.  Host arithmetic only. */
+ncclResult_t amemTunerPlan(int kind, size_t count, ncclDataType_t dtype, int nranks, int nvls, size_t stage_bytes, int* algo,
+                           int* blocks, size_t* chunk_elems);
 ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices);
 /* One kernel: C[M,N] = allgather_rows(a_shard)[M,K] * B[N,K]^T.  a_shard holds this rank's
  * M/nranks rows; the transfer of the other ranks' rows overlaps the tensor-core work. */

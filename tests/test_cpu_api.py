@@ -132,3 +132,45 @@ def test_gemm_planner_picks_tile_form_and_tail_split():
         rows, cols, slices = plan(*shape)
         assert rows in (128, 256) and 128 <= cols <= 256 and cols % 32 == 0 and 1 <= slices <= 32
     assert lib.amemGemmPlan(128, 100, 64, 148, None, None, None) == 4   # N not a multiple of 8
+
+
+def test_tuner_plan_is_deterministic_and_within_staging():
+    """Variant picker: thresholds measured on 2 and 8 GPUs, chunk sizes that fit the staging
+    layout, identical answers on repeated calls (every rank must pick the same plan)."""
+    os.environ["AMEM_BACKEND"] = "mock"
+    from asystem_amem_b200 import bindings as B
+    lib = B.load_library()
+    lib.amemTunerPlan.argtypes = [ctypes.c_int, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_size_t,
+                                  ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_size_t)]
+    BF16 = B.DTYPES["bfloat16"]
+
+    def plan(kind, nbytes, n, nvls=1, dtype=BF16, es=2):
+        a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_size_t()
+        assert lib.amemTunerPlan(kind, nbytes // es, dtype, n, nvls, 0, ctypes.byref(a), ctypes.byref(b), ctypes.byref(c)) == 0
+        return a.value, b.value, c.value * es
+
+    ONE, TWO, NVLS = 1, 2, 3
+    # all-reduce variants
+    assert plan(0, 64 << 10, 8)[0] == ONE and plan(0, 256 << 10, 8)[0] == ONE
+    assert plan(0, 1 << 20, 8)[0] == NVLS and plan(0, 1 << 30, 8)[0] == NVLS and plan(0, 1 << 30, 4)[0] == NVLS
+    assert plan(0, 1 << 30, 8, nvls=0)[0] == TWO
+    assert plan(0, 1 << 20, 2)[0] == ONE and plan(0, 16 << 20, 2)[0] == ONE     # two GPUs: one-shot up to 16 MiB
+    assert plan(0, 32 << 20, 2)[0] == TWO and plan(0, 1 << 30, 2)[0] == TWO      # never NVLS between two GPUs
+    # grid grows with the message and is capped
+    assert plan(0, 8, 8)[1] == 1 and plan(0, 1 << 30, 8)[1] == 128
+    # chunks: whole message up to 32 MiB (NVLS), then about eight chunks of at least 16 MiB, never above a third of a half
+    stage = 288 << 20
+    quarter = ((stage - 8 * 2 * 32 * (64 << 10)) // 4) & ~4095
+    assert plan(0, 32 << 20, 8)[2] >= 32 << 20
+    assert plan(0, 256 << 20, 8)[2] == 32 << 20
+    assert 16 << 20 <= plan(0, 64 << 20, 8)[2] <= (2 * quarter) // 3
+    assert plan(0, 8 << 30, 8)[2] <= (2 * quarter) // 3
+    # all-gather / reduce-scatter / all-to-all: per-rank chunk never above one rank's slot of a quarter
+    for kind in (1, 2, 5):
+        for n in (2, 4, 8):
+            for per_rank in (1 << 20, 40 << 20, 1 << 30):
+                chunk = plan(kind, per_rank, n)[2]
+                assert 0 < chunk <= max(per_rank, 4096) and chunk <= quarter // n + 4096
+    # same question, same answer
+    assert plan(0, 123456789 * 2, 8) == plan(0, 123456789 * 2, 8)
+    assert lib.amemTunerPlan(9, 1, BF16, 8, 1, 0, None, None, None) == 4
