@@ -181,6 +181,10 @@ class Communicator:
         B.check(self.lib.amemCommInfo(self._h, ctypes.byref(emu), ctypes.byref(nvls), ctypes.byref(stage)), "amemCommInfo")
         return {"emulated": bool(emu.value), "nvls": bool(nvls.value), "stage_bytes": stage.value}
 
+    def check_canary(self) -> None:
+        """Raises if a kernel wrote past the staging layout (guard enabled with AMEM_CANARY=1)."""
+        B.check(self.lib.amemCheckCanary(self._h), "amemCheckCanary")
+
     def destroy(self) -> None:
         if self._h is not None and self._h.value:
             B.check(self.lib.ncclCommDestroy(self._h), "ncclCommDestroy")

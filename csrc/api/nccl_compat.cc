@@ -448,6 +448,16 @@ ncclResult_t amemTunerPlan(int kind, size_t count, ncclDataType_t dtype, int nra
   if (chunk_elems) *chunk_elems = p.chunk_elems;
   return ncclSuccess;
 }
+// Checks the staging guard of `comm` now (AMEM_CANARY=1; ncclSuccess when the guard is off).
+ncclResult_t amemCheckCanary(ncclComm_t comm) {
+  NEED_COMM(comm);
+  return R(C(comm)->check_canary());
+}
+// Test hook: simulates an out-of-bounds write behind the staging layout.
+ncclResult_t amemDebugDirtyCanary(ncclComm_t comm) {
+  NEED_COMM(comm);
+  return R(C(comm)->debug_dirty_canary());
+}
 ncclResult_t amemInject(const char* what, int nth, int param) {
   if (!what) return ncclInvalidArgument;
   if (!strncmp(what, "uds:", 4)) {

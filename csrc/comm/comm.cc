@@ -114,7 +114,12 @@ Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cf
   AMEM_TRY(sym_alloc(round_up(sizeof(CtrlBlock) + (1u << 16), gran_), ctrl_cat, kTagP2P, &ctrl_));
   AMEM_TRY(be_->memset_zero(ctrl_.va[rank_], ctrl_.size, dev_));
   AMEM_TRY(be_->copies_sync(dev_));
-  AMEM_TRY(sym_alloc(round_up(stage, gran_), kScratch, kTagP2P, &stage_));
+  canary_bytes_ = env_long("AMEM_CANARY", 0) ? gran_ : 0;
+  AMEM_TRY(sym_alloc(round_up(stage, gran_) + canary_bytes_, kScratch, kTagP2P, &stage_));
+  if (canary_bytes_) {
+    AMEM_TRY(be_->memset_zero(stage_.va[rank_] + stage_.size - canary_bytes_, canary_bytes_, dev_));
+    AMEM_TRY(be_->copies_sync(dev_));
+  }
   int want_nvls = cfg.nvls >= 0 ? cfg.nvls : (int)env_long("AMEM_NVLS", 1);
   if (device && !emulate && nranks > 1 && all_mc && want_nvls) {
     Status st = setup_multicast();
@@ -327,12 +332,40 @@ Comm::~Comm() {
   delete mesh_;
 }
 
+Status Comm::check_canary() {
+  if (!canary_bytes_ || paused_) return kSuccess;
+  if (be_->is_device()) AMEM_TRY(be_->device_sync(dev_));
+  std::vector<uint64_t> host(canary_bytes_ / 8);
+  void* pinned = nullptr;
+  AMEM_TRY(be_->host_alloc(canary_bytes_, &pinned));
+  Status st = be_->copy_to_host_async(pinned, stage_.va[rank_] + stage_.size - canary_bytes_, canary_bytes_, dev_);
+  if (st == kSuccess) st = be_->copies_sync(dev_);
+  if (st == kSuccess) memcpy(host.data(), pinned, canary_bytes_);
+  be_->host_free(pinned, canary_bytes_);
+  AMEM_TRY(st);
+  for (size_t i = 0; i < host.size(); ++i)
+    if (host[i]) {
+      return fail(kInternalError, "rank %d: staging guard is dirty at offset %zu past the layout (value %#llx): a kernel wrote out of bounds",
+                  rank_, i * 8, (unsigned long long)host[i]);
+    }
+  return kSuccess;
+}
+
+Status Comm::debug_dirty_canary() {
+  if (!canary_bytes_ || paused_) return fail(kInvalidUsage, "no staging guard to write to (AMEM_CANARY=1, communicator not paused)");
+  static const uint64_t word = 0xdeadbeefcafef00dull;
+  AMEM_TRY(be_->copy_to_device_async(stage_.va[rank_] + stage_.size - canary_bytes_ + 4096, &word, sizeof(word), dev_));
+  return be_->copies_sync(dev_);
+}
+
 Status Comm::destroy() {
   {
     std::lock_guard<std::mutex> g(g_comms_mu);
     g_comms.erase(std::remove(g_comms.begin(), g_comms.end(), this), g_comms.end());
   }
   if (be_->is_device()) be_->device_sync(dev_);
+  Status guard = aborted_ ? kSuccess : check_canary();
+  if (guard != kSuccess) LOGE("%s", last_error_slot().c_str());
   // Peers must be done with my memory before I unmap it.
   if (!aborted_ && mesh_ && nranks_ > 1) mesh_->barrier();
   for (auto& s : fused_)
@@ -344,7 +377,7 @@ Status Comm::destroy() {
   emu_.reset();
   EmuGroup::drop(gkey);
   delete this;
-  return kSuccess;
+  return guard;
 }
 
 void Comm::abort() {

@@ -50,6 +50,12 @@ class Comm {
   // New communicator over the ranks of this one that are NOT in `exclude` (ncclCommShrink); only
   // the surviving ranks call it, the excluded ones may be gone.
   Status shrink(const int* exclude, int n_exclude, const CommConfig& cfg, Comm** out);
+  // Debug guard (AMEM_CANARY=1): one extra granule after the staging layout is kept at zero; a
+  // kernel that writes past its region shows up here.  Checked before every pause, at destroy
+  // and on request; kInternalError names the first dirty offset.
+  Status check_canary();
+  size_t canary_bytes() const { return canary_bytes_; }
+  Status debug_dirty_canary();  // test hook: writes one non-zero word into the guard
   Status destroy();
   void abort();
 
@@ -129,6 +135,7 @@ class Comm {
   bool status_pinned_ = false;
   unsigned long long timeout_ns_ = 0;
   int max_blocks_ = 64;
+  size_t canary_bytes_ = 0;
   bool paused_ = false, aborted_ = false;
   int async_error_ = 0;
   cudaStream_t last_stream_ = nullptr;

@@ -26,7 +26,7 @@ void Comm::fill_args(CollArgs* a) const {
     a->stage[r] = (char*)stage_.va[r];
   }
   a->mc_stage = (char*)stage_.mc_va;
-  a->stage_bytes = stage_.size;
+  a->stage_bytes = stage_.size - canary_bytes_;  // the guard granule is not part of the layout
   a->p2p_slot_bytes = p2p_slot_bytes_;
   a->status = status_;
   a->timeout_ns = timeout_ns_;
@@ -152,7 +152,7 @@ Status Comm::collective(int kind, const void* send, void* recv, size_t count, in
   ti.dtype = a.dtype;
   ti.redop = redop;
   ti.nranks = nranks_;
-  ti.stage_bytes = stage_.size;
+  ti.stage_bytes = stage_.size - canary_bytes_;
   ti.p2p_slot_bytes = p2p_slot_bytes_;
   ti.nvls = nvls();
   ti.max_blocks = max_blocks_;
@@ -317,6 +317,7 @@ Status Comm::pause(PauseResumeStats* st) {
   std::lock_guard<std::mutex> g(mu_);
   if (paused_) return kSuccess;
   if (!pending_.empty()) return fail(kInvalidUsage, "ncclPause inside an open group");
+  AMEM_TRY(check_canary());
   Status s = pause_scope(Registry::instance(), be_, id(), dev_, mesh_, opt_, &stats_);
   if (s == kSuccess) paused_ = true;
   if (st) *st = stats_;
@@ -328,6 +329,10 @@ Status Comm::resume(PauseResumeStats* st) {
   if (!paused_) return kSuccess;
   Status s = resume_scope(Registry::instance(), be_, id(), dev_, mesh_, opt_, &stats_);
   if (s == kSuccess) paused_ = false;
+  if (s == kSuccess && canary_bytes_) {  // fresh physical memory: the guard starts at zero again
+    s = be_->memset_zero(stage_.va[rank_] + stage_.size - canary_bytes_, canary_bytes_, dev_);
+    if (s == kSuccess) s = be_->copies_sync(dev_);
+  }
   if (st) *st = stats_;
   return s;
 }

@@ -210,6 +210,9 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
  * GPUs; stage_bytes 0 = default staging.  Host arithmetic only. */
 ncclResult_t amemTunerPlan(int kind, size_t count, ncclDataType_t dtype, int nranks, int nvls, size_t stage_bytes, int* algo,
                            int* blocks, size_t* chunk_elems);
+/* Debug guard behind the staging layout (AMEM_CANARY=1): ncclInternalError if a kernel wrote past it. */
+ncclResult_t amemCheckCanary(ncclComm_t comm);
+ncclResult_t amemDebugDirtyCanary(ncclComm_t comm); /* test hook: dirties the guard */
 ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices);
 /* One kernel: C[M,N] = allgather_rows(a_shard)[M,K] * B[N,K]^T.  a_shard holds this rank's
  * M/nranks rows; the transfer of the other ranks' rows overlaps the tensor-core work. */

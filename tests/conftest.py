@@ -8,6 +8,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# every communicator of the test suite carries the debug guard behind its staging layout: a
+# kernel (or host executor) that writes out of bounds fails the test at pause or destroy
+os.environ.setdefault("AMEM_CANARY", "1")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
 

@@ -159,3 +159,32 @@ def _shrink_after_loss(rank, world, uid):
 
 def test_survivors_shrink_the_communicator():
     assert all(run_ranks(_shrink_after_loss, 3, env=FAST))
+
+
+def _guard_catches_overflow(rank, world, uid):
+    import numpy as np
+    from asystem_amem_b200 import Communicator, NcclError
+    comm = Communicator(world, rank, uid)
+    x = np.ones(1 << 16, dtype=np.float32)
+    comm.all_reduce(x)
+    comm.check_canary()                      # clean after real traffic
+    out = {"clean": True}
+    if rank == 0:
+        assert comm.lib.amemDebugDirtyCanary(comm._h) == 0
+        try:
+            comm.check_canary()
+            out["caught"] = False
+        except NcclError as e:
+            out["caught"] = "guard is dirty" in str(e)
+        try:
+            comm.pause()                     # a dirty guard also refuses the pause
+            out["pause_refused"] = False
+        except NcclError:
+            out["pause_refused"] = True
+    comm.abort()
+    return out
+
+
+def test_staging_guard_reports_out_of_bounds_write():
+    res = run_ranks(_guard_catches_overflow, 2, env=dict(FAST, AMEM_CANARY="1"))
+    assert res[0] == {"clean": True, "caught": True, "pause_refused": True} and res[1] == {"clean": True}
