@@ -37,7 +37,7 @@ def time_interleaved(fns, iters=30, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/gemm.jsonl")
+    ap.add_argument("--out", default="bench_results/gemm.jsonl")
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--shapes", default="8192x3584x8192,8192x8192x3584,8192x8192x8192,4096x4096x4096,1024x3584x8192,2048x2048x2048")
     args = ap.parse_args()

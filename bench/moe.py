@@ -31,7 +31,7 @@ def main():
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--tp", type=int, default=2)
     ap.add_argument("--cycles", type=int, default=100)
-    ap.add_argument("--out", default="gpurun_out/moe.jsonl")
+    ap.add_argument("--out", default="bench_results/moe.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -149,6 +149,7 @@ def main():
     if rank == 0:
         res = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items()}
         print(json.dumps(res), flush=True)
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         with open(args.out, "a") as f:
             f.write(json.dumps(res) + "\n")
     dist.barrier(group=gloo)

@@ -6,7 +6,7 @@ under a few GB, so that `ncu --set full -k regex:<kernel> -c 1..3` finishes in a
 Multi-rank kernels run as emulated ranks (threads of this process, one cooperative grid).
 
     python bench/ncu_cases.py --case gemm
-    ncu --set full --clock-control none -k regex:gemm_kernel -s 1 -c 1 -o gpurun_out/prof_gemm python bench/ncu_cases.py --case gemm
+    ncu --set full --clock-control none -k regex:gemm_kernel -s 1 -c 1 -o /tmp/prof_gemm python bench/ncu_cases.py --case gemm
 """
 import argparse
 import os

@@ -88,7 +88,7 @@ def main():
     ap.add_argument("--infer-batch", type=int, default=64)
     ap.add_argument("--infer-seq", type=int, default=2048)
     ap.add_argument("--cycles", type=int, default=3)
-    ap.add_argument("--out", default="gpurun_out/rl_cycle.jsonl")
+    ap.add_argument("--out", default="bench_results/rl_cycle.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -159,6 +159,7 @@ def main():
         rows.append(row)
         if rank == 0:
             print(json.dumps(row), flush=True)
+            os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
             with open(args.out, "a") as f:
                 f.write(json.dumps(row) + "\n")
     infer_comm.resume()

@@ -30,7 +30,7 @@ def main():
     ap.add_argument("--colls", default="allreduce,allgather,reducescatter,alltoall")
     ap.add_argument("--dtypes", default="bf16,fp32")
     ap.add_argument("--no-pause", action="store_true")
-    ap.add_argument("--out", default="gpurun_out/sweep.jsonl")
+    ap.add_argument("--out", default="bench_results/sweep.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -40,6 +40,8 @@ def main():
     comm = Communicator.from_torch_distributed(gloo)
     info = comm.info()
     flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
     out_f = open(args.out, "a") if rank == 0 else None
     dts = {"bf16": torch.bfloat16, "fp32": torch.float32}
 

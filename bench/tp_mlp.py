@@ -30,7 +30,7 @@ def main():
     ap.add_argument("--ffn", type=int, default=28672)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--no-pause", action="store_true", help="do not pause/resume between iterations")
-    ap.add_argument("--out", default="gpurun_out/tp_mlp.jsonl")
+    ap.add_argument("--out", default="bench_results/tp_mlp.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -116,6 +116,7 @@ def main():
     if rank == 0:
         res = {k: (round(v, 4) if isinstance(v, float) else v) for k, v in res.items()}
         print(json.dumps(res), flush=True)
+        os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
         with open(args.out, "a") as f:
             f.write(json.dumps(res) + "\n")
     comm.destroy()
