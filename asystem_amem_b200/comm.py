@@ -5,6 +5,10 @@ CUDA backend; CPU tensors with ``AMEM_BACKEND=mock``) or numpy arrays and run on
 torch CUDA stream unless ``stream`` is given.  ``pause()`` / ``resume()`` release and restore
 the communicator's device memory; :func:`pause_all` / :func:`resume_all` do so for every
 communicator of the process (the reference's ``ncclPause(NULL)`` / ``ncclResume(NULL)``).
+
+Reference parity: the pynccl-style integration the reference documents for SGLang / vLLM
+(README.md:262-294: load the patched libnccl, call ncclPause / ncclResume / ncclSetGroupID
+through ctypes); here the same calls plus the collectives sit behind one Communicator class.
 """
 from __future__ import annotations
 

@@ -1,6 +1,10 @@
 """Llama-3-architecture decoder (RMSNorm, rotary embeddings, grouped-query attention, SwiGLU)
 with random initialisation.  The math is plain PyTorch; the library's part is the
-communication around it (see parallel.fsdp)."""
+communication around it (see parallel.fsdp).
+
+Reference parity: none -- the reference ships no model; this decoder is the workload of the
+train / infer switching benchmark (the RL co-location scenario of README.md:1-60).
+"""
 from __future__ import annotations
 
 from dataclasses import dataclass

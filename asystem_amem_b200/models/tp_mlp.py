@@ -1,6 +1,10 @@
 """Tensor-parallel SwiGLU MLP block (Llama-3-70B shape by default: d=8192, ffn=28672) with
 sequence-parallel activations: all-gather -> GEMM for the gate/up projection, GEMM ->
-reduce-scatter for the down projection, both single fused kernels."""
+reduce-scatter for the down projection, both single fused kernels.
+
+Reference parity: none -- the reference ships no model and no GEMM; baseline for these layers
+is cuBLAS + NCCL.
+"""
 from __future__ import annotations
 
 import torch

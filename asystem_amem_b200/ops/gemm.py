@@ -2,6 +2,9 @@
 
 All take bf16 CUDA tensors with K contiguous: ``a`` is [M, K] (activations), ``b`` is [N, K]
 (a ``torch.nn.Linear`` weight), the result is [M, N] = a @ b.T in bf16 with fp32 accumulation.
+
+Reference parity: none -- the reference contains no GEMM and no fused operator (its plugin is
+host code only, amem_nccl_plugin/Makefile:36).
 """
 from __future__ import annotations
 

@@ -7,6 +7,10 @@ recomputes the unit (activation checkpointing at unit granularity), back-propaga
 reduce-scatters the flat gradient with the averaging scale and the bf16 -> fp32 cast fused into
 the reduce-scatter kernel.  All communicator memory is pausable: ``pause_all()`` between steps
 gives the staging memory back and ``resume_all()`` restores it without re-initialisation.
+
+Reference parity: none to match -- the reference implements no parallelism strategy, it pauses
+whatever communicators a process created (README.md:259, README.md:129-134); this wrapper
+exists because the RL co-location use case (README.md:1-60) needs a training step to pause.
 """
 from __future__ import annotations
 

@@ -4,6 +4,9 @@ Two transports: the library's own pausable ncclSend / ncclRecv (default), and
 ``torch.distributed`` NCCL point-to-point as the declared baseline path (its memory is outside
 the registry and is reported separately).  Transfers are issued on a side stream so the next
 micro-batch's compute overlaps them.
+
+Reference parity: none to match -- the reference has no pipeline code; send/recv are NCCL's
+(entry points guarded in nccl_patch/nccl_2.27.5-1.diff:113-230).
 """
 from __future__ import annotations
 

@@ -4,6 +4,10 @@ Activations between the two linears of a block are sharded by rows (tokens).  Th
 column-parallel linear all-gathers them inside its GEMM kernel; the row-parallel linear
 reduce-scatters its output from the GEMM epilogue.  Backward uses the mirrored fused kernels
 for the activation gradients and a library GEMM for the weight gradients.
+
+Reference parity: none to match -- tensor parallelism appears in the reference only as
+integration text (README.md:279-293, SGLang's tensor-model-parallel group); its users run
+cuBLAS and NCCL back to back.
 """
 from __future__ import annotations
 

@@ -1,4 +1,9 @@
-"""CUDA-event timing with L2 flushes, nvidia-smi clock sampling, measured-peak lookup."""
+"""CUDA-event timing with L2 flushes, nvidia-smi clock sampling, measured-peak lookup.
+
+Reference parity: the reference times pause and resume with std::chrono around the calls and
+prints milliseconds (amem_nccl_plugin/amem_nccl.cpp:490,563-569,602,668-674); nothing is timed
+on the device there.
+"""
 from __future__ import annotations
 
 import json

@@ -1,7 +1,10 @@
 #!/usr/bin/env python
 """Single-GPU throughput of the tcgen05 GEMM against cuBLAS (torch.matmul) on the tensor-parallel
 MLP shapes (Llama-3-70B, TP=8: d=8192, ffn/8=3584, 8192 tokens).  CUDA-event timing, L2 flushed
-between iterations, fraction of the measured cuBLAS peak from MEASURED_PEAKS.json."""
+between iterations, fraction of the measured cuBLAS peak from MEASURED_PEAKS.json.
+
+Reference parity: none -- the reference has no GEMM; cuBLAS is the baseline.
+"""
 import argparse
 import json
 import os

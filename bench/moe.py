@@ -7,6 +7,10 @@ layer's output stays bit-identical and that device memory use is flat.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29540 bench/moe.py --cycles 100
+
+Reference parity: the reference names all-to-all as the largest consumer of NCCL memory
+(README.md:132, docs/images/result1.webp) and pauses every communicator of the process together
+(nccl_patch/nccl_2.27.5-1.diff:70-77).
 """
 import argparse
 import json

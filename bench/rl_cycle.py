@@ -15,6 +15,9 @@ returns.  `--layers` shrinks the model for small boxes (default: the full 32 lay
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29550 bench/rl_cycle.py --cycles 3
+
+Reference parity: the use case the reference is built for (README.md:1-60, 'offload + reload <
+1 s per step'): two process groups share the GPUs and take turns.
 """
 import argparse
 import json

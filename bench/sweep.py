@@ -9,6 +9,10 @@ times this library and NCCL with CUDA events on the launching stream (3 warm-ups
 between iterations, max over ranks) and, like the reference's patched nccl-tests, calls
 ncclPause()/ncclResume() once between sizes.  busBW follows nccl-tests: all-reduce
 algBW*2(n-1)/n; all-gather, reduce-scatter, all-to-all algBW*(n-1)/n.
+
+Reference parity: the reference's own test is this sweep on nccl-tests binaries (run.sh:22-30:
+all_reduce_perf, all_gather_perf, alltoall_perf, broadcast_perf, -b 4M -e 8M -f 2) with one
+ncclPause / ncclResume after every size (nccl_patch/nccl-tests.diff:24-50).
 """
 import argparse
 import json

@@ -8,6 +8,9 @@ back to back, with the communicator paused and resumed between the 20 iterations
 
 Times are CUDA events on the launching stream, max over ranks.  Roofline per fused kernel: the
 slower of FLOPs / measured cuBLAS peak and NVLink bytes / 770 GB/s (measured peer copy rate).
+
+Reference parity: none -- baseline is what the reference's users run, cuBLAS + NCCL back to
+back.
 """
 import argparse
 import json

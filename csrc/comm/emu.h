@@ -6,6 +6,7 @@
 // device run at the same time.  The ranks therefore meet here on the host; the last one to
 // arrive launches ONE cooperative grid that carries all ranks (blockIdx.y = rank) and the
 // other ranks' streams are made to wait for it through events.
+// Reference parity: none -- the reference is tested only on eight real GPUs under mpirun (run.sh:26-30).
 #pragma once
 #include <cuda_runtime.h>
 

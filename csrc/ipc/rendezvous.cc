@@ -1,3 +1,6 @@
+// Reference parity: replaces the admin thread + shared-memory directory + lock file of the reference
+// (amem_nccl_plugin/gmm_server_impl.cpp:95-101, gmm_common.h:418-473) by socket names derived from
+// the ncclUniqueId.
 #include "rendezvous.h"
 
 #include <fcntl.h>

@@ -1,3 +1,5 @@
+// Reference parity: the framing and SCM_RIGHTS passing of amem_nccl_plugin/gmm_common_impl.cpp:341-434
+// (one fixed-size request per message, one descriptor as ancillary data), with deadlines added.
 #include "uds.h"
 
 #include <fcntl.h>

@@ -12,6 +12,8 @@
 // alternate chunks, which removes every trailing barrier.  All waits are bounded: on expiry
 // the block records {code, rank, peer, block, epoch} in a host-mapped status word and the
 // kernel runs to completion without faulting.
+// Reference parity: the reference has no device code of its own (amem_nccl_plugin/Makefile:36); its
+// collectives are NCCL 2.27.5's kernels, whose buffers it re-creates on resume.
 #pragma once
 #include <cstddef>
 #include <cstdint>

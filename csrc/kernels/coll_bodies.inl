@@ -8,6 +8,8 @@
 // Conventions: `es` = bytes per input element, every staging offset is a multiple of 256
 // bytes, block ranges start on 16-byte boundaries, `p.opseq` picks the staging half and the
 // chunk index picks the quarter inside it.
+// Reference parity: stands in for the NCCL collectives the reference guards and exercises
+// (nccl_patch/nccl_2.27.5-1.diff:113-230; run.sh:22: all_reduce, all_gather, alltoall, broadcast).
 
 // Peer visited at step k (1..n-1) by `block`; different blocks start at different peers so
 // that the stores of one rank fan out over all NVLink destinations at once.

@@ -2,6 +2,8 @@
 // the bounded block-level cross-rank barrier, 16-byte vector copy / reduce loops and the
 // element-type traits.  Everything here is plain sm_100a CUDA C++ with inline PTX for the
 // memory-model sensitive accesses; no library device code is used.
+// Reference parity: none -- the reference's waits are on the host and several are unbounded
+// (amem_nccl_plugin/amem_nccl.cpp:659-662, gmm_client_impl.cpp:108-111,182-187).
 #pragma once
 #include <type_traits>
 #include <cuda_bf16.h>

@@ -9,6 +9,8 @@
 // (blockIdx.y = rank): kernels of different ranks wait on one another, so they must never be
 // separate launches on the same device.  This is what lets the single-GPU test-suite cover
 // the multi-rank protocol.
+// Reference parity: see coll_bodies.inl; the NVLS variant corresponds to NCCL's NVLS algorithm, whose
+// multicast handles the reference unbinds and rebinds (amem_nccl_plugin/amem_nccl.cpp:536-538,614-616).
 #include "coll_kernels.cuh"
 
 namespace amem {
