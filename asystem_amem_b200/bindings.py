@@ -122,6 +122,7 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "amemPauseResumeStatsGet": [c_void_p, P(PauseResumeStats)],
         "amemCommInfo": [c_void_p, P(c_int), P(c_int), P(c_size_t)],
         "amemInject": [ctypes.c_char_p, c_int, c_int],
+        "amemAlltoAllv": [c_void_p, P(c_size_t), P(c_size_t), c_void_p, P(c_size_t), P(c_size_t), c_int, c_void_p, c_void_p],
         "amemCheckCanary": [c_void_p],
         "amemDebugDirtyCanary": [c_void_p],
         "amemBackendUsage": [P(c_size_t), P(c_size_t), P(ctypes.c_char_p)],

@@ -273,25 +273,9 @@ class Communicator:
         sd, rd = displs(send_counts, send_displs), displs(recv_counts, recv_displs)
         if int(send_counts[me]) != int(recv_counts[me]):
             raise ValueError("all_to_all_v: this rank's own send and receive counts differ")
-        es, dt, st = send.itemsize if hasattr(send, "itemsize") else send.element_size(), _dtype_code(send), _stream_handle(stream, send)
-        sp, rp = _ptr(send), _ptr(recv)
-        if send_counts[me]:
-            flat_s, flat_r = send.reshape(-1), recv.reshape(-1)
-            c = int(send_counts[me])
-            if hasattr(flat_r, "copy_"):
-                flat_r[rd[me]:rd[me] + c].copy_(flat_s[sd[me]:sd[me] + c])
-            else:
-                flat_r[rd[me]:rd[me] + c] = flat_s[sd[me]:sd[me] + c]
-        group_start()
-        try:
-            for k in range(1, n):
-                to, frm = (me + k) % n, (me - k) % n
-                if send_counts[to]:
-                    B.check(self.lib.ncclSend(sp + sd[to] * es, int(send_counts[to]), dt, to, self._h, st), "ncclSend")
-                if recv_counts[frm]:
-                    B.check(self.lib.ncclRecv(rp + rd[frm] * es, int(recv_counts[frm]), dt, frm, self._h, st), "ncclRecv")
-        finally:
-            group_end()
+        arr = lambda v: (ctypes.c_size_t * n)(*[int(x) for x in v])  # noqa: E731
+        B.check(self.lib.amemAlltoAllv(_ptr(send), arr(send_counts), arr(sd), _ptr(recv), arr(recv_counts), arr(rd),
+                                       _dtype_code(send), self._h, _stream_handle(stream, send)), "amemAlltoAllv")
         return recv
 
     def send(self, tensor, peer: int, stream=None):

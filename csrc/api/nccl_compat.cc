@@ -355,6 +355,29 @@ ncclResult_t ncclRecv(void* r, size_t count, ncclDataType_t dt, int peer, ncclCo
   NEED_COMM(comm);
   return R(C(comm)->p2p(false, nullptr, r, count * dtype_size(dt), peer, st));
 }
+// Variable-size all-to-all (MPI_Alltoallv argument convention, counts and displacements in
+// elements): one grouped launch of a send and a receive per peer, the form NCCL applications
+// write by hand (nccl-tests' alltoall is the same grouped send/recv); the block a rank keeps for
+// itself is paired inside the group and never touches the network.
+ncclResult_t amemAlltoAllv(const void* sendbuff, const size_t* sendcounts, const size_t* sdispls, void* recvbuff,
+                           const size_t* recvcounts, const size_t* rdispls, ncclDataType_t dt, ncclComm_t comm, cudaStream_t st) {
+  NEED_COMM(comm);
+  if (!sendcounts || !sdispls || !recvcounts || !rdispls) return ncclInvalidArgument;
+  const size_t es = dtype_size(dt);
+  if (es == 0) return ncclInvalidArgument;
+  Comm* c = C(comm);
+  const int n = c->nranks(), me = c->rank();
+  if (sendcounts[me] != recvcounts[me]) return R(fail(kInvalidArgument, "amemAlltoAllv: rank %d keeps %zu elements but expects %zu", me, sendcounts[me], recvcounts[me]));
+  Status s = Comm::group_start();
+  if (s != kSuccess) return R(s);
+  for (int k = 0; k < n && s == kSuccess; ++k) {
+    const int to = (me + k) % n, from = (me - k + n) % n;
+    if (sendcounts[to]) s = c->p2p(true, (const char*)sendbuff + sdispls[to] * es, nullptr, sendcounts[to] * es, to, st);
+    if (s == kSuccess && recvcounts[from]) s = c->p2p(false, nullptr, (char*)recvbuff + rdispls[from] * es, recvcounts[from] * es, from, st);
+  }
+  Status e = Comm::group_end();
+  return R(s != kSuccess ? s : e);
+}
 ncclResult_t ncclGroupStart(void) {
   // A paused process may not batch work either (the reference guards group calls too,
   // nccl_2.27.5-1.diff:205-229).

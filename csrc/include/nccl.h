@@ -211,6 +211,9 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
 ncclResult_t amemTunerPlan(int kind, size_t count, ncclDataType_t dtype, int nranks, int nvls, size_t stage_bytes, int* algo,
                            int* blocks, size_t* chunk_elems);
 /* Debug guard behind the staging layout (AMEM_CANARY=1): ncclInternalError if a kernel wrote past it. */
+/* Variable-size all-to-all; counts and displacements in elements, MPI_Alltoallv convention. */
+ncclResult_t amemAlltoAllv(const void* sendbuff, const size_t* sendcounts, const size_t* sdispls, void* recvbuff,
+                           const size_t* recvcounts, const size_t* rdispls, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
 ncclResult_t amemCheckCanary(ncclComm_t comm);
 ncclResult_t amemDebugDirtyCanary(ncclComm_t comm); /* test hook: dirties the guard */
 ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices);
