@@ -6,6 +6,7 @@ import os
 import threading
 
 import numpy as np
+import pytest
 
 from mp_util import run_ranks
 
@@ -174,3 +175,35 @@ def test_tuner_plan_is_deterministic_and_within_staging():
     # same question, same answer
     assert plan(0, 123456789 * 2, 8) == plan(0, 123456789 * 2, 8)
     assert lib.amemTunerPlan(9, 1, BF16, 8, 1, 0, None, None, None) == 4
+
+
+def test_c_program_against_nccl_h_runs_pause_cycles(tmp_path):
+    """examples/pause_cycle.c uses nothing but nccl.h (plus ncclPause / ncclResume / ncclMemStats):
+    built with gcc against the in-tree library, three forked ranks on the mock backend."""
+    import shutil
+    import subprocess
+    from asystem_amem_b200 import bindings as B
+    B.load_library()
+    gcc = shutil.which("gcc")
+    if not gcc:
+        pytest.skip("gcc not available")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "asystem_amem_b200", "lib")
+    exe = tmp_path / "pause_cycle"
+    res = subprocess.run([gcc, "-std=c11", "-Wall", "-Werror", "-I" + os.path.join(root, "csrc", "include"),
+                          os.path.join(root, "examples", "pause_cycle.c"), "-L" + libdir, "-lamem_b200",
+                          "-Wl,-rpath," + libdir, "-o", str(exe)], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    env = dict(os.environ, AMEM_BACKEND="mock", GMM_IPC_DIR=str(tmp_path), GMM_LOG="2")
+    run = subprocess.run([str(exe), "3"], capture_output=True, text=True, timeout=300, env=env)
+    assert run.returncode == 0 and "pause cycle ok: 3 ranks" in run.stdout, (run.stdout, run.stderr[-3000:])
+
+
+def test_python_switch_example_runs_on_the_mock_backend():
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, AMEM_BACKEND="mock", GMM_LOG="2")
+    run = subprocess.run([sys.executable, os.path.join(root, "examples", "train_infer_switch.py"), "--cpu", "--cycles", "2"],
+                         capture_output=True, text=True, timeout=300, env=env)
+    assert run.returncode == 0 and "switch example ok" in run.stdout, (run.stdout, run.stderr[-3000:])
