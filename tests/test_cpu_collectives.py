@@ -148,3 +148,78 @@ def _alltoallv(rank, world, uid):
 
 def test_all_to_all_v():
     assert all(run_ranks(_alltoallv, 3))
+
+
+def _fuzz(rank, world, uid, seed, cases):
+    """Random (collective, type, operator, size) cases against numpy, same order of additions
+    (rank 0 .. n-1), so floating-point results must match bit for bit.  Sizes run from one
+    element to several staging slots so that single-chunk, multi-chunk and ragged-tail paths of
+    every body are hit; the staging guard (AMEM_CANARY) is checked at the end."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator
+    comm = Communicator(world, rank, uid)
+    rng = np.random.default_rng(seed)              # same stream on every rank: same cases
+    dtypes = [np.float32, np.float64, np.int32, np.int64, np.uint8]
+    bad = []
+
+    def make(r, n, dt, salt):
+        g = np.random.default_rng(1000 * salt + r)
+        if np.issubdtype(dt, np.floating):
+            return g.standard_normal(n).astype(dt)
+        return g.integers(0, 7, n).astype(dt)
+
+    def fold(arrs, op):
+        acc = arrs[0].copy()
+        for a in arrs[1:]:
+            acc = {"sum": acc + a, "max": np.maximum(acc, a), "min": np.minimum(acc, a), "prod": acc * a}[op]
+        return acc.astype(arrs[0].dtype)
+
+    for case in range(cases):
+        kind = ["allreduce", "allgather", "reducescatter", "alltoall", "broadcast", "reduce"][int(rng.integers(0, 6))]
+        dt = dtypes[int(rng.integers(0, len(dtypes)))]
+        op = ["sum", "max", "min", "prod"][int(rng.integers(0, 4))]
+        n = int(rng.choice([1, 2, 3, 17, 255, 4097, 65537, int(rng.integers(1, 900_000))]))
+        root = int(rng.integers(0, world))
+        ok = True
+        if kind == "allreduce":
+            xs = [make(r, n, dt, case) for r in range(world)]
+            x = xs[rank].copy()
+            comm.all_reduce(x, op=op)
+            ok = np.array_equal(x, fold(xs, op))
+        elif kind == "allgather":
+            xs = [make(r, n, dt, case) for r in range(world)]
+            out = np.empty(world * n, dtype=dt)
+            comm.all_gather(xs[rank].copy(), out)
+            ok = np.array_equal(out, np.concatenate(xs))
+        elif kind == "reducescatter":
+            xs = [make(r, world * n, dt, case) for r in range(world)]
+            out = np.empty(n, dtype=dt)
+            comm.reduce_scatter(xs[rank].copy(), out, op=op)
+            ok = np.array_equal(out, fold([x[rank * n:(rank + 1) * n] for x in xs], op))
+        elif kind == "alltoall":
+            xs = [make(r, world * n, dt, case) for r in range(world)]
+            out = np.empty(world * n, dtype=dt)
+            comm.all_to_all(xs[rank].copy(), out)
+            ok = np.array_equal(out, np.concatenate([xs[j][rank * n:(rank + 1) * n] for j in range(world)]))
+        elif kind == "broadcast":
+            xs = [make(r, n, dt, case) for r in range(world)]
+            x = xs[rank].copy()
+            comm.broadcast(x, root=root)
+            ok = np.array_equal(x, xs[root])
+        else:
+            xs = [make(r, n, dt, case) for r in range(world)]
+            out = np.zeros(n, dtype=dt)
+            comm.reduce(xs[rank].copy(), out, root=root, op=op)
+            ok = rank != root or np.array_equal(out, fold(xs, op))
+        if not ok:
+            bad.append((case, kind, np.dtype(dt).name, op, n, root))
+    comm.check_canary()
+    comm.destroy()
+    return bad
+
+
+@pytest.mark.parametrize("world,seed", [(2, 11), (3, 12)])
+def test_random_cases_match_numpy_bit_for_bit(world, seed):
+    # a small staging segment makes most of the random sizes span several chunks
+    for bad in run_ranks(_fuzz, world, args=(seed, 200), timeout=600, env={"AMEM_STAGE_MB": "8", "AMEM_CANARY": "1"}):
+        assert bad == [], bad
