@@ -22,12 +22,27 @@ def _check(a: torch.Tensor, b: torch.Tensor) -> None:
         raise ValueError(f"inner dimensions differ: {tuple(a.shape)} vs {tuple(b.shape)}")
 
 
+def _on_host(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """Host tensors (mock backend, no GPU): the operation is composed from the library's
+    collective and a PyTorch matmul with fp32 accumulation, so that the parallel wrappers can be
+    tested without a GPU.  CUDA tensors never take this path: they go to the tcgen05 kernels or
+    fail."""
+    return not a.is_cuda and not b.is_cuda
+
+
+def _host_matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    return a.float() @ b.float().t()
+
+
 def _stream(stream) -> int:
     return (stream or torch.cuda.current_stream()).cuda_stream
 
 
 def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """out[M, N] = a[M, K] @ b[N, K].T on one GPU."""
+    if _on_host(a, b):
+        res = _host_matmul(a, b).to(a.dtype)
+        return res if out is None else out.copy_(res)
     _check(a, b)
     M, K = a.shape
     N = b.shape[0]
@@ -40,6 +55,11 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
 def all_gather_gemm(comm, a_shard: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """out[M, N] = all_gather_rows(a_shard)[M, K] @ b[N, K].T in ONE kernel (column-parallel
     linear under sequence parallelism).  ``a_shard`` holds this rank's M / nranks rows."""
+    if _on_host(a_shard, b):
+        full = torch.empty(a_shard.shape[0] * comm.nranks, a_shard.shape[1], dtype=a_shard.dtype)
+        comm.all_gather(a_shard.contiguous(), full)
+        res = _host_matmul(full, b).to(a_shard.dtype)
+        return res if out is None else out.copy_(res)
     _check(a_shard, b)
     m_local, K = a_shard.shape
     M, N = m_local * comm.nranks, b.shape[0]
@@ -52,6 +72,12 @@ def all_gather_gemm(comm, a_shard: torch.Tensor, b: torch.Tensor, out: torch.Ten
 def gemm_reduce_scatter(comm, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """out[M / nranks, N] = reduce_scatter_rows(a[M, K_local] @ b[N, K_local].T) in ONE kernel
     (row-parallel linear under sequence parallelism)."""
+    if _on_host(a, b):
+        part = _host_matmul(a, b).contiguous()                     # fp32 partial products
+        res32 = torch.empty(a.shape[0] // comm.nranks, b.shape[0], dtype=torch.float32)
+        comm.reduce_scatter(part, res32)
+        res = res32.to(a.dtype)
+        return res if out is None else out.copy_(res)
     _check(a, b)
     M, K = a.shape
     N = b.shape[0]

@@ -128,3 +128,44 @@ def _context_parallel(rank, world, uid, causal):
 def test_context_parallel_attention_matches_full_attention(world, causal):
     for err_ulysses, err_ring in run_ranks(_context_parallel, world, args=(causal,), timeout=300):
         assert err_ulysses < 1e-5 and err_ring < 1e-5, (err_ulysses, err_ring)
+
+
+def _tp_mlp(rank, world, uid):
+    """Column-parallel + row-parallel linears under sequence parallelism (host tensors: the
+    composed form of the fused operations) against the dense computation, forward and backward."""
+    import torch
+    from asystem_amem_b200 import Communicator
+    from asystem_amem_b200.parallel import ColumnParallelLinear, RowParallelLinear
+    comm = Communicator(world, rank, uid)
+    tokens, dim, ffn = 8 * world, 32, 16 * world
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(tokens, dim, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(ffn, dim, generator=g) * 0.2).to(torch.bfloat16)
+    w2 = (torch.randn(dim, ffn, generator=g) * 0.2).to(torch.bfloat16)
+    gout = torch.randn(tokens, dim, generator=g).to(torch.bfloat16)
+    rows, fl = tokens // world, ffn // world
+    col = ColumnParallelLinear(dim, ffn, comm, device="cpu")
+    row = RowParallelLinear(ffn, dim, comm, device="cpu")
+    with torch.no_grad():
+        col.weight.copy_(w1[rank * fl:(rank + 1) * fl])
+        row.weight.copy_(w2[:, rank * fl:(rank + 1) * fl])
+    xs = x[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+    y = row(torch.nn.functional.gelu(col(xs).float()).to(torch.bfloat16))
+    y.backward(gout[rank * rows:(rank + 1) * rows])
+    # dense reference in fp32 with the same bf16 rounding points
+    xr = x.float().requires_grad_(True)
+    w1r, w2r = w1.float().requires_grad_(True), w2.float().requires_grad_(True)
+    h = torch.nn.functional.gelu((xr @ w1r.t()).to(torch.bfloat16).float()).to(torch.bfloat16).float()
+    yr = h @ w2r.t()
+    yr.backward(gout.float())
+    sl = slice(rank * rows, (rank + 1) * rows)
+    errs = (float((y.float() - yr[sl]).abs().max()), float((xs.grad.float() - xr.grad[sl]).abs().max()),
+            float((col.weight.grad.float() - w1r.grad[rank * fl:(rank + 1) * fl]).abs().max()),
+            float((row.weight.grad.float() - w2r.grad[:, rank * fl:(rank + 1) * fl]).abs().max()))
+    comm.destroy()
+    return errs
+
+
+def test_tensor_parallel_layers_match_dense_on_host():
+    for errs in run_ranks(_tp_mlp, 2, timeout=300):
+        assert errs[0] < 0.03 and errs[1] < 0.03 and errs[2] < 0.08 and errs[3] < 0.08, errs   # bf16 rounding of outputs and gradients
