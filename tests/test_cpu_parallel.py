@@ -169,3 +169,52 @@ def _tp_mlp(rank, world, uid):
 def test_tensor_parallel_layers_match_dense_on_host():
     for errs in run_ranks(_tp_mlp, 2, timeout=300):
         assert errs[0] < 0.03 and errs[1] < 0.03 and errs[2] < 0.08 and errs[3] < 0.08, errs   # bf16 rounding of outputs and gradients
+
+
+def _expert_parallel(rank, world, uid):
+    """loss.backward() through ep_dispatch / ep_combine with every rank a real process (host form
+    of the dispatcher), against the dense computation out[t] = sum_c w[t,c] * (x[t] @ W[idx[t,c]])."""
+    import torch
+    from asystem_amem_b200 import Communicator
+    from asystem_amem_b200.ops import MoeDispatcher
+    from asystem_amem_b200.parallel.ep import ep_combine, ep_dispatch
+    comm = Communicator(world, rank, uid)
+    E, k, T, d = 2 * world, 2, 12, 16
+    El = E // world
+    g = torch.Generator().manual_seed(77)
+    xs = [torch.randn(T, d, generator=g).to(torch.bfloat16) for _ in range(world)]
+    logits = [torch.randn(T, E, generator=g) for _ in range(world)]
+    W = (torch.randn(E, d, d, generator=g) / d ** 0.5)
+    G = [torch.randn(T, d, generator=g).to(torch.bfloat16) for _ in range(world)]
+    idx = [lg.topk(k, dim=1).indices.to(torch.int32) for lg in logits]
+    disp = MoeDispatcher(comm, E, d, world * T * k)
+    x = xs[rank].clone().requires_grad_(True)
+    lg = logits[rank].clone().requires_grad_(True)
+    w = torch.softmax(lg.gather(1, idx[rank].long()), dim=1)
+    Wl = W[rank * El:(rank + 1) * El].clone().requires_grad_(True)
+    rows, offsets, send_pos = ep_dispatch(disp, x, idx[rank])
+    offs = offsets.tolist()
+    y_rows = torch.cat([(rows[offs[e]:offs[e + 1]].float() @ Wl[e]) for e in range(El)]).to(torch.bfloat16)
+    out = ep_combine(disp, y_rows, w, idx[rank], send_pos)
+    (out.float() * G[rank].float()).sum().backward()
+    # dense reference
+    Wr = W.clone().requires_grad_(True)
+    ref = []
+    for r in range(world):
+        xr = xs[r].float().requires_grad_(True)
+        lr = logits[r].clone().requires_grad_(True)
+        wr = torch.softmax(lr.gather(1, idx[r].long()), dim=1)
+        yr = torch.einsum("td,tkde->tke", xr, Wr[idx[r].long()])
+        o = (yr * wr.unsqueeze(2)).sum(1)
+        (o * G[r].float()).sum().backward()
+        ref.append((o.detach(), xr.grad, lr.grad))
+    errs = (float((out.float() - ref[rank][0]).abs().max()), float((x.grad.float() - ref[rank][1]).abs().max()),
+            float((lg.grad - ref[rank][2]).abs().max()), float((Wl.grad - Wr.grad[rank * El:(rank + 1) * El]).abs().max()))
+    comm.destroy()
+    return errs
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_expert_parallel_autograd_across_processes(world):
+    for errs in run_ranks(_expert_parallel, world, timeout=300):
+        assert errs[0] < 0.03 and errs[1] < 0.03 and errs[2] < 0.03 and errs[3] < 0.06, errs   # bf16 rounding
