@@ -218,3 +218,47 @@ def _expert_parallel(rank, world, uid):
 def test_expert_parallel_autograd_across_processes(world):
     for errs in run_ranks(_expert_parallel, world, timeout=300):
         assert errs[0] < 0.03 and errs[1] < 0.03 and errs[2] < 0.03 and errs[3] < 0.06, errs   # bf16 rounding
+
+
+def _moe_layer(rank, world, uid):
+    """The expert-parallel MoE layer (router, dispatch, SwiGLU experts, combine) trained one step
+    per rank process on host tensors; compared with the same layer written densely."""
+    import torch
+    import torch.nn.functional as F
+    from asystem_amem_b200 import Communicator
+    from asystem_amem_b200.models import MoELayer
+    comm = Communicator(world, rank, uid)
+    dim, ffn, E, k, T = 32, 16, 2 * world, 2, 20
+    layer = MoELayer(comm, dim, ffn, E, k, tokens_per_rank=T, capacity_factor=float(world), device="cpu", seed=5)
+    g = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(T, dim, generator=g).to(torch.bfloat16).requires_grad_(True)
+    G = torch.randn(T, dim, generator=g).to(torch.bfloat16)
+    out = layer(x)
+    (out.float() * G.float()).sum().backward()
+    # every rank needs all experts' weights for the dense reference
+    El = E // world
+    w13_all = torch.empty(world * layer.w13.numel(), dtype=torch.bfloat16)
+    w2_all = torch.empty(world * layer.w2.numel(), dtype=torch.bfloat16)
+    comm.all_gather(layer.w13.detach().contiguous().view(-1), w13_all)
+    comm.all_gather(layer.w2.detach().contiguous().view(-1), w2_all)
+    A = w13_all.view(E, 2 * ffn, dim).float()
+    B2 = w2_all.view(E, dim, ffn).float()
+    xr = x.detach().float().requires_grad_(True)
+    R = layer.router.detach().float().requires_grad_(True)
+    top = (x.detach() @ layer.router.detach().t()).float().topk(k, dim=1)
+    w = torch.softmax((xr @ R.t()).gather(1, top.indices), dim=1)
+    h = torch.einsum("td,tkfd->tkf", xr, A[top.indices])
+    a = F.silu(h[..., :ffn]) * h[..., ffn:]
+    y = torch.einsum("tkf,tkdf->tkd", a, B2[top.indices])
+    ref = (y * w.unsqueeze(2)).sum(1)
+    (ref * G.float()).sum().backward()
+    errs = (float((out.float() - ref.detach()).abs().max()), float((x.grad.float() - xr.grad).abs().max()),
+            float((layer.router.grad.float() - R.grad).abs().max()))
+    has_expert_grads = bool(layer.w13.grad is not None and layer.w2.grad is not None and layer.w2.grad.abs().sum() > 0)
+    comm.destroy()
+    return errs, has_expert_grads, El
+
+
+def test_moe_layer_trains_across_processes_on_host():
+    for errs, has_grads, _ in run_ranks(_moe_layer, 2, timeout=300):
+        assert has_grads and errs[0] < 0.03 and errs[1] < 0.05 and errs[2] < 0.1, errs
