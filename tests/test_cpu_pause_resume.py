@@ -184,3 +184,61 @@ def _resident_control(rank, world, uid):
 
 def test_control_segment_stays_resident_by_default():
     assert all(run_ranks(_resident_control, 3))
+
+
+def test_random_alloc_free_pause_resume_sequence_keeps_contents_and_leaks_nothing():
+    """Process-level scope (ncclMemAlloc memory, no communicator): a seeded random walk of
+    allocate / free / pause / resume; every live buffer keeps its address and contents across
+    every pause, allocations are refused while paused, nothing is left mapped at the end."""
+    import ctypes
+    import random
+    os.environ["AMEM_BACKEND"] = "mock"
+    from asystem_amem_b200 import NcclError, backend_usage, mem_alloc, mem_free, mem_stats, pause_all, resume_all
+    rnd = random.Random(2024)
+    base = backend_usage()["physical_bytes"]
+    live = {}                                    # ptr -> (size, seed)
+    paused = False
+
+    def fill(ptr, size, seed):
+        buf = (ctypes.c_uint8 * size).from_address(ptr)
+        for i in range(0, size, 4093):
+            buf[i] = (i * 31 + seed) & 0xFF
+
+    def intact(ptr, size, seed):
+        buf = (ctypes.c_uint8 * size).from_address(ptr)
+        return all(buf[i] == ((i * 31 + seed) & 0xFF) for i in range(0, size, 4093))
+
+    pauses = 0
+    for step in range(200):
+        action = rnd.choice(["alloc", "alloc", "free", "pause", "resume"])
+        if action == "alloc":
+            size = rnd.choice([1, 4096, 70_000, 1 << 20, 3 << 20])
+            if paused:
+                with pytest.raises(NcclError):
+                    mem_alloc(size)
+            elif len(live) < 24:
+                p = mem_alloc(size)
+                assert p not in live
+                live[p] = (size, step)
+                fill(p, size, step)
+        elif action == "free" and live and not paused:
+            p = rnd.choice(sorted(live))
+            size, seed = live.pop(p)
+            assert intact(p, size, seed)
+            mem_free(p)
+        elif action == "pause" and not paused:
+            pause_all()
+            paused = True
+            pauses += 1
+            assert backend_usage()["physical_bytes"] == base, "a pause must return every physical byte"
+        elif action == "resume" and paused:
+            resume_all()
+            paused = False
+            assert all(intact(p, s, seed) for p, (s, seed) in live.items())
+    if paused:
+        resume_all()
+    assert pauses > 10 and all(intact(p, s, seed) for p, (s, seed) in live.items())
+    for p in sorted(live):
+        mem_free(p)
+    assert backend_usage()["physical_bytes"] == base
+    assert mem_stats()["live_bytes"] == 0 or backend_usage()["physical_bytes"] == base
