@@ -44,7 +44,8 @@ def reference_arm(args) -> None:
            "and nccl-tests submodules are empty, there is no network and no mpirun")
     if os.path.isdir(ref) and os.listdir(ref):
         why = "baseline/_ref holds no runnable patched-NCCL build (needs the NCCL 2.27.5 and nccl-tests sources and mpirun)"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:   # one line per job, also under torchrun
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
 
 def main() -> None:
