@@ -207,3 +207,14 @@ def test_python_switch_example_runs_on_the_mock_backend():
     run = subprocess.run([sys.executable, os.path.join(root, "examples", "train_infer_switch.py"), "--cpu", "--cycles", "2"],
                          capture_output=True, text=True, timeout=300, env=env)
     assert run.returncode == 0 and "switch example ok" in run.stdout, (run.stdout, run.stderr[-3000:])
+
+
+def test_timing_helpers_without_a_gpu():
+    from asystem_amem_b200.utils.timing import ClockSampler, load_measured_peaks
+    peaks = load_measured_peaks()
+    assert peaks["hbm_gbs"] > 1000 and peaks["bf16_tflops"] > 100 and peaks["source"] in ("measured", "fallback")
+    s = ClockSampler(0, period_s=None)          # no thread: samples only on request
+    with s:
+        s.sample_now()
+    out = s.summary()
+    assert set(out) == {"sm_mhz", "sm_max_mhz", "reasons", "samples"} and out["reasons"] == []
