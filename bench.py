@@ -23,9 +23,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
