@@ -70,7 +70,11 @@ inline void log_write(int level, const char* file, const char* func, int line, c
     n = snprintf(out, sizeof(out), "AMEM [%s] pid:%d %s:%s:%d %s\n", names[level], (int)getpid(),
                  base, func, line, msg);
   }
-  if (n > (int)sizeof(out)) n = sizeof(out);
+  if (n >= (int)sizeof(out)) {  // cut: keep the line well-formed (closing quote / brace, newline)
+    n = (int)sizeof(out) - 1;
+    if (log_json()) memcpy(out + n - 3, "\"}\n", 3);
+    else out[n - 1] = '\n';
+  }
   ssize_t w = write(2, out, (size_t)n);
   (void)w;
 }

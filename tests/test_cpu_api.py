@@ -218,3 +218,22 @@ def test_timing_helpers_without_a_gpu():
         s.sample_now()
     out = s.summary()
     assert set(out) == {"sm_mhz", "sm_max_mhz", "reasons", "samples"} and out["reasons"] == []
+
+
+def test_json_log_lines_are_well_formed(tmp_path):
+    """AMEM_LOG_JSON=1: every log line is one JSON object (level, pid, time, place, message)."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys; sys.path.insert(0, %r)\n"
+            "from asystem_amem_b200 import Communicator, get_unique_id, mem_stats\n"
+            "c = Communicator(1, 0, get_unique_id()); c.pause(); c.resume(); mem_stats(print_too=True); c.destroy()\n" % root)
+    env = dict(os.environ, AMEM_BACKEND="mock", AMEM_LOG_JSON="1", GMM_LOG="5", GMM_IPC_DIR=str(tmp_path))
+    run = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120, env=env)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = [l for l in run.stderr.splitlines() if l.startswith("{")]
+    assert len(lines) >= 3
+    for l in lines:
+        rec = json.loads(l)
+        assert rec["amem"] in ("FATAL", "ERROR", "WARN", "INFO", "DEBUG", "VERBOSE") and rec["pid"] > 0 and ":" in rec["at"] and "msg" in rec
