@@ -12,6 +12,7 @@ through ctypes); here the same calls plus the collectives sit behind one Communi
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 from typing import Optional
 
@@ -99,6 +100,27 @@ def pause_all() -> None:
 
 def resume_all() -> None:
     B.check(B.load_library().ncclResume(None), "ncclResume")
+
+
+@contextlib.contextmanager
+def paused(*comms):
+    """``with paused():`` hands every communicator (and ncclMemAlloc buffer) of the process back
+    to the driver for the duration of the block; ``with paused(a, b):`` only the named
+    communicators.  Everything is resumed on the way out, also when the block raises.  Every rank
+    must enter and leave the block, like ncclPause / ncclResume themselves."""
+    if comms:
+        for c in comms:
+            c.pause()
+    else:
+        pause_all()
+    try:
+        yield
+    finally:
+        if comms:
+            for c in comms:
+                c.resume()
+        else:
+            resume_all()
 
 
 def process_pause_resume_stats() -> dict:

@@ -237,3 +237,22 @@ def test_json_log_lines_are_well_formed(tmp_path):
     for l in lines:
         rec = json.loads(l)
         assert rec["amem"] in ("FATAL", "ERROR", "WARN", "INFO", "DEBUG", "VERBOSE") and rec["pid"] > 0 and ":" in rec["at"] and "msg" in rec
+
+
+def test_paused_context_manager():
+    os.environ["AMEM_BACKEND"] = "mock"
+    from asystem_amem_b200 import Communicator, NcclError, backend_usage, get_unique_id, paused
+    c = Communicator(1, 0, get_unique_id())
+    x = np.ones(10, dtype=np.float32)
+    held = backend_usage()["physical_bytes"]
+    with paused():                                   # whole process
+        assert backend_usage()["physical_bytes"] < held
+        with pytest.raises(NcclError):
+            c.all_reduce(x)
+    c.all_reduce(x)
+    with pytest.raises(RuntimeError):
+        with paused(c):                              # one communicator; resumed although the block raises
+            raise RuntimeError("work failed while paused")
+    assert backend_usage()["physical_bytes"] == held
+    c.all_reduce(x)
+    c.destroy()
