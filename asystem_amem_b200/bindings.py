@@ -24,7 +24,8 @@ RESULT_NAMES = {
 }
 # ncclDataType_t / ncclRedOp_t
 DTYPES = {"int8": 0, "uint8": 1, "int32": 2, "uint32": 3, "int64": 4, "uint64": 5,
-          "float16": 6, "float32": 7, "float64": 8, "bfloat16": 9}
+          "float16": 6, "float32": 7, "float64": 8, "bfloat16": 9,
+          "float8_e4m3fn": 10, "float8_e5m2": 11}   # 8-bit floats: copy collectives only
 OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "avg": 4}
 ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3}
 

@@ -85,7 +85,9 @@ typedef enum {
   ncclFloat32 = 7, ncclFloat = 7,
   ncclFloat64 = 8, ncclDouble = 8,
   ncclBfloat16 = 9,
-  ncclNumTypes = 10
+  ncclFloat8e4m3 = 10, /* copy collectives only: all-gather, all-to-all, broadcast, send/recv */
+  ncclFloat8e5m2 = 11,
+  ncclNumTypes = 12
 } ncclDataType_t;
 
 /* ---- memory ------------------------------------------------------------------------- */

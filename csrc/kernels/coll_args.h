@@ -40,12 +40,14 @@ enum CollKind : int {
 enum Algo : int { kAlgoAuto = 0, kAlgoOneShot = 1, kAlgoTwoShot = 2, kAlgoNvls = 3 };
 
 // ncclDataType_t / ncclRedOp_t numbering.
-enum DType : int { kI8 = 0, kU8 = 1, kI32 = 2, kU32 = 3, kI64 = 4, kU64 = 5, kF16 = 6, kF32 = 7, kF64 = 8, kBF16 = 9 };
+// 8-bit floats are carried by the copy collectives (all-gather, all-to-all, broadcast, send/recv);
+// reductions on them are refused (NCCL numbering: ncclFloat8e4m3 = 10, ncclFloat8e5m2 = 11).
+enum DType : int { kI8 = 0, kU8 = 1, kI32 = 2, kU32 = 3, kI64 = 4, kU64 = 5, kF16 = 6, kF32 = 7, kF64 = 8, kBF16 = 9, kF8E4M3 = 10, kF8E5M2 = 11 };
 enum RedOp : int { kSum = 0, kProd = 1, kMax = 2, kMin = 3, kAvg = 4 };
 
 inline size_t dtype_size(int dt) {
   switch (dt) {
-    case kI8: case kU8: return 1;
+    case kI8: case kU8: case kF8E4M3: case kF8E5M2: return 1;
     case kF16: case kBF16: return 2;
     case kI32: case kU32: case kF32: return 4;
     case kI64: case kU64: case kF64: return 8;

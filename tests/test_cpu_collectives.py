@@ -223,3 +223,37 @@ def test_random_cases_match_numpy_bit_for_bit(world, seed):
     # a small staging segment makes most of the random sizes span several chunks
     for bad in run_ranks(_fuzz, world, args=(seed, 200), timeout=600, env={"AMEM_STAGE_MB": "8", "AMEM_CANARY": "1"}):
         assert bad == [], bad
+
+
+def _fp8(rank, world, uid):
+    import torch
+    from asystem_amem_b200 import Communicator, NcclError
+    comm = Communicator(world, rank, uid)
+    out = {}
+    for dt in (torch.float8_e4m3fn, torch.float8_e5m2):
+        n = 70_001
+        mine = (torch.arange(n) % 13 + rank).float().to(dt)
+        every = [(torch.arange(n) % 13 + r).float().to(dt) for r in range(world)]
+        g = torch.empty(world * n, dtype=dt)
+        comm.all_gather(mine, g)
+        out[f"ag {dt}"] = bool(torch.equal(g.view(torch.uint8), torch.cat(every).view(torch.uint8)))
+        b = mine.clone()
+        comm.broadcast(b, root=world - 1)
+        out[f"bcast {dt}"] = bool(torch.equal(b.view(torch.uint8), every[world - 1].view(torch.uint8)))
+        send = torch.cat([(torch.full((500,), float(rank + j))).to(dt) for j in range(world)])
+        recv = torch.empty_like(send)
+        comm.all_to_all(send, recv)
+        exp = torch.cat([(torch.full((500,), float(j + rank))).to(dt) for j in range(world)])
+        out[f"a2a {dt}"] = bool(torch.equal(recv.view(torch.uint8), exp.view(torch.uint8)))
+        try:
+            comm.all_reduce(mine.clone())
+            out[f"reduce refused {dt}"] = False
+        except NcclError as e:
+            out[f"reduce refused {dt}"] = e.code == 4
+    comm.destroy()
+    return out
+
+
+def test_8bit_floats_ride_the_copy_collectives():
+    for r in run_ranks(_fp8, 2):
+        assert all(r.values()), r
