@@ -242,3 +242,46 @@ def test_random_alloc_free_pause_resume_sequence_keeps_contents_and_leaks_nothin
         mem_free(p)
     assert backend_usage()["physical_bytes"] == base
     assert mem_stats()["live_bytes"] == 0 or backend_usage()["physical_bytes"] == base
+
+
+def _two_groups(rank, world, _uid, share_dir):
+    """Two co-located process groups with their own group ids (the reference's AMEM_GROUPID /
+    ncclSetGroupID): socket names do not collide, and one group pauses while the other works."""
+    import time
+    import numpy as np
+    from asystem_amem_b200 import Communicator, backend_usage, get_unique_id, mem_stats, set_group_id
+    group, local = rank // 2, rank % 2
+    set_group_id(group + 1)                          # before anything is allocated
+    path = os.path.join(share_dir, f"uid_{group}")
+    if local == 0:
+        uid = get_unique_id()
+        with open(path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.rename(path + ".tmp", path)
+    else:
+        for _ in range(400):
+            if os.path.exists(path):
+                break
+            time.sleep(0.05)
+        uid = open(path, "rb").read()
+    comm = Communicator(2, local, uid)
+    out = {"gid": mem_stats()["group_id"] == group + 1}
+    x = np.full(1000, float(local + 1 + 10 * group), dtype=np.float32)
+    comm.all_reduce(x)
+    out["first"] = bool(np.all(x == 3.0 + 20 * group))
+    held = backend_usage()["physical_bytes"]
+    for cycle in range(3):
+        if group == cycle % 2:                       # the groups take turns being parked
+            comm.pause()
+            out[f"released {cycle}"] = backend_usage()["physical_bytes"] < held
+            comm.resume()
+        y = np.full(1000, float(local + 1), dtype=np.float32)
+        comm.all_reduce(y)
+        out[f"sum {cycle}"] = bool(np.all(y == 3.0))
+    comm.destroy()
+    return out
+
+
+def test_two_process_groups_with_their_own_group_ids(tmp_path):
+    for r in run_ranks(_two_groups, 4, args=(str(tmp_path),), timeout=300):
+        assert all(r.values()), r
