@@ -256,3 +256,23 @@ def test_paused_context_manager():
     assert backend_usage()["physical_bytes"] == held
     c.all_reduce(x)
     c.destroy()
+
+
+def test_gemm_planner_invariants_on_random_shapes():
+    import random
+    os.environ["AMEM_BACKEND"] = "mock"
+    from asystem_amem_b200 import bindings as B
+    lib = B.load_library()
+    rnd = random.Random(7)
+    for _ in range(500):
+        M, N, K = rnd.randint(1, 20000), 8 * rnd.randint(1, 2500), 8 * rnd.randint(1, 2500)
+        sms = rnd.choice([1, 16, 132, 148, 160])
+        r, c, s = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        assert lib.amemGemmPlan(M, N, K, sms, ctypes.byref(r), ctypes.byref(c), ctypes.byref(s)) == 0
+        assert r.value in (128, 256) and (r.value == 128 or M > 128)
+        assert 128 <= c.value <= 256 and c.value % 32 == 0
+        assert 1 <= s.value <= 32
+        k_blocks = (K + 63) // 64
+        tiles = -(-M // r.value) * -(-N // c.value)
+        if s.value > 1:                         # a split only of a partly filled last wave, in slices of >= 8 K blocks
+            assert tiles % sms != 0 and s.value * (tiles % sms) <= sms and s.value <= max(1, k_blocks // 8)
