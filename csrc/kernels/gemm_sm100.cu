@@ -16,6 +16,13 @@
 // accumulators so the epilogue of tile i overlaps the main loop of tile i+1.  TMA loads never
 // use cluster multicast and only ever read this GPU's own memory; peers are reached with plain
 // or bulk stores.  Every wait is bounded and ends in an error status, not a hang.
+//
+// The plain mode has two more forms, chosen per problem by the host (gemm_tall_pays,
+// gemm_tail_slices): tiles of 256 x 256 (template parameter MT = 2: two 128-row accumulators fill
+// all 512 TMEM columns and share one B tile, 3 stages of 64 KB, eight epilogue warps), and a
+// split of the partly filled last wave of tiles along K (its CTAs park fp32 partial accumulators
+// in a workspace, meet on a counter, and each sums one band of rows over all slices in slice
+// order, fetching the bands with bulk copies into the idle operand ring).
 #include <algorithm>
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
