@@ -121,6 +121,7 @@ class Comm {
   Status init(const UniqueId& id, int nranks, int rank, const CommConfig& cfg, VmmBackend* be);
   Status setup_multicast();
   Status flush_p2p(cudaStream_t stream);
+  Status after_resume(Status engine_result);   // caller holds mu_
   Status run(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream);
 
   VmmBackend* be_ = nullptr;

@@ -319,8 +319,19 @@ Status Comm::pause(PauseResumeStats* st) {
   if (!pending_.empty()) return fail(kInvalidUsage, "ncclPause inside an open group");
   AMEM_TRY(check_canary());
   Status s = pause_scope(Registry::instance(), be_, id(), dev_, mesh_, opt_, &stats_);
-  if (s == kSuccess) paused_ = true;
+  // a failure after the first release still ends PAUSED (and is reported), so that ncclResume
+  // can bring the memory back; a failure before it leaves the communicator running
+  paused_ = Registry::instance().owner_state(id()) == kRunPaused;
   if (st) *st = stats_;
+  return s;
+}
+
+Status Comm::after_resume(Status s) {
+  paused_ = Registry::instance().owner_state(id()) == kRunPaused;
+  if (s == kSuccess && !paused_ && canary_bytes_) {  // fresh physical memory: the guard starts at zero again
+    s = be_->memset_zero(stage_.va[rank_] + stage_.size - canary_bytes_, canary_bytes_, dev_);
+    if (s == kSuccess) s = be_->copies_sync(dev_);
+  }
   return s;
 }
 
@@ -328,23 +339,21 @@ Status Comm::resume(PauseResumeStats* st) {
   std::lock_guard<std::mutex> g(mu_);
   if (!paused_) return kSuccess;
   Status s = resume_scope(Registry::instance(), be_, id(), dev_, mesh_, opt_, &stats_);
-  if (s == kSuccess) paused_ = false;
-  if (s == kSuccess && canary_bytes_) {  // fresh physical memory: the guard starts at zero again
-    s = be_->memset_zero(stage_.va[rank_] + stage_.size - canary_bytes_, canary_bytes_, dev_);
-    if (s == kSuccess) s = be_->copies_sync(dev_);
-  }
+  s = after_resume(s);
   if (st) *st = stats_;
   return s;
 }
 
 static void accumulate(PauseResumeStats* into, const PauseResumeStats& s, bool pause_part) {
-  if (!into) return;
+  // bytes and counts add up over the scopes; the phase times are those of the one pass
   if (pause_part) {
-    into->quiesce_us += s.quiesce_us;
-    into->offload_us += s.offload_us;
-    into->release_import_us += s.release_import_us;
-    into->release_local_us += s.release_local_us;
-    into->pause_barrier_us += s.pause_barrier_us;
+    into->quiesce_us = s.quiesce_us;
+    into->offload_us = s.offload_us;
+    into->release_import_us = s.release_import_us;
+    into->release_local_us = s.release_local_us;
+    into->pause_barrier_us = s.pause_barrier_us;
+    into->free_before_pause = s.free_before_pause;
+    into->free_after_pause = s.free_after_pause;
     into->bytes_offloaded += s.bytes_offloaded;
     into->bytes_released_local += s.bytes_released_local;
     into->bytes_released_peer += s.bytes_released_peer;
@@ -352,137 +361,128 @@ static void accumulate(PauseResumeStats* into, const PauseResumeStats& s, bool p
     into->n_release_local += s.n_release_local;
     into->n_release_peer += s.n_release_peer;
   } else {
-    into->create_map_us += s.create_map_us;
-    into->agree_us += s.agree_us;
-    into->exchange_us += s.exchange_us;
-    into->import_us += s.import_us;
-    into->preload_us += s.preload_us;
-    into->resume_barrier_us += s.resume_barrier_us;
+    into->create_map_us = s.create_map_us;
+    into->agree_us = s.agree_us;
+    into->exchange_us = s.exchange_us;
+    into->import_us = s.import_us;
+    into->preload_us = s.preload_us;
+    into->resume_barrier_us = s.resume_barrier_us;
+    into->free_after_resume = s.free_after_resume;
     into->bytes_preloaded += s.bytes_preloaded;
   }
 }
 
+static std::mutex g_all_mu;   // one process-wide pause or resume at a time
 
-// Runs fn on every live communicator in creation order.  Several ranks of ONE communicator may
-// live in this process (emulated ranks, ncclCommInitAll): their pause/resume steps contain
-// cross-rank barriers, so those ranks run on helper threads side by side.
-static Status for_each_comm_grouped(const std::function<Status(Comm*)>& fn) {
-  std::vector<Comm*> comms = Comm::all();
-  std::vector<uint64_t> order;
-  for (Comm* c : comms)
-    if (std::find(order.begin(), order.end(), c->group_key()) == order.end()) order.push_back(c->group_key());
-  for (uint64_t cid : order) {
-    std::vector<Comm*> members;
-    for (Comm* c : comms)
-      if (c->group_key() == cid) members.push_back(c);
-    if (members.size() == 1) {
-      AMEM_TRY(fn(members[0]));
-      continue;
-    }
-    std::vector<Status> res(members.size(), kSuccess);
-    std::vector<std::string> msgs(members.size());
-    std::vector<std::thread> th;
-    for (size_t i = 0; i < members.size(); ++i) {
-      th.emplace_back([&, i] {
-        if (members[i]->backend()->is_device()) cudaSetDevice(members[i]->device());
-        res[i] = fn(members[i]);
-        if (res[i] != kSuccess) msgs[i] = last_error_slot();
-      });
-    }
-    for (auto& t : th) t.join();
-    for (size_t i = 0; i < members.size(); ++i)
-      if (res[i] != kSuccess) return fail(res[i], "%s", msgs[i].c_str());
-  }
-  return kSuccess;
-}
-
-// Process-wide pause: every communicator in creation order (all ranks created them in the
-// same order, so the per-communicator barriers line up), then allocations that belong to no
-// communicator (ncclMemAlloc).  New allocations are refused until resume.
+// Process-wide pause: ONE engine pass over every communicator of the process plus the
+// allocations that belong to no communicator (ncclMemAlloc).  Every rank holds its communicators
+// in the same creation order, so the per-communicator messages line up; within the pass all
+// communicators' messages are sent before any is awaited.  Ranks of one communicator that live in
+// this process (emulated ranks, ncclCommInitAll) are served by the same pass.  New allocations
+// are refused until resume.
 Status Comm::pause_all(PauseResumeStats* st) {
+  std::lock_guard<std::mutex> all_lock(g_all_mu);
   Registry& reg = Registry::instance();
   PauseResumeStats total;
   memset(&total, 0, sizeof(total));
   double t0 = now_ms();
-  VmmBackend* be = nullptr;
-  int dev = 0;
-  bool first = true;
-  std::mutex acc_mu;
-  AMEM_TRY(for_each_comm_grouped([&](Comm* c) -> Status {
-    PauseResumeStats s;
-    memset(&s, 0, sizeof(s));
-    AMEM_TRY(c->pause(&s));
-    std::lock_guard<std::mutex> g(acc_mu);
-    if (first) total.free_before_pause = s.free_before_pause;
-    first = false;
-    total.free_after_pause = s.free_after_pause;
-    accumulate(&total, s, true);
-    be = c->backend();
-    dev = c->device();
-    return kSuccess;
-  }));
-  if (!be) be = default_backend();
-  if (be) {
-    if (be->is_device()) cudaGetDevice(&dev);
-    PauseResumeStats s;
-    memset(&s, 0, sizeof(s));
-    EngineOptions opt;
-    opt.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
-    if (reg.owner_state(0) != kRunPaused) {
-      AMEM_TRY(pause_scope(reg, be, 0, dev, nullptr, opt, &s));
-      if (first) total.free_before_pause = s.free_before_pause;
-      total.free_after_pause = s.free_after_pause;
-      accumulate(&total, s, true);
-    }
+  std::vector<Comm*> comms = Comm::all();
+  VmmBackend* be = comms.empty() ? default_backend() : comms[0]->backend();
+  if (!be) return kSuccess;
+  std::vector<Comm*> active;
+  for (Comm* c : comms) {
+    std::lock_guard<std::mutex> g(c->mu_);
+    if (c->paused_) continue;
+    if (!c->pending_.empty()) return fail(kInvalidUsage, "ncclPause inside an open group");
+    AMEM_TRY(c->check_canary());
+    active.push_back(c);
   }
-  reg.set_process_paused(true);
+  std::vector<PauseResumeStats> stats(active.size() + 1);
+  for (auto& s : stats) memset(&s, 0, sizeof(s));
+  std::vector<EngineScope> scopes(active.size() + 1);
+  for (size_t i = 0; i < active.size(); ++i) {
+    scopes[i].owner = active[i]->id();
+    scopes[i].dev = active[i]->dev_;
+    scopes[i].px = active[i]->mesh_;
+    scopes[i].opt = active[i]->opt_;
+    scopes[i].stats = &stats[i];
+  }
+  EngineScope& proc = scopes.back();   // process-level allocations
+  proc.owner = 0;
+  proc.dev = 0;
+  if (be->is_device()) cudaGetDevice(&proc.dev);
+  proc.opt.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
+  proc.stats = &stats.back();
+  Status s = pause_scopes(reg, be, scopes);
+  std::string why = last_error_slot();
+  bool all_paused = reg.owner_state(0) == kRunPaused;
+  for (size_t i = 0; i < active.size(); ++i) {
+    Comm* c = active[i];
+    c->paused_ = reg.owner_state(c->id()) == kRunPaused;
+    all_paused = all_paused && c->paused_;
+    c->stats_ = stats[i];
+  }
+  for (auto& x : stats) accumulate(&total, x, true);
+  if (all_paused) reg.set_process_paused(true);
   total.pause_total_us = (now_ms() - t0) * 1000.0;
   if (st) *st = total;
-  return kSuccess;
+  last_error_slot() = why;
+  return s;
 }
 
 Status Comm::resume_all(PauseResumeStats* st) {
+  std::lock_guard<std::mutex> all_lock(g_all_mu);
   Registry& reg = Registry::instance();
   PauseResumeStats total;
   memset(&total, 0, sizeof(total));
   double t0 = now_ms();
+  std::vector<Comm*> comms = Comm::all();
+  VmmBackend* be = comms.empty() ? default_backend() : comms[0]->backend();
+  if (!be) return kSuccess;
   reg.set_process_paused(false);
-  VmmBackend* be = nullptr;
-  int dev = 0;
-  std::mutex acc_mu;
-  Status all_st = for_each_comm_grouped([&](Comm* c) -> Status {
-    PauseResumeStats s;
-    memset(&s, 0, sizeof(s));
-    AMEM_TRY(c->resume(&s));
-    std::lock_guard<std::mutex> g(acc_mu);
-    total.free_after_resume = s.free_after_resume;
-    accumulate(&total, s, false);
-    be = c->backend();
-    dev = c->device();
-    return kSuccess;
-  });
-  if (all_st != kSuccess) {
-    reg.set_process_paused(true);
-    return all_st;
+  std::vector<Comm*> active;
+  for (Comm* c : comms)
+    if (c->paused_) active.push_back(c);
+  std::vector<PauseResumeStats> stats(active.size() + 1);
+  for (auto& s : stats) memset(&s, 0, sizeof(s));
+  std::vector<EngineScope> scopes(active.size() + 1);
+  for (size_t i = 0; i < active.size(); ++i) {
+    scopes[i].owner = active[i]->id();
+    scopes[i].dev = active[i]->dev_;
+    scopes[i].px = active[i]->mesh_;
+    scopes[i].opt = active[i]->opt_;
+    scopes[i].stats = &stats[i];
   }
-  if (!be) be = default_backend();
-  if (be && reg.owner_state(0) == kRunPaused) {
-    if (be->is_device()) cudaGetDevice(&dev);
-    PauseResumeStats s;
-    memset(&s, 0, sizeof(s));
-    EngineOptions opt;
-    opt.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
-    Status r = resume_scope(reg, be, 0, dev, nullptr, opt, &s);
-    if (r != kSuccess) {
-      reg.set_process_paused(true);
-      return r;
+  EngineScope& proc = scopes.back();
+  proc.owner = 0;
+  proc.dev = 0;
+  if (be->is_device()) cudaGetDevice(&proc.dev);
+  proc.opt.offload_free_tag = (int)env_long("AMEM_NCCL_OFFLOAD_FREE_TAG", -1);
+  proc.stats = &stats.back();
+  Status s = resume_scopes(reg, be, scopes);
+  std::string why = last_error_slot();
+  bool any_paused = reg.owner_state(0) == kRunPaused;
+  for (size_t i = 0; i < active.size(); ++i) {
+    Comm* c = active[i];
+    std::lock_guard<std::mutex> g(c->mu_);
+    Status a = c->after_resume(scopes[i].result);
+    if (a != kSuccess && s == kSuccess) {
+      s = a;
+      why = last_error_slot();
     }
-    total.free_after_resume = s.free_after_resume;
-    accumulate(&total, s, false);
+    any_paused = any_paused || c->paused_;
+    PauseResumeStats keep = c->stats_;   // pause half stays, resume half is replaced
+    accumulate(&keep, stats[i], false);
+    keep.bytes_preloaded = stats[i].bytes_preloaded;
+    keep.resume_total_us = stats[i].resume_total_us;
+    c->stats_ = keep;
   }
+  for (auto& x : stats) accumulate(&total, x, false);
+  if (any_paused) reg.set_process_paused(true);   // something did not come back: still refuse collectives; ncclResume may be retried
   total.resume_total_us = (now_ms() - t0) * 1000.0;
   if (st) *st = total;
-  return kSuccess;
+  last_error_slot() = why;
+  return s;
 }
 
 }  // namespace amem

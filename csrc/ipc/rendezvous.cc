@@ -55,6 +55,9 @@ Status Mesh::connect(const UniqueId& id, int rank, int nranks, Mesh** out) {
   m->comm_id_ = id.nonce | 1;  // never 0: owner 0 means "process level" in the registry
   m->op_timeout_ms_ = (double)env_long("AMEM_OP_TIMEOUT_MS", 30000);
   m->socks_.assign(nranks, -1);
+  m->held_.assign(nranks, Frame{});
+  m->has_held_.assign(nranks, 0);
+  m->held_fd_.assign(nranks, -1);
   if (nranks == 1) {
     *out = m;
     return kSuccess;
@@ -110,6 +113,10 @@ Mesh::~Mesh() { shutdown_all(); }
 
 void Mesh::shutdown_all() {
   std::lock_guard<std::mutex> g(mu_);
+  for (int& h : held_fd_) {
+    if (h >= 0) close(h);
+    h = -1;
+  }
   for (int& s : socks_) {
     if (s >= 0) close(s);
     s = -1;
@@ -118,61 +125,153 @@ void Mesh::shutdown_all() {
 
 Status Mesh::send_frame(int to, uint16_t op, uint32_t arg, uint64_t val, int fd) {
   if (to < 0 || to >= nranks_ || socks_[to] < 0) return fail(kRemoteError, "no connection to rank %d", to);
-  Frame f{kFrameMagic, op, (uint16_t)rank_, comm_id_, seq_, arg, val};
+  Frame f{kFrameMagic, op, (uint16_t)rank_, comm_id_, epoch_, arg, val};
   Status st = uds_send(socks_[to], &f, sizeof(f), fd, Deadline::after_ms(op_timeout_ms_));
   if (st != kSuccess) LOGW("rank %d: send op %u to rank %d failed: %s", rank_, op, to, last_error_slot().c_str());
   return st;
 }
 
+void Mesh::begin_attempt() {
+  std::lock_guard<std::mutex> g(mu_);
+  ++epoch_;
+}
+
+// Frames carry the sender's attempt number (one per pause or resume pass; every rank makes the
+// same sequence of passes).  A frame of an earlier attempt is what a failed attempt left in the
+// socket: it is discarded.  A frame of this attempt with another op, or of a later attempt, means
+// the message asked for was lost: the frame is kept for the receive that will ask for it, and this
+// receive fails at once.  So one lost message fails one attempt; the next attempt starts clean.
 Status Mesh::recv_frame(int from, uint16_t op, Frame* f, int* fd) {
   if (from < 0 || from >= nranks_ || socks_[from] < 0) return fail(kRemoteError, "no connection to rank %d", from);
-  Status st = uds_recv(socks_[from], f, sizeof(*f), fd, Deadline::after_ms(op_timeout_ms_));
-  if (st != kSuccess) {
-    std::string why = last_error_slot();
-    return fail(st, "rank %d waiting for op %u from rank %d: %s", rank_, op, from, why.c_str());
+  if (fd) *fd = -1;
+  Deadline dl = Deadline::after_ms(op_timeout_ms_);
+  for (;;) {
+    int got = -1;
+    if (has_held_[from]) {
+      Frame& h = held_[from];
+      if (h.seq < epoch_) {          // left over from an abandoned attempt
+        if (held_fd_[from] >= 0) close(held_fd_[from]);
+        held_fd_[from] = -1;
+        has_held_[from] = 0;
+        continue;
+      }
+      if (h.seq == epoch_ && h.op == op) {
+        *f = h;
+        got = held_fd_[from];
+        held_fd_[from] = -1;
+        has_held_[from] = 0;
+        if (fd) *fd = got;
+        else if (got >= 0) close(got);
+        return kSuccess;
+      }
+      return fail(kRemoteError, "rank %d: the op %u message of rank %d never arrived (its op %u message of attempt %u is already here)",
+                  rank_, op, from, h.op, h.seq);
+    }
+    Status st = uds_recv(socks_[from], f, sizeof(*f), &got, dl);
+    if (st != kSuccess) {
+      std::string why = last_error_slot();
+      return fail(st, "rank %d waiting for op %u from rank %d: %s", rank_, op, from, why.c_str());
+    }
+    if (f->magic != kFrameMagic || f->comm != comm_id_ || f->src != from) {
+      if (got >= 0) close(got);
+      return fail(kInternalError, "rank %d: corrupt frame from rank %d", rank_, from);
+    }
+    if (f->op == kOpAbort) {
+      if (got >= 0) close(got);
+      return fail(kRemoteError, "rank %d aborted the communicator", from);
+    }
+    if (f->seq < epoch_) {           // stale: drop it and read on
+      if (got >= 0) close(got);
+      continue;
+    }
+    if (f->seq == epoch_ && f->op == op) {
+      if (fd) *fd = got;
+      else if (got >= 0) close(got);
+      return kSuccess;
+    }
+    held_[from] = *f;
+    held_fd_[from] = got;
+    has_held_[from] = 1;
+    return fail(kRemoteError, "rank %d: expected op %u from rank %d in attempt %u, got op %u of attempt %u (a message was lost)", rank_, op,
+                from, epoch_, f->op, f->seq);
   }
-  if (f->magic != kFrameMagic || f->comm != comm_id_ || f->src != from) {
-    if (fd && *fd >= 0) close(*fd);
-    return fail(kInternalError, "rank %d: corrupt frame from rank %d", rank_, from);
+}
+
+Status Mesh::barrier_begin() {
+  std::lock_guard<std::mutex> g(mu_);
+  ++seq_;
+  Status first = kSuccess;
+  for (int p = 0; p < nranks_; ++p) {
+    if (p == rank_) continue;
+    Status s = send_frame(p, kOpBarrier, 0, 0, -1);   // every peer gets its frame even if one send fails
+    if (s != kSuccess && first == kSuccess) first = s;
   }
-  if (f->op == kOpAbort) {
-    if (fd && *fd >= 0) close(*fd);
-    return fail(kRemoteError, "rank %d aborted the communicator", from);
+  return first;
+}
+
+Status Mesh::barrier_end() {
+  std::lock_guard<std::mutex> g(mu_);
+  Status first = kSuccess;
+  std::string why;
+  for (int p = 0; p < nranks_; ++p) {
+    if (p == rank_) continue;
+    Frame f;
+    Status s = recv_frame(p, kOpBarrier, &f, nullptr);
+    if (s != kSuccess && first == kSuccess) {
+      first = s;
+      why = last_error_slot();
+    }
   }
-  if (f->op != op) {
-    if (fd && *fd >= 0) close(*fd);
-    return fail(kInternalError, "rank %d: expected op %u from rank %d, got %u (ranks called different operations)", rank_, op, from, f->op);
-  }
-  return kSuccess;
+  if (first != kSuccess) last_error_slot() = why;
+  return first;
 }
 
 Status Mesh::barrier() {
-  std::lock_guard<std::mutex> g(mu_);
-  ++seq_;
-  for (int p = 0; p < nranks_; ++p)
-    if (p != rank_) AMEM_TRY(send_frame(p, kOpBarrier, 0, 0, -1));
-  for (int p = 0; p < nranks_; ++p) {
-    if (p == rank_) continue;
-    Frame f;
-    AMEM_TRY(recv_frame(p, kOpBarrier, &f, nullptr));
-  }
-  return kSuccess;
+  AMEM_TRY(barrier_begin());
+  return barrier_end();
 }
 
-Status Mesh::all_ok(bool mine, bool* all) {
+Status Mesh::vote_begin(bool mine) {
   std::lock_guard<std::mutex> g(mu_);
   ++seq_;
-  bool acc = mine;
-  for (int p = 0; p < nranks_; ++p)
-    if (p != rank_) AMEM_TRY(send_frame(p, kOpVote, mine ? 1 : 0, 0, -1));
+  pending_vote_ = mine;
+  Status first = kSuccess;
+  for (int p = 0; p < nranks_; ++p) {
+    if (p == rank_) continue;
+    Status s = send_frame(p, kOpVote, mine ? 1 : 0, 0, -1);
+    if (s != kSuccess && first == kSuccess) first = s;
+  }
+  return first;
+}
+
+Status Mesh::vote_end(bool* all) {
+  std::lock_guard<std::mutex> g(mu_);
+  bool acc = pending_vote_;
+  Status first = kSuccess;
+  std::string why;
   for (int p = 0; p < nranks_; ++p) {
     if (p == rank_) continue;
     Frame f;
-    AMEM_TRY(recv_frame(p, kOpVote, &f, nullptr));
+    Status s = recv_frame(p, kOpVote, &f, nullptr);
+    if (s != kSuccess) {
+      if (first == kSuccess) {
+        first = s;
+        why = last_error_slot();
+      }
+      acc = false;
+      continue;
+    }
     acc = acc && f.arg != 0;
   }
   *all = acc;
-  return kSuccess;
+  if (first != kSuccess) last_error_slot() = why;
+  return first;
+}
+
+Status Mesh::all_ok(bool mine, bool* all) {
+  Status s = vote_begin(mine);
+  Status e = vote_end(all);
+  return s != kSuccess ? s : e;
 }
 
 Status Mesh::send_fd(int to, uint32_t sym_id, uint64_t size, int fd) {
@@ -180,11 +279,20 @@ Status Mesh::send_fd(int to, uint32_t sym_id, uint64_t size, int fd) {
   return send_frame(to, kOpFd, sym_id, size, fd);
 }
 
+Status Mesh::send_no_fd(int to, uint32_t sym_id) {
+  std::lock_guard<std::mutex> g(mu_);
+  return send_frame(to, kOpFd, sym_id, ~0ull, -1);
+}
+
 Status Mesh::recv_fd(int from, uint32_t* sym_id, uint64_t* size, int* fd) {
   std::lock_guard<std::mutex> g(mu_);
   Frame f;
   int got = -1;
   AMEM_TRY(recv_frame(from, kOpFd, &f, &got));
+  if (f.val == ~0ull) {
+    if (got >= 0) close(got);
+    return fail(kRemoteError, "rank %d could not export its segment %u", from, f.arg);
+  }
   if (got < 0) return fail(kSystemError, "rank %d: handle message from rank %d carried no file descriptor", rank_, from);
   *sym_id = f.arg;
   *size = f.val;

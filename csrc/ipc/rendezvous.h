@@ -44,8 +44,14 @@ class Mesh : public PeerExchange {
 
   Status barrier() override;
   Status all_ok(bool mine, bool* all) override;
+  Status barrier_begin() override;
+  Status barrier_end() override;
+  Status vote_begin(bool mine) override;
+  Status vote_end(bool* all) override;
   Status send_fd(int to, uint32_t sym_id, uint64_t size, int fd) override;
   Status recv_fd(int from, uint32_t* sym_id, uint64_t* size, int* fd) override;
+  Status send_no_fd(int to, uint32_t sym_id) override;
+  void begin_attempt() override;
 
   // Every rank contributes `len` bytes (at most 16 KiB); `all` receives nranks * len.
   Status allgather(const void* mine, size_t len, void* all);
@@ -64,6 +70,13 @@ class Mesh : public PeerExchange {
   uint64_t comm_id_ = 0;
   uint32_t seq_ = 0;
   std::vector<int> socks_;  // socks_[peer], -1 for self
+  // A frame of a LATER step that arrived where an earlier one was expected (the earlier one was
+  // lost): kept here, with its descriptor, and handed to the receive that asks for it, so one
+  // lost message fails one attempt instead of putting the whole stream out of step.
+  std::vector<Frame> held_;
+  std::vector<char> has_held_;
+  std::vector<int> held_fd_;
+  uint32_t epoch_ = 0;      // attempt number stamped on every frame sent
   std::mutex mu_;
 };
 

@@ -44,6 +44,15 @@ class VmmBackend {
   // Map `handle` at `va` and give device `dev` read/write access.
   virtual Status map(uint64_t va, size_t size, uint64_t handle, int dev) = 0;
   virtual Status unmap(uint64_t va, size_t size) = 0;
+  // Map now, grant access later: a backend whose access call is expensive maps only and sets
+  // *needs_access; the caller then covers any number of adjacent mappings with ONE grant_access.
+  // The default maps with access at once.
+  virtual Status map_deferred(uint64_t va, size_t size, uint64_t handle, int dev, bool* needs_access) {
+    *needs_access = false;
+    return map(va, size, handle, dev);
+  }
+  // Read/write access for device `dev` to [va, va+size), all of which must be mapped.
+  virtual Status grant_access(uint64_t va, size_t size, int dev) { (void)va; (void)size; (void)dev; return kSuccess; }
 
   // Pinned host shadows and the side-stream copies of pause/resume
   // (the reference's amem_launchOffload / amem_lauchPreload, amem_nccl.h:304-327).

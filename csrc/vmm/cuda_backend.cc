@@ -257,6 +257,30 @@ class CudaBackend : public VmmBackend {
     mappings_.fetch_add(1);
     return kSuccess;
   }
+  Status map_deferred(uint64_t va, size_t size, uint64_t handle, int dev, bool* needs_access) override {
+    (void)dev;
+    if (should_fail("map")) return fail(kCudaError, "cuMemMap: injected failure");
+    static const long defer = env_long("AMEM_DEFER_ACCESS", 1);
+    if (!defer) {
+      *needs_access = false;
+      return map(va, size, handle, dev);
+    }
+    Timed t(kTMap);
+    DRV(drv().MemMap((CUdeviceptr)va, size, 0, (CUmemGenericAllocationHandle)handle, 0), "cuMemMap");
+    mappings_.fetch_add(1);
+    *needs_access = true;
+    return kSuccess;
+  }
+  Status grant_access(uint64_t va, size_t size, int dev) override {
+    Timed t(kTAccess);
+    CUmemAccessDesc a;
+    memset(&a, 0, sizeof(a));
+    a.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    a.location.id = dev;
+    a.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    DRV(drv().MemSetAccess((CUdeviceptr)va, size, &a, 1), "cuMemSetAccess");
+    return kSuccess;
+  }
   Status unmap(uint64_t va, size_t size) override {
     {
       Timed t(kTUnmap);

@@ -108,6 +108,92 @@ def test_allocation_failure_on_resume_rolls_every_rank_back():
         assert rolled_back and guarded and same, res
 
 
+def _fault_after_the_vote(rank, world, uid, what, nth, who):
+    """A failure AFTER every rank agreed that its memory is back (handle export, descriptor
+    passing, import, map): every rank must end PAUSED again, with nothing mapped, and a second
+    ncclResume must succeed."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator, NcclError, backend_usage, inject
+    comm = Communicator(world, rank, uid)
+    x = (np.arange(5000, dtype=np.float32) + rank)
+    first = x.copy()
+    comm.all_reduce(first)
+    comm.pause()
+    if rank == who:
+        inject(what, nth)
+    try:
+        comm.resume()
+        code = 0
+    except NcclError as e:
+        code = e.code
+    rolled_back = backend_usage()["mappings"] == 0 and backend_usage()["physical_bytes"] == 0
+    try:
+        comm.all_reduce(x.copy())
+        guarded = False
+    except NcclError as e:
+        guarded = e.code == 5
+    comm.resume()  # nothing injected now
+    again = x.copy()
+    comm.all_reduce(again)
+    comm.pause()   # and the communicator keeps cycling
+    comm.resume()
+    third = x.copy()
+    comm.all_reduce(third)
+    comm.destroy()
+    return code, rolled_back, guarded, bool(np.array_equal(first, again) and np.array_equal(first, third))
+
+
+# with two ranks and the control segment pausable, a resuming rank sends: its first vote, one handle
+# per segment (2), its second vote ("nofd" counts only messages that carry a descriptor); and maps: its own two segments, then the peer's two
+@pytest.mark.parametrize("what,nth,who", [("uds:drop", 2, 0), ("uds:nofd", 2, 0), ("vmm:export", 1, 0), ("vmm:import", 1, 1),
+                                           ("vmm:import", 2, 1), ("vmm:map", 3, 1)])
+def test_failure_after_the_resume_vote_rolls_back_and_resume_can_be_retried(what, nth, who):
+    res = run_ranks(_fault_after_the_vote, 2, args=(what, nth, who), env=FAST)
+    for code, rolled_back, guarded, same in res:
+        assert code != 0 and rolled_back and guarded and same, res
+
+
+def _pause_all_fault(rank, world, uid):
+    """The same through ncclPause(NULL) / ncclResume(NULL) with two communicators and user memory:
+    one pass serves all of them; after the failed pass everything is PAUSED, after the retry
+    everything works."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator, NcclError, inject, pause_all, resume_all
+    comm = Communicator(world, rank, uid)
+    sub = comm.split(0, rank)
+    x = (np.arange(3000, dtype=np.float32) + rank)
+    a = x.copy()
+    comm.all_reduce(a)
+    b = x.copy()
+    sub.all_reduce(b)
+    pause_all()
+    if rank == 1:
+        inject("vmm:import", 3)      # one of the second communicator's imports
+    try:
+        resume_all()
+        code = 0
+    except NcclError as e:
+        code = e.code
+    try:
+        comm.all_reduce(x.copy())
+        guarded = False
+    except NcclError as e:
+        guarded = e.code == 5
+    resume_all()
+    a2, b2 = x.copy(), x.copy()
+    comm.all_reduce(a2)
+    sub.all_reduce(b2)
+    sub.destroy()
+    comm.destroy()
+    return code, guarded, bool(np.array_equal(a, a2) and np.array_equal(b, b2))
+
+
+def test_process_wide_resume_failure_is_retried():
+    res = run_ranks(_pause_all_fault, 2, env=FAST)
+    for code, guarded, same in res:
+        assert code != 0 and guarded and same, res
+
+
 def _peer_skips_collective(rank, world, uid):
     import numpy as np
     from asystem_amem_b200 import Communicator, NcclError
