@@ -27,7 +27,7 @@ DTYPES = {"int8": 0, "uint8": 1, "int32": 2, "uint32": 3, "int64": 4, "uint64": 
           "float16": 6, "float32": 7, "float64": 8, "bfloat16": 9,
           "float8_e4m3fn": 10, "float8_e5m2": 11}   # 8-bit floats: copy collectives only
 OPS = {"sum": 0, "prod": 1, "max": 2, "min": 3, "avg": 4}
-ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3}
+ALGOS = {"auto": 0, "oneshot": 1, "twoshot": 2, "nvls": 3, "window": 4}
 
 
 class NcclError(RuntimeError):
@@ -127,6 +127,9 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "amemCheckCanary": [c_void_p],
         "amemDebugDirtyCanary": [c_void_p],
         "amemBackendUsage": [P(c_size_t), P(c_size_t), P(ctypes.c_char_p)],
+        "amemBackendIsDevice": [],
+        "ncclCommWindowRegister": [c_void_p, c_void_p, c_size_t, P(c_void_p), c_int],
+        "ncclCommWindowDeregister": [c_void_p, c_void_p],
         "amemMoeBuffers": [c_void_p, c_int, c_int, P(c_void_p), P(c_void_p)],
         "amemMoeDispatch": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "amemMoeCombine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],

@@ -151,6 +151,49 @@ def mem_free(ptr: int) -> None:
     B.check(B.load_library().ncclMemFree(ctypes.c_void_p(ptr)), "ncclMemFree")
 
 
+class _RawBuffer:
+    """Lets torch view device memory that the library allocated (no copy, no ownership)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class Window:
+    """Memory from ``ncclMemAlloc`` registered with a communicator (``ncclCommWindowRegister``):
+    every rank maps it, all-reduces whose buffers lie inside run in place, and it is saved,
+    released and restored with the communicator on pause / resume.
+
+    Reference parity: the allocations the reference tracks for NCCL's symmetric windows and
+    registered user buffers (nccl_patch/nccl_2.27.5-1.diff:56-58, 630-632)."""
+
+    def __init__(self, comm: "Communicator", ptr: int, nbytes: int, handle: int, owns: bool):
+        self.comm, self.ptr, self.nbytes, self._h, self._owns = comm, ptr, nbytes, handle, owns
+
+    def tensor(self, dtype=None, numel: Optional[int] = None, offset_bytes: int = 0):
+        """A torch view of (part of) this rank's window memory (CUDA backend) or a numpy view
+        (mock backend)."""
+        if self.comm.lib.amemBackendIsDevice():
+            torch = _torch()
+            t = torch.as_tensor(_RawBuffer(self.ptr + offset_bytes, self.nbytes - offset_bytes), device="cuda")
+            if dtype is not None:
+                t = t.view(dtype)
+            return t if numel is None else t[:numel]
+        import numpy as np
+        buf = (ctypes.c_ubyte * (self.nbytes - offset_bytes)).from_address(self.ptr + offset_bytes)
+        arr = np.frombuffer(buf, dtype=np.uint8)
+        if dtype is not None:
+            arr = arr.view(dtype)
+        return arr if numel is None else arr[:numel]
+
+    def free(self) -> None:
+        """Collective: deregisters the window and, if it was made by ``window_alloc``, frees it."""
+        if self._h:
+            B.check(self.comm.lib.ncclCommWindowDeregister(self.comm._h, ctypes.c_void_p(self._h)), "ncclCommWindowDeregister")
+            self._h = 0
+            if self._owns:
+                mem_free(self.ptr)
+
+
 class Communicator:
     """A rank's handle on a communicator (``ncclComm_t``)."""
 
@@ -201,6 +244,16 @@ class Communicator:
     @property
     def handle(self) -> int:
         return self._h.value
+
+    def window_register(self, ptr: int, nbytes: int, _owns: bool = False) -> Window:
+        """Collective: registers memory from :func:`mem_alloc` as a window of this communicator."""
+        w = ctypes.c_void_p()
+        B.check(self.lib.ncclCommWindowRegister(self._h, ctypes.c_void_p(ptr), ctypes.c_size_t(nbytes), ctypes.byref(w), 0), "ncclCommWindowRegister")
+        return Window(self, ptr, nbytes, w.value, _owns)
+
+    def window_alloc(self, nbytes: int) -> Window:
+        """Collective: ``ncclMemAlloc`` + ``ncclCommWindowRegister``; same size on every rank."""
+        return self.window_register(mem_alloc(nbytes), nbytes, _owns=True)
 
     def info(self) -> dict:
         emu, nvls, stage = ctypes.c_int(), ctypes.c_int(), ctypes.c_size_t()

@@ -48,12 +48,32 @@ def restrict_visible_devices(world: int) -> None:
     os.environ["CUDA_VISIBLE_DEVICES"] = ",".join(devs[:world])
 
 
+def point_reference_at_libcuda() -> None:
+    """The plugin dlopen()s libcuda.so.1 from two fixed directories unless CUDA_LIB_PATH names the
+    file (amem_nccl_plugin/gmm_client_cfg.cpp:33-37) and aborts when it finds none; container images
+    keep the driver library elsewhere.  The path the dynamic loader actually resolves is taken from
+    this process's own mappings."""
+    if os.environ.get("CUDA_LIB_PATH"):
+        return
+    try:
+        ctypes.CDLL("libcuda.so.1")
+        with open("/proc/self/maps") as f:
+            for line in f:
+                path = line.split()[-1]
+                if "libcuda.so" in path and os.path.exists(path):
+                    os.environ["CUDA_LIB_PATH"] = path
+                    return
+    except OSError:
+        pass
+
+
 class ReferenceArm:
     def __init__(self, rank: int, world: int, local: int, shared_bytes: int, records: int, stateful_bytes: int, barrier):
         self.rank, self.world, self.local = rank, world, local
         self.barrier = barrier
         os.environ["AMEM_ENABLE"] = "1"            # the plugin is off unless asked (amem_nccl.cpp:711)
         os.environ.setdefault("GMM_LOG", "3")
+        point_reference_at_libcuda()
         # the plugin first, so that the harness resolves against this exact file
         self.plugin = ctypes.CDLL(str(LIB_DIR / "libamem_nccl.so.1"), mode=ctypes.RTLD_GLOBAL)
         self.h = ctypes.CDLL(str(LIB_DIR / "libref_harness.so"))

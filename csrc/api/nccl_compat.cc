@@ -166,18 +166,37 @@ ncclResult_t ncclCommUserRank(const ncclComm_t comm, int* rank) {
   *rank = C(comm)->rank();
   return ncclSuccess;
 }
-ncclResult_t ncclCommRegister(const ncclComm_t, void* buff, size_t, void** handle) {
-  if (handle) *handle = buff;
+// Local registration (not collective, as in NCCL): the buffer is checked and remembered; peers
+// reach user buffers through this library's own staging, so nothing is mapped anywhere.  Memory
+// that peers should reach in place is registered with ncclCommWindowRegister.
+ncclResult_t ncclCommRegister(const ncclComm_t comm, void* buff, size_t size, void** handle) {
+  if (!comm || !buff || !handle) return ncclInvalidArgument;
+  (void)size;
+  *handle = buff;
   return ncclSuccess;
 }
-ncclResult_t ncclCommDeregister(const ncclComm_t, void*) { return ncclSuccess; }
+ncclResult_t ncclCommDeregister(const ncclComm_t comm, void* handle) {
+  if (!comm || !handle) return ncclInvalidArgument;
+  return ncclSuccess;
+}
 
-ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t, ncclWindow_t* win, int) {
+// Collective.  `buff` must come from ncclMemAlloc; the whole allocation becomes a window that
+// every rank maps (and that is bound to a multicast object when the communicator has NVLS).
+// All-reduce calls whose two buffers lie in windows then run in place on them.  The window is
+// tracked: ncclPause saves and releases it with the communicator, ncclResume brings it back at
+// the same addresses on every rank.
+ncclResult_t ncclCommWindowRegister(ncclComm_t comm, void* buff, size_t size, ncclWindow_t* win, int) {
   if (!comm || !win) return ncclInvalidArgument;
-  *win = reinterpret_cast<ncclWindow_t>(buff);  // the push protocol reaches peers through its own staging
-  return ncclSuccess;
+  Window* w = nullptr;
+  Status s = C(comm)->window_register(buff, size, &w);
+  *win = reinterpret_cast<ncclWindow_t>(w);
+  return R(s);
 }
-ncclResult_t ncclCommWindowDeregister(ncclComm_t, ncclWindow_t) { return ncclSuccess; }
+ncclResult_t ncclCommWindowDeregister(ncclComm_t comm, ncclWindow_t win) {
+  if (!comm || !win) return ncclInvalidArgument;
+  if (C(comm)->paused()) return R(fail(kInvalidUsage, "ncclCommWindowDeregister while the communicator is paused"));
+  return R(C(comm)->window_deregister(reinterpret_cast<Window*>(win)));
+}
 
 ncclResult_t ncclCommInitRankScalable(ncclComm_t* newcomm, int nranks, int myrank, int nId, ncclUniqueId* commIds, ncclConfig_t* config) {
   if (!commIds || nId < 1) return ncclInvalidArgument;
@@ -282,8 +301,9 @@ ncclResult_t ncclMemAlloc(void** ptr, size_t size) {
 ncclResult_t ncclMemFree(void* ptr) {
   if (!ptr) return ncclSuccess;
   Allocation a;
-  if (!Registry::instance().find((uint64_t)ptr, &a) || a.owner != 0)
+  if (!Registry::instance().find((uint64_t)ptr, &a) || from_peer(a.type))
     return R(fail(kInvalidArgument, "ncclMemFree: pointer was not returned by ncclMemAlloc"));
+  if (a.owner != 0) return R(fail(kInvalidUsage, "ncclMemFree: the buffer is still registered as a window (ncclCommWindowDeregister first)"));
   VmmBackend* be = default_backend();
   if (a.state != kMemHole) {
     if (be->is_device()) be->device_sync(a.dev);
@@ -501,6 +521,10 @@ ncclResult_t amemBackendTimings(char* buf, size_t len, int reset) {
   std::string s = be->timings(reset != 0);
   snprintf(buf, len, "%s", s.c_str());
   return ncclSuccess;
+}
+int amemBackendIsDevice(void) {
+  VmmBackend* be = default_backend();
+  return be && be->is_device() ? 1 : 0;
 }
 ncclResult_t amemBackendUsage(size_t* physical_bytes, size_t* mappings, const char** backend_name) {
   VmmBackend* be = default_backend();

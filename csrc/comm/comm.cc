@@ -122,7 +122,7 @@ Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cf
   }
   int want_nvls = cfg.nvls >= 0 ? cfg.nvls : (int)env_long("AMEM_NVLS", 1);
   if (device && !emulate && nranks > 1 && all_mc && want_nvls) {
-    Status st = setup_multicast();
+    Status st = setup_multicast(&stage_, stage_.va[rank_]);
     if (st != kSuccess) LOGW("rank %d: NVLS disabled: %s", rank_, last_error_slot().c_str());
   }
   AMEM_TRY(mesh_->barrier());  // everybody's control block is zeroed and mapped
@@ -255,26 +255,27 @@ Status Comm::sym_free(Segment* seg) {
 // rank adds its device, binds its staging memory and maps the multicast address range.  The
 // object and its mapping survive pause; only the binding is undone and redone
 // (the reference does the same for NCCL's NVLS buffers, amem_nccl.cpp:536-538,614-616).
-Status Comm::setup_multicast() {
+Status Comm::setup_multicast(Segment* seg, uint64_t local_va) {
   uint64_t mc = 0;
   Status st = kSuccess;
   size_t mc_gran = 0;
-  st = be_->mc_granularity(nranks_, stage_.size, &mc_gran);
-  bool ok = st == kSuccess && mc_gran && stage_.size % mc_gran == 0;
+  const size_t size = seg->size;
+  st = be_->mc_granularity(nranks_, size, &mc_gran);
+  bool ok = st == kSuccess && mc_gran && size % mc_gran == 0;
   if (ok && rank_ == 0) {
-    st = be_->mc_create(nranks_, stage_.size, &mc);
+    st = be_->mc_create(nranks_, size, &mc);
     ok = st == kSuccess;
   }
   bool all = false;
   AMEM_TRY(mesh_->all_ok(ok, &all));
   if (!all) {
     if (mc) be_->release(mc);
-    return fail(kInvalidUsage, "multicast object could not be created (granularity %zu, staging %zu)", mc_gran, stage_.size);
+    return fail(kInvalidUsage, "multicast object could not be created (granularity %zu, segment %zu)", mc_gran, size);
   }
   if (rank_ == 0) {
     int fd = -1;
     AMEM_TRY(be_->export_fd(mc, &fd));
-    for (int r = 1; r < nranks_ && st == kSuccess; ++r) st = mesh_->send_fd(r, 0xffffffffu, stage_.size, fd);
+    for (int r = 1; r < nranks_ && st == kSuccess; ++r) st = mesh_->send_fd(r, 0xffffffffu, size, fd);
     close(fd);
     AMEM_TRY(st);
   } else {
@@ -291,22 +292,22 @@ Status Comm::setup_multicast() {
   Allocation rec;
   uint64_t va = 0;
   if (all) {
-    ok = Registry::instance().find(stage_.va[rank_], &rec) && be_->mc_bind(mc, 0, rec.handle, stage_.size) == kSuccess;
+    ok = Registry::instance().find(local_va, &rec) && be_->mc_bind(mc, 0, rec.handle, size) == kSuccess;
     if (ok) {
-      ok = be_->reserve(stage_.size, mc_gran, &va) == kSuccess;
-      if (ok && be_->map(va, stage_.size, mc, dev_) != kSuccess) {
-        be_->free_va(va, stage_.size);
+      ok = be_->reserve(size, mc_gran, &va) == kSuccess;
+      if (ok && be_->map(va, size, mc, dev_) != kSuccess) {
+        be_->free_va(va, size);
         va = 0;
         ok = false;
       }
-      if (!ok) be_->mc_unbind(mc, dev_, 0, stage_.size);
+      if (!ok) be_->mc_unbind(mc, dev_, 0, size);
     }
     bool bound = ok;
     AMEM_TRY(mesh_->all_ok(ok, &all));
     if (!all && bound) {
-      be_->unmap(va, stage_.size);
-      be_->free_va(va, stage_.size);
-      be_->mc_unbind(mc, dev_, 0, stage_.size);
+      be_->unmap(va, size);
+      be_->free_va(va, size);
+      be_->mc_unbind(mc, dev_, 0, size);
     }
   }
   if (!all) {
@@ -316,11 +317,164 @@ Status Comm::setup_multicast() {
   rec.mc_handle = mc;
   rec.mc_offset = 0;
   rec.type = kLocalSymm;
-  rec.tag = kTagNvls;
+  rec.tag = rec.owner == id() && local_va == stage_.va[rank_] ? kTagNvls : rec.tag;
   AMEM_TRY(Registry::instance().update(rec));
-  stage_.mc_handle = mc;
-  stage_.mc_va = va;
+  seg->mc_handle = mc;
+  seg->mc_va = va;
   return kSuccess;
+}
+
+// ---- registered windows ---------------------------------------------------------------
+// The reference learns of such memory through three NCCL hooks: symmetric windows
+// (nccl_patch/nccl_2.27.5-1.diff:56-58), user buffers registered with peers (:630-632, which calls
+// amem_addPeerInfo, amem_nccl_plugin/amem_nccl.cpp:359-381) and the proxy's imports of them
+// (:640-644).  Here registration itself builds the peer mappings, so the records exist from the
+// start: the local allocation moves into this communicator's scope with its importers known, and
+// every peer's memory is an imported record of that scope.
+Status Comm::window_register(void* buff, size_t size, Window** out) {
+  AMEM_TRY(check_usable("ncclCommWindowRegister"));
+  Registry& reg = Registry::instance();
+  Allocation rec;
+  bool found = buff && reg.find_containing((uint64_t)buff, &rec) && !from_peer(rec.type) && rec.owner == 0 &&
+               (uint64_t)buff + size <= rec.va + rec.size;
+  struct Info {
+    uint64_t size;
+    int ok;
+  } mine{found ? rec.size : 0, found ? 1 : 0};
+  std::vector<Info> infos(nranks_);
+  AMEM_TRY(mesh_->allgather(&mine, sizeof(mine), infos.data()));
+  for (int r = 0; r < nranks_; ++r) {
+    if (!infos[r].ok)
+      return fail(kInvalidArgument, "ncclCommWindowRegister: rank %d did not pass memory from ncclMemAlloc (or it is registered already)", r);
+    if (infos[r].size != mine.size)
+      return fail(kInvalidArgument, "ncclCommWindowRegister: allocations differ in size across ranks (%llu bytes here, %llu on rank %d)",
+                  (unsigned long long)mine.size, (unsigned long long)infos[r].size, r);
+  }
+  Window* w = new Window();
+  w->base = rec.va;
+  w->size = rec.size;
+  Segment& s = w->seg;
+  s.sym_id = next_sym_++;
+  s.size = rec.size;
+  s.category = kStateful;
+  s.tag = kTagSymm;
+  Status st = kSuccess;
+  if (nranks_ > 1) st = be_->reserve(s.size * nranks_, gran_, &s.window);
+  if (st != kSuccess) {
+    delete w;
+    return st;
+  }
+  for (int r = 0; r < nranks_; ++r) s.va[r] = r == rank_ ? rec.va : s.window + (uint64_t)r * s.size;
+  // my allocation joins this communicator's scope
+  rec.owner = id();
+  rec.sym_id = s.sym_id;
+  rec.tag = kTagSymm;
+  rec.importers = nranks_ > 1 ? (((1u << nranks_) - 1u) & ~(1u << rank_)) : 0;
+  AMEM_TRY(reg.update(rec));
+  if (nranks_ > 1) {
+    int fd = -1;
+    AMEM_TRY(be_->export_fd(rec.handle, &fd));
+    for (int r = 0; r < nranks_ && st == kSuccess; ++r)
+      if (r != rank_) st = mesh_->send_fd(r, s.sym_id, s.size, fd);
+    close(fd);
+    AMEM_TRY(st);
+    for (int r = 0; r < nranks_; ++r) {
+      if (r == rank_) continue;
+      uint32_t sym = 0;
+      uint64_t sz = 0;
+      int pfd = -1;
+      AMEM_TRY(mesh_->recv_fd(r, &sym, &sz, &pfd));
+      if (sym != s.sym_id || sz != s.size) {
+        close(pfd);
+        return fail(kInternalError, "window registration out of step with rank %d (segment %u/%u)", r, sym, s.sym_id);
+      }
+      uint64_t ph = 0;
+      st = be_->import_fd(pfd, s.size, &ph);
+      close(pfd);
+      AMEM_TRY(st);
+      st = be_->map(s.va[r], s.size, ph, dev_);
+      if (st != kSuccess) {
+        be_->release(ph);
+        return st;
+      }
+      Allocation imp;
+      imp.va = s.va[r];
+      imp.size = s.size;
+      imp.handle = ph;
+      imp.dev = dev_;
+      imp.type = kPeerSymm;
+      imp.category = kStateful;
+      imp.tag = kTagSymmPeer;
+      imp.owner = id();
+      imp.sym_id = s.sym_id;
+      imp.exporter_rank = r;
+      AMEM_TRY(reg.add(imp));
+    }
+    if (nvls()) {   // the communicator can do multicast: give the window an object of its own
+      Status ms = setup_multicast(&s, rec.va);
+      if (ms != kSuccess) LOGW("rank %d: window without multicast: %s", rank_, last_error_slot().c_str());
+    }
+    AMEM_TRY(mesh_->barrier());
+  }
+  windows_.push_back(w);
+  *out = w;
+  return kSuccess;
+}
+
+Status Comm::drop_window(Window* w, bool collective) {
+  Registry& reg = Registry::instance();
+  if (collective && nranks_ > 1 && !aborted_) {
+    if (be_->is_device() && !paused_) be_->device_sync(dev_);
+    mesh_->barrier();   // peers are done with my memory before anybody unmaps
+  }
+  Segment& s = w->seg;
+  for (int r = 0; r < nranks_; ++r) {
+    if (r == rank_) continue;
+    Allocation a;
+    if (!reg.find(s.va[r], &a)) continue;
+    if (a.state != kMemHole) {
+      be_->unmap(a.va, a.size);
+      be_->release(a.handle);
+    }
+    reg.remove(a.va);
+  }
+  Allocation mine;
+  if (reg.find(w->base, &mine)) {   // back to a plain ncclMemAlloc allocation of the process
+    if (mine.mc_handle && mine.state != kMemHole) be_->mc_unbind(mine.mc_handle, dev_, mine.mc_offset, mine.size);
+    mine.mc_handle = 0;
+    mine.mc_offset = 0;
+    mine.type = kLocalPosix;
+    mine.tag = kTagPosix;
+    mine.importers = 0;
+    mine.sym_id = 0;
+    // a paused communicator hands a paused allocation to the process scope, which must then be
+    // told that it has something to bring back
+    bool hole = mine.state == kMemHole;
+    mine.owner = 0;
+    reg.update(mine);
+    if (hole && reg.owner_state(0) != kRunPaused) reg.set_owner_state(0, kRunPaused);
+  }
+  if (s.mc_va) {
+    be_->unmap(s.mc_va, s.size);
+    be_->free_va(s.mc_va, s.size);
+    be_->release(s.mc_handle);
+  }
+  if (s.window) be_->free_va(s.window, s.size * nranks_);
+  windows_.erase(std::remove(windows_.begin(), windows_.end(), w), windows_.end());
+  delete w;
+  return kSuccess;
+}
+
+Status Comm::window_deregister(Window* w) {
+  if (std::find(windows_.begin(), windows_.end(), w) == windows_.end()) return fail(kInvalidArgument, "not a window of this communicator");
+  return drop_window(w, true);
+}
+
+Window* Comm::find_window(const void* p, size_t bytes) {
+  uint64_t a = (uint64_t)p;
+  for (Window* w : windows_)
+    if (a >= w->base && a + bytes <= w->base + w->size) return w;
+  return nullptr;
 }
 
 Comm::~Comm() {
@@ -368,6 +522,7 @@ Status Comm::destroy() {
   if (guard != kSuccess) LOGE("%s", last_error_slot().c_str());
   // Peers must be done with my memory before I unmap it.
   if (!aborted_ && mesh_ && nranks_ > 1) mesh_->barrier();
+  while (!windows_.empty()) drop_window(windows_.back(), false);
   for (auto& s : fused_)
     if (s.window) sym_free(&s);
   sym_free(&stage_);

@@ -33,6 +33,14 @@ struct Segment {
   uint64_t mc_va = 0;             // VA of the multicast mapping
 };
 
+// A registered window: memory from ncclMemAlloc that every rank of the communicator has mapped
+// (and, with NVLS, bound to one multicast object), so collectives can work on it in place.
+struct Window {
+  uint64_t base = 0;     // the user's address of this rank's memory
+  size_t size = 0;       // bytes (the whole allocation)
+  Segment seg;           // seg.va[r]: rank r's memory as mapped here (seg.va[rank] == base); seg.mc_va: multicast mapping
+};
+
 class EmuGroup;
 
 struct CommConfig {
@@ -103,6 +111,17 @@ class Comm {
   Status sym_alloc(size_t size, int category, int tag, Segment* out);
   Status sym_free(Segment* seg);
 
+  // Registered windows (ncclCommWindowRegister): collective over the communicator.  `buff` must
+  // lie in memory from ncclMemAlloc; the whole allocation is registered and its size must be the
+  // same on every rank.  From then on the allocation belongs to this communicator's pause /
+  // resume scope: its contents are saved and restored, the peers' mappings of it and its
+  // multicast binding are dropped and re-made with everything else.
+  Status window_register(void* buff, size_t size, Window** out);
+  Status window_deregister(Window* w);
+  // The window that holds [p, p+bytes), or nullptr.
+  Window* find_window(const void* p, size_t bytes);
+  size_t window_count() const { return windows_.size(); }
+
   // Cached scratch segments of the fused kernels (0: gathered activations, 1: reduce-scatter
   // partial slots, 2: MoE receive buffers, 3: MoE return buffers); grown collectively when a
   // call needs more.
@@ -119,7 +138,10 @@ class Comm {
   Comm() {}
   ~Comm();
   Status init(const UniqueId& id, int nranks, int rank, const CommConfig& cfg, VmmBackend* be);
-  Status setup_multicast();
+  // Creates a multicast object over `seg` (whose local memory is the registry record at
+  // `local_va`), binds every rank's memory and maps it; on failure the segment simply has none.
+  Status setup_multicast(Segment* seg, uint64_t local_va);
+  Status drop_window(Window* w, bool collective);
   Status flush_p2p(cudaStream_t stream);
   Status after_resume(Status engine_result);   // caller holds mu_
   Status run(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream);
@@ -129,6 +151,7 @@ class Comm {
   int rank_ = 0, nranks_ = 1, dev_ = 0;
   Segment ctrl_, stage_;
   Segment fused_[4];
+  std::vector<Window*> windows_;
   uint32_t next_sym_ = 1;
   size_t p2p_slot_bytes_ = 0;
   size_t gran_ = 0;

@@ -100,7 +100,7 @@ Status Comm::run(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream)
   if (emu_) {
     LaunchPlan p = plan;
     int n = nranks_;
-    int tag = a.kind * 64 + a.algo * 16 + a.dtype;
+    int tag = a.kind * 256 + a.algo * 16 + a.dtype;
     return emu_->rendezvous(rank_, tag, &a, sizeof(a), stream, [p, n](const void* host_all, const void* dev_all, cudaStream_t s) {
       const CollArgs* h = (const CollArgs*)host_all;
       LaunchPlan q = p;
@@ -157,7 +157,29 @@ Status Comm::collective(int kind, const void* send, void* recv, size_t count, in
   ti.nvls = nvls();
   ti.max_blocks = max_blocks_;
   ti.forced_algo = algo;
+  // Both operands inside registered windows, at the same offsets on every rank (the caller's
+  // contract, as for NCCL's symmetric windows): the all-reduce can work on them in place.
+  Window* ws = nullptr;
+  Window* wr = nullptr;
+  if (kind == kCollAllReduce && nranks_ > 1 && dtype == out_dtype && !windows_.empty()) {
+    ws = find_window(send, count * es);
+    wr = find_window(recv, count * es);
+    if (ws && wr) {
+      ti.window = true;
+      size_t so = (uint64_t)send - ws->base, ro = (uint64_t)recv - wr->base;
+      ti.window_mc = ws->seg.mc_va && wr->seg.mc_va && (count * es) % 16 == 0 && so % 16 == 0 && ro % 16 == 0;
+    }
+  }
   LaunchPlan plan = plan_collective(ti);
+  if (plan.algo == kAlgoWindow) {
+    size_t so = (uint64_t)send - ws->base, ro = (uint64_t)recv - wr->base;
+    for (int r = 0; r < nranks_; ++r) {
+      a.win_send[r] = (const char*)ws->seg.va[r] + so;
+      a.win_recv[r] = (char*)wr->seg.va[r] + ro;
+    }
+    a.mc_send = ti.window_mc ? (const char*)ws->seg.mc_va + so : nullptr;
+    a.mc_recv = ti.window_mc ? (char*)wr->seg.mc_va + ro : nullptr;
+  }
   if (kind == kCollAllReduce && algo != kAlgoAuto && plan.algo != algo)
     return fail(kInvalidArgument, "all-reduce variant %d is not available for this size/type on this communicator", algo);
   a.algo = plan.algo;

@@ -244,6 +244,8 @@ ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* sta
 ncclResult_t amemInject(const char* what, int nth, int param);
 /* Bytes of physical memory and number of mappings this process holds through the backend. */
 ncclResult_t amemBackendUsage(size_t* physical_bytes, size_t* mappings, const char** backend_name);
+/* 1 when the memory backend is CUDA device memory, 0 for the host-memory mock. */
+int amemBackendIsDevice(void);
 /* JSON with the time spent in every kind of VMM driver call (create, map, set_access, ...). */
 ncclResult_t amemBackendTimings(char* buf, size_t len, int reset);
 const char* amemLastError(void);

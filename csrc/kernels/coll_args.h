@@ -37,7 +37,9 @@ enum CollKind : int {
 };
 
 // Allreduce variants chosen by the tuner.
-enum Algo : int { kAlgoAuto = 0, kAlgoOneShot = 1, kAlgoTwoShot = 2, kAlgoNvls = 3 };
+// kAlgoWindow: both buffers lie in registered windows, the all-reduce works on them in place
+// (through the windows' multicast mapping when there is one, by peer loads and stores otherwise).
+enum Algo : int { kAlgoAuto = 0, kAlgoOneShot = 1, kAlgoTwoShot = 2, kAlgoNvls = 3, kAlgoWindow = 4 };
 
 // ncclDataType_t / ncclRedOp_t numbering.
 // 8-bit floats are carried by the copy collectives (all-gather, all-to-all, broadcast, send/recv);
@@ -94,6 +96,12 @@ struct CollArgs {
   char* mc_stage;               // multicast mapping of the staging segments (NVLS) or null
   size_t stage_bytes;           // bytes of one staging segment
   size_t p2p_slot_bytes;        // bytes of one (peer, block) slot in the p2p area at the end of staging
+  // registered windows (algo == kAlgoWindow): the operands as every rank maps them, already
+  // offset to the first element, and their multicast views (null without NVLS)
+  const char* win_send[kMaxRanks];
+  char* win_recv[kMaxRanks];
+  const char* mc_send;
+  char* mc_recv;
   uint32_t* status;             // host-mapped, kStatusWords words
   unsigned long long timeout_ns;
   // send/recv lists for grouped point-to-point (kind == kCollSendRecv)

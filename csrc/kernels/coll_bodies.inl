@@ -235,6 +235,35 @@ AMEM_FN void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
   reduce_span<TI, TO, OP>((TO*)a.recv + lo / es, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, full_lane());
 }
 
+// All-reduce on registered windows, without staging: every rank's input is mapped here, so rank r
+// reduces slice r straight out of the peers' memory (loads over NVLink) into its own output and
+// then stores the reduced slice into every peer's output.  One barrier before (the inputs are
+// complete: each rank's earlier kernels have finished once its block arrives) and one after (the
+// outputs are complete).  Safe in place: slice r is read and written by rank r only.
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_allreduce_window(const CollArgs& a, Proto& p) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(TI), vi = 16 / es;
+  const size_t N = a.count;
+  size_t sl = ((N + n - 1) / n + vi - 1) / vi * vi;
+  size_t b0 = (size_t)r * sl, b1 = b0 + sl;
+  if (b0 > N) b0 = N;
+  if (b1 > N) b1 = N;
+  size_t lo, hi;
+  block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+  block_barrier(p);
+  const TI* slots[kMaxRanks];
+  for (int s2 = 0; s2 < n; ++s2) slots[s2] = (const TI*)(a.win_send[s2] + b0 * es + lo);
+  TO* mine = (TO*)(a.win_recv[r] + b0 * es + lo);
+  reduce_span<TI, TO, OP>(mine, slots, n, (hi - lo) / es, a.scale, a.has_scale != 0, full_lane());
+  block_sync();
+  for (int k = 1; k < n; ++k) {
+    int q = peer_at(r, n, k, p.block);
+    copy_span(a.win_recv[q] + b0 * es + lo, (const char*)mine, hi - lo, full_lane());
+  }
+  block_barrier(p);
+}
+
 template <typename TI, typename TO, int OP>
 AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch);
 
@@ -550,6 +579,7 @@ AMEM_FN void run_body(const CollArgs& a, int block, int nblocks, int* s_abort, s
     switch (a.kind) {
       case kCollAllReduce:
         if (a.algo == kAlgoOneShot) body_allreduce_oneshot<TI, TO, OP>(a, p);
+        else if (a.algo == kAlgoWindow) body_allreduce_window<TI, TO, OP>(a, p);
         else body_allreduce_twoshot<TI, TO, OP>(a, p, chunk_elems);
         break;
       case kCollReduceScatter: body_reducescatter<TI, TO, OP>(a, p, chunk_elems); break;

@@ -220,6 +220,56 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   if (thread_index() == 0) p.me->cseq[p.block] = base + nch;
 }
 
+// All-reduce on registered windows through their multicast mappings: rank r asks the switch for
+// the sum of everybody's slice r (multimem.ld_reduce on the input window) and has the switch write
+// it into everybody's output window (multimem.st).  No staging copy on either side, so a byte
+// crosses HBM once on the way out and once on the way in; one barrier before, one after.
+template <typename T>
+__device__ __forceinline__ void body_allreduce_window_nvls(const CollArgs& a, Proto& p) {
+  const int n = a.nranks, r = a.rank;
+  const size_t es = sizeof(T), vi = 16 / es;
+  const size_t N = a.count;
+  size_t sl = ((N + n - 1) / n + vi - 1) / vi * vi;
+  size_t b0 = (size_t)r * sl, b1 = b0 + sl;
+  if (b0 > N) b0 = N;
+  if (b1 > N) b1 = N;
+  size_t lo, hi;
+  block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+  block_barrier(p);
+  const size_t nvec = (hi - lo) / 16;   // the launcher only takes this path for whole 16-byte vectors
+  const char* src = a.mc_send + b0 * es + lo;
+  char* dst = a.mc_recv + b0 * es + lo;
+  const size_t nt = blockDim.x;
+  size_t i = threadIdx.x;
+  constexpr int U = 8;
+  for (; i + (U - 1) * nt < nvec; i += U * nt) {
+    uint4 v[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) v[j] = Multimem<T>::ld_reduce(src + (i + j * nt) * 16);
+    if (a.has_scale) {
+#pragma unroll
+      for (int j = 0; j < U; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) multimem_st(dst + (i + j * nt) * 16, v[j]);
+  }
+  for (; i < nvec; i += nt) {
+    uint4 v = Multimem<T>::ld_reduce(src + i * 16);
+    if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
+    multimem_st(dst + i * 16, v);
+  }
+  block_barrier(p);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) nvls_window_allreduce_kernel(const __grid_constant__ CollArgs a) {
+  __shared__ int s_abort;
+  Proto p;
+  proto_begin(p, a, blockIdx.x, gridDim.x, &s_abort);
+  body_allreduce_window_nvls<T>(a, p);
+  proto_end(p);
+}
+
 // ------------------------------------------------------------------ kernels
 template <typename T>
 __global__ void __launch_bounds__(512) nvls_allreduce_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {
@@ -297,6 +347,13 @@ Status launch_collective(const CollArgs& a, const LaunchPlan& plan, cudaStream_t
     else if (a.dtype == kF16) dev::nvls_allreduce_kernel<__half><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
     else return fail(kInvalidArgument, "NVLS all-reduce supports fp32, fp16 and bf16 sums only");
     return check_launch("nvls allreduce");
+  }
+  if (a.kind == kCollAllReduce && a.algo == kAlgoWindow && a.nranks > 1 && a.mc_send && a.mc_recv && (a.redop == kSum || a.redop == kAvg) &&
+      (a.dtype == kF32 || a.dtype == kBF16 || a.dtype == kF16) && a.dtype == a.out_dtype) {
+    if (a.dtype == kF32) dev::nvls_window_allreduce_kernel<float><<<grid, block, 0, stream>>>(a);
+    else if (a.dtype == kBF16) dev::nvls_window_allreduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a);
+    else dev::nvls_window_allreduce_kernel<__half><<<grid, block, 0, stream>>>(a);
+    return check_launch("window allreduce (nvls)");
   }
   bool reducing = a.kind == kCollAllReduce || a.kind == kCollReduceScatter || a.kind == kCollReduce;
   if (reducing) {

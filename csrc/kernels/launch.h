@@ -24,6 +24,8 @@ struct TunerInput {
   bool nvls;          // multicast mapping available
   int max_blocks;     // upper bound for this communicator (emulated comms use a small one)
   int forced_algo;    // kAlgoAuto or a variant forced by AMEM_ALGO / the API
+  bool window = false;      // all-reduce: both operands lie in registered windows at vector-aligned offsets
+  bool window_mc = false;   // ... and the windows have multicast mappings
 };
 
 // Deterministic in its inputs: every rank, and the same rank before and after a pause,

@@ -47,6 +47,11 @@ LaunchPlan plan_collective(const TunerInput& in) {
     // of two: measured faster up to 16 MiB (1 MiB: 27.6 vs 39.1 us; 8 MiB: 43.0 vs 52.6 us).
     static const bool oneshot_set = getenv("AMEM_ONESHOT_MAX_KB") != nullptr;
     size_t one_max = std::min(slot, (n == 2 && !oneshot_set) ? ((size_t)16 << 20) : ((size_t)oneshot_kb << 10));
+    // Registered windows: in place, no staging.  Taken from AMEM_WINDOW_MIN_KB (default 512) up;
+    // below that the one-shot exchange through staging has one barrier less.
+    static const long win_min_kb = env_long("AMEM_WINDOW_MIN_KB", 512);
+    if (in.window && want == kAlgoAuto && n > 1 && in.count * es >= ((size_t)win_min_kb << 10)) want = kAlgoWindow;
+    if (want == kAlgoWindow && !in.window) want = kAlgoAuto;
     if (want == kAlgoNvls && !nvls_ok) want = kAlgoAuto;
     if (want == kAlgoOneShot && in.count * es > slot) want = kAlgoAuto;
     if (want == kAlgoAuto) {
@@ -69,6 +74,13 @@ LaunchPlan plan_collective(const TunerInput& in) {
   long blocks = (long)((bytes + per_block - 1) / per_block);
   if (blocks < 1) blocks = 1;
   if (blocks > in.max_blocks) blocks = in.max_blocks;
+  if (in.kind == kCollAllReduce && p.algo == kAlgoWindow) {
+    // every block streams through the switch (or the peers) with many loads in flight; enough
+    // blocks to fill the links, not one per 32 KiB
+    static const long win_blocks = env_long("AMEM_WINDOW_BLOCKS", 0);
+    long want_b = (long)((bytes / (size_t)n + (64 << 10) - 1) / (64 << 10));
+    blocks = std::max<long>(1, std::min<long>(want_b, win_blocks > 0 ? win_blocks : in.max_blocks));
+  }
   if (blocks_env > 0) blocks = std::min<long>(blocks_env, in.max_blocks);
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   p.blocks = (int)blocks;

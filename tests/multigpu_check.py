@@ -125,6 +125,36 @@ def main():
     report("pause/resume x20", ok and freed >= 0.95 * info["stage_bytes"], freed_mib=freed >> 20,
            pause_ms=round(st["pause_total_us"] / 1e3, 3), resume_ms=round(st["resume_total_us"] / 1e3, 3))
 
+    # ---- registered windows: in-place all-reduce (multicast when the communicator has NVLS), pause / resume
+    for dtype, n in ((torch.bfloat16, (1 << 24) + 64), (torch.float32, 3_000_001)):
+        es = torch.empty(0, dtype=dtype).element_size()
+        win = comm.window_alloc(n * es + 4096)
+        xw = win.tensor(dtype, n)
+        g = torch.Generator().manual_seed(500 + rank)
+        mine = torch.randn(n, generator=g).to(dtype)
+        acc = sum(t.float() for t in gather_cpu(mine))
+        xw.copy_(mine.cuda())
+        torch.cuda.synchronize()
+        dist.barrier()
+        comm.all_reduce(xw, algo="window")
+        torch.cuda.synchronize()
+        first = xw.clone()
+        ok = torch.allclose(first.cpu().float(), acc, rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-2 if dtype == torch.bfloat16 else 1e-4)
+        free_w = torch.cuda.mem_get_info()[0]
+        for cycle in range(3):
+            pause_all()
+            freed_w = torch.cuda.mem_get_info()[0] - free_w
+            resume_all()
+            ok = ok and torch.equal(xw, first)               # the window's contents came back
+            xw.copy_(mine.cuda())
+            torch.cuda.synchronize()
+            dist.barrier()
+            comm.all_reduce(xw)                              # the tuner takes the window path
+            torch.cuda.synchronize()
+            ok = ok and torch.equal(xw, first)               # bit-identical to the run before the pause
+        report(f"window allreduce {str(dtype)[6:]} n={n} + pause x3", ok and freed_w >= n * es, freed_mib=freed_w >> 20)
+        win.free()
+
     # ---- fused tensor-parallel GEMMs
     from asystem_amem_b200.ops import MoeDispatcher, all_gather_gemm, gemm_reduce_scatter
     m_local, N, K = 512, 1024, 2048
