@@ -132,6 +132,7 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "ncclCommWindowDeregister": [c_void_p, c_void_p],
         "amemMoeBuffers": [c_void_p, c_int, c_int, P(c_void_p), P(c_void_p)],
         "amemMoeDispatch": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "amemMoeDispatchCounted": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "amemMoeCombine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "amemGemmBf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "amemGemmPlan": [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],

@@ -35,7 +35,8 @@ class DispatchResult:
     recv_x: torch.Tensor          # bf16 [capacity_rows, d]; rows [0, total_rows) are valid
     expert_counts: torch.Tensor   # int32 [experts_per_rank]
     expert_offsets: torch.Tensor  # int32 [experts_per_rank + 1]
-    send_pos: torch.Tensor        # int32 [T, k]: row of every (token, choice) on its expert's rank
+    send_pos: torch.Tensor        # int32 [T, k]: row of every (token, choice) on its expert's rank (-1: left out, no room)
+    dropped: torch.Tensor | None = None   # int32 [1]: rows routed to THIS rank that did not fit its capacity
 
 
 class MoeDispatcher:
@@ -69,12 +70,13 @@ class MoeDispatcher:
         counts = torch.empty(self.experts_per_rank, dtype=torch.int32, device=x.device)
         offsets = torch.empty(self.experts_per_rank + 1, dtype=torch.int32, device=x.device)
         send_pos = torch.empty(T, k, dtype=torch.int32, device=x.device)
+        dropped = torch.zeros(1, dtype=torch.int32, device=x.device)
         st = (stream or torch.cuda.current_stream()).cuda_stream
-        B.check(self.comm.lib.amemMoeDispatch(x.data_ptr(), topk_idx.data_ptr(), T, k, self.d, self.E, self.capacity,
-                                              counts.data_ptr(), offsets.data_ptr(), send_pos.data_ptr(), self.comm._h, st),
-                "amemMoeDispatch")
+        B.check(self.comm.lib.amemMoeDispatchCounted(x.data_ptr(), topk_idx.data_ptr(), T, k, self.d, self.E, self.capacity,
+                                                     counts.data_ptr(), offsets.data_ptr(), send_pos.data_ptr(), dropped.data_ptr(),
+                                                     self.comm._h, st), "amemMoeDispatch")
         self._last_idx = topk_idx
-        return DispatchResult(self.recv_x, counts, offsets, send_pos)
+        return DispatchResult(self.recv_x, counts, offsets, send_pos, dropped)
 
     def combine(self, topk_idx: torch.Tensor, topk_w: torch.Tensor, send_pos: torch.Tensor, out: torch.Tensor | None = None,
                 stream=None) -> torch.Tensor:

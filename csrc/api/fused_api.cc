@@ -14,6 +14,7 @@
 #include "../include/nccl.h"
 #include "../kernels/gemm_sm100.h"
 #include "../kernels/moe.h"
+#include "../vmm/tracked.h"
 
 using namespace amem;
 
@@ -70,14 +71,22 @@ SplitKWs* splitk_workspace(int dev, cudaStream_t stream, int ctas) {
     cudaGetLastError();
     return nullptr;  // not recorded: a later launch outside the capture may allocate
   }
+  // Tracked, process-level memory: the partial tiles are SCRATCH (dead between launches), the
+  // counters are STATEFUL (they must read zero at every launch, also after a pause).
   SplitKWs w;
   size_t ctr_bytes = gemm_splitk_ctr_words(ctas) * sizeof(uint32_t);
-  if (cudaMalloc((void**)&w.partials, gemm_splitk_ws_bytes(ctas)) != cudaSuccess ||
-      cudaMalloc((void**)&w.counters, ctr_bytes) != cudaSuccess || cudaMemset(w.counters, 0, ctr_bytes) != cudaSuccess) {
+  VmmBackend* be = cuda_backend();
+  uint64_t pv = 0, cv = 0;
+  if (!be || tracked_alloc(be, 0, dev, gemm_splitk_ws_bytes(ctas), kScratch, kTagDefault, &pv, nullptr) != kSuccess ||
+      tracked_alloc(be, 0, dev, ctr_bytes, kStateful, kTagDefault, &cv, nullptr) != kSuccess ||
+      cudaMemset((void*)cv, 0, ctr_bytes) != cudaSuccess) {
     cudaGetLastError();
-    if (w.partials) cudaFree(w.partials);
-    w = SplitKWs();  // remembered as "no workspace": the GEMM runs unsplit on this stream
+    if (pv) tracked_free(be, pv);
+    if (cv) tracked_free(be, cv);
+    pv = cv = 0;  // remembered as "no workspace": the GEMM runs unsplit on this stream
   }
+  w.partials = (float*)pv;
+  w.counters = (uint32_t*)cv;
   auto ins = all.emplace(key, w);
   return ins.first->second.partials ? &ins.first->second : nullptr;
 }
@@ -134,10 +143,15 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   {
     std::lock_guard<std::mutex> lk(init_mu);
     if (!ctrl[dev]) {
-      CtrlBlock* c = nullptr;
-      if (cudaMalloc((void**)&c, sizeof(CtrlBlock) + sizeof(FusedFlags)) != cudaSuccess) return ncclUnhandledCudaError;
-      cudaMemset(c, 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
-      ctrl[dev] = c;
+      // tracked and RESIDENT: the plain GEMM stays usable while everything else is paused
+      uint64_t va = 0;
+      VmmBackend* be = cuda_backend();
+      cudaFree(0);
+      Status ts = be ? tracked_alloc(be, 0, dev, sizeof(CtrlBlock) + sizeof(FusedFlags), kResident, kTagDefault, &va, nullptr)
+                     : fail(kInvalidUsage, "no CUDA memory backend");
+      if (ts != kSuccess) return R(ts);
+      cudaMemset((void*)va, 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
+      ctrl[dev] = (CtrlBlock*)va;
     }
     if (!status_dev[dev]) {
       uint32_t* st = nullptr;
@@ -167,7 +181,8 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   // the first launch of a stream; a stream that is being captured gets no split unless it
   // already has one (allocation is not allowed there).  AMEM_GEMM_SPLITK=0 turns the split off.
   const long splitk_on = env_long("AMEM_GEMM_SPLITK", 1);  // read per call: benches flip it
-  SplitKWs* ws = splitk_on ? splitk_workspace(dev, stream, sms) : nullptr;
+  // (while the process is paused the workspace is not mapped: the GEMM then runs unsplit)
+  SplitKWs* ws = splitk_on && !Registry::instance().is_paused(0) ? splitk_workspace(dev, stream, sms) : nullptr;
   GemmPlan plan = plan_gemm(M, N, K, sms, ws != nullptr);
   const bool tall = plan.tall != 0;
   int slices = plan.slices;
@@ -302,6 +317,7 @@ ncclResult_t amemMoeBuffers(ncclComm_t comm, int capacity_rows, int d, void** re
 static Status moe_args(Comm* c, int T, int k, int d, int E, int capacity_rows, MoeArgs* a) {
   if (T < 0 || k <= 0 || d <= 0 || d % 8 || E <= 0 || E > kMoeMaxExperts || E % c->nranks())
     return fail(kInvalidArgument, "MoE shape: T=%d k=%d d=%d (multiple of 8) E=%d (<= %d, divisible by %d ranks)", T, k, d, E, kMoeMaxExperts, c->nranks());
+  if (capacity_rows <= 0) return fail(kInvalidArgument, "MoE capacity_rows must be positive, got %d", capacity_rows);
   Segment *rx = nullptr, *yb = nullptr;
   size_t bytes = (size_t)capacity_rows * d * 2;
   AMEM_TRY(c->fused_segment(2, bytes, &rx));
@@ -317,18 +333,16 @@ static Status moe_args(Comm* c, int T, int k, int d, int E, int capacity_rows, M
     a->recv[r] = (char*)rx->va[r];
     a->ybuf[r] = (char*)yb->va[r];
   }
-  // small per-communicator work area in ordinary device memory
-  static std::mutex mu;
-  static std::map<Comm*, int*> work;
-  std::lock_guard<std::mutex> g(mu);
-  int*& w = work[c];
-  if (!w) {
-    size_t ints = (size_t)kMoeSegments * kMoeMaxExperts * 2 + kMoeMaxExperts;
-    if (cudaMalloc((void**)&w, ints * sizeof(int)) != cudaSuccess) return fail(kCudaError, "cudaMalloc of the MoE work area failed");
-  }
+  // small per-communicator work area: tracked scratch of the communicator (every word of it is
+  // rewritten by each dispatch before it is read, so nothing has to survive a pause)
+  void* wp = nullptr;
+  size_t ints = (size_t)kMoeSegments * kMoeMaxExperts * 2 + kMoeMaxExperts + 64;
+  AMEM_TRY(c->local_scratch(0, ints * sizeof(int), &wp));
+  int* w = (int*)wp;
   a->seg_hist = w;
   a->seg_base = w + (size_t)kMoeSegments * kMoeMaxExperts;
   a->send_off = w + (size_t)kMoeSegments * kMoeMaxExperts * 2;
+  a->dropped_rows = w + (size_t)kMoeSegments * kMoeMaxExperts * 2 + kMoeMaxExperts;
   return kSuccess;
 }
 
@@ -336,8 +350,20 @@ static Status moe_args(Comm* c, int T, int k, int d, int E, int capacity_rows, M
 // receive buffer holds the rows of its local experts, grouped by expert in (source rank, token)
 // order; expert_counts[E/nranks] and expert_offsets[E/nranks + 1] describe the groups and
 // send_pos[T*k] remembers where every (token, choice) went (needed by amemMoeCombine).
+//
+// Capacity: a rank that is routed more rows than capacity_rows keeps the first capacity_rows of
+// them (rows are ordered by expert, then source rank, then token); the rest are not sent, their
+// send_pos is -1 (amemMoeCombine gives them weight zero), expert_counts / expert_offsets count
+// only stored rows, and *dropped_rows (optional device int) receives how many this rank left
+// out.  The communicator stays usable: overflow is a result of the call, not an error state.
+ncclResult_t amemMoeDispatchCounted(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
+                                    int* expert_offsets, int* send_pos, int* dropped_rows, ncclComm_t comm, cudaStream_t stream);
 ncclResult_t amemMoeDispatch(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
                              int* expert_offsets, int* send_pos, ncclComm_t comm, cudaStream_t stream) {
+  return amemMoeDispatchCounted(x, topk_idx, T, k, d, E, capacity_rows, expert_counts, expert_offsets, send_pos, nullptr, comm, stream);
+}
+ncclResult_t amemMoeDispatchCounted(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
+                                    int* expert_offsets, int* send_pos, int* dropped_rows, ncclComm_t comm, cudaStream_t stream) {
   if (!comm) return ncclInvalidArgument;
   Comm* c = reinterpret_cast<Comm*>(comm);
   Status s = c->check_usable("amemMoeDispatch");
@@ -350,6 +376,7 @@ ncclResult_t amemMoeDispatch(const void* x, const int* topk_idx, int T, int k, i
   a.expert_counts = expert_counts;
   a.expert_offsets = expert_offsets;
   a.send_pos = send_pos;
+  if (dropped_rows) a.dropped_rows = dropped_rows;
   if (c->emulated()) {
     int n = c->nranks();
     return R(c->emu()->rendezvous(c->rank(), 2001, &a, sizeof(a), stream, [n](const void* h, const void* dv, cudaStream_t st) {

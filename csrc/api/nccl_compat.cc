@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "../comm/comm.h"
+#include "../vmm/tracked.h"
 #include "../core/log.h"
 #include "../include/nccl.h"
 #include "../kernels/launch.h"
@@ -264,36 +265,9 @@ ncclResult_t ncclMemAlloc(void** ptr, size_t size) {
     cudaFree(0);
   }
   if (Registry::instance().is_paused(0)) return R(fail(kInvalidUsage, "ncclMemAlloc while paused"));
-  size_t gran = 0;
-  Status s = be->granularity(dev, &gran);
+  uint64_t va = 0;
+  Status s = tracked_alloc(be, 0, dev, size, kStateful, kTagPosix, &va, nullptr);
   if (s != kSuccess) return R(s);
-  size_t sz = (size + gran - 1) / gran * gran;
-  uint64_t va = 0, h = 0;
-  if ((s = be->reserve(sz, gran, &va)) != kSuccess) return R(s);
-  if ((s = be->create(dev, sz, &h)) != kSuccess) {
-    be->free_va(va, sz);
-    return R(s);
-  }
-  if ((s = be->map(va, sz, h, dev)) != kSuccess) {
-    be->release(h);
-    be->free_va(va, sz);
-    return R(s);
-  }
-  Allocation rec;
-  rec.va = va;
-  rec.size = sz;
-  rec.handle = h;
-  rec.dev = dev;
-  rec.type = kLocalPosix;
-  rec.category = kStateful;
-  rec.tag = kTagPosix;
-  rec.owner = 0;
-  if ((s = Registry::instance().add(rec)) != kSuccess) {
-    be->unmap(va, sz);
-    be->release(h);
-    be->free_va(va, sz);
-    return R(s);
-  }
   *ptr = (void*)va;
   return ncclSuccess;
 }
@@ -304,16 +278,7 @@ ncclResult_t ncclMemFree(void* ptr) {
   if (!Registry::instance().find((uint64_t)ptr, &a) || from_peer(a.type))
     return R(fail(kInvalidArgument, "ncclMemFree: pointer was not returned by ncclMemAlloc"));
   if (a.owner != 0) return R(fail(kInvalidUsage, "ncclMemFree: the buffer is still registered as a window (ncclCommWindowDeregister first)"));
-  VmmBackend* be = default_backend();
-  if (a.state != kMemHole) {
-    if (be->is_device()) be->device_sync(a.dev);
-    be->unmap(a.va, a.size);
-    be->release(a.handle);
-  }
-  if (a.shadow) be->host_free(a.shadow, a.size);
-  be->free_va(a.va, a.size);
-  Registry::instance().remove(a.va);
-  return ncclSuccess;
+  return R(tracked_free(default_backend(), a.va));
 }
 
 // ---- collectives ----------------------------------------------------------------------

@@ -9,6 +9,7 @@
 #include "../core/log.h"
 #include "../kernels/launch.h"
 #include "emu.h"
+#include "../vmm/tracked.h"
 
 namespace amem {
 
@@ -225,6 +226,23 @@ Status Comm::fused_segment(int which, size_t bytes, Segment** out) {
   AMEM_TRY(sym_alloc(bytes, kScratch, kTagSymm, &s));
   if (nranks_ > 1) AMEM_TRY(mesh_->barrier());
   *out = &s;
+  return kSuccess;
+}
+
+Status Comm::local_scratch(int which, size_t bytes, void** out) {
+  if (which < 0 || which >= 2) return fail(kInvalidArgument, "local scratch index %d", which);
+  std::lock_guard<std::mutex> g(mu_);
+  if (local_va_[which] && local_bytes_[which] >= bytes) {
+    *out = (void*)local_va_[which];
+    return kSuccess;
+  }
+  if (local_va_[which]) {
+    AMEM_TRY(tracked_free(be_, local_va_[which]));
+    local_va_[which] = 0;
+    local_bytes_[which] = 0;
+  }
+  AMEM_TRY(tracked_alloc(be_, id(), dev_, bytes, kScratch, kTagDefault, &local_va_[which], &local_bytes_[which]));
+  *out = (void*)local_va_[which];
   return kSuccess;
 }
 
@@ -523,6 +541,11 @@ Status Comm::destroy() {
   // Peers must be done with my memory before I unmap it.
   if (!aborted_ && mesh_ && nranks_ > 1) mesh_->barrier();
   while (!windows_.empty()) drop_window(windows_.back(), false);
+  for (int i = 0; i < 2; ++i)
+    if (local_va_[i]) {
+      tracked_free(be_, local_va_[i]);
+      local_va_[i] = 0;
+    }
   for (auto& s : fused_)
     if (s.window) sym_free(&s);
   sym_free(&stage_);

@@ -111,6 +111,11 @@ class Comm {
   Status sym_alloc(size_t size, int category, int tag, Segment* out);
   Status sym_free(Segment* seg);
 
+  // Work memory of the fused kernels in this rank's own device memory (not shared with peers):
+  // a tracked SCRATCH allocation of this communicator, grown on demand, released by ncclPause
+  // and re-made by ncclResume with undefined contents, freed at destroy.
+  Status local_scratch(int which, size_t bytes, void** out);
+
   // Registered windows (ncclCommWindowRegister): collective over the communicator.  `buff` must
   // lie in memory from ncclMemAlloc; the whole allocation is registered and its size must be the
   // same on every rank.  From then on the allocation belongs to this communicator's pause /
@@ -152,6 +157,8 @@ class Comm {
   Segment ctrl_, stage_;
   Segment fused_[4];
   std::vector<Window*> windows_;
+  uint64_t local_va_[2] = {0, 0};
+  size_t local_bytes_[2] = {0, 0};
   uint32_t next_sym_ = 1;
   size_t p2p_slot_bytes_ = 0;
   size_t gran_ = 0;

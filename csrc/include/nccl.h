@@ -234,6 +234,11 @@ ncclResult_t amemGemmReduceScatter(const void* A, const void* B, void* out, int 
 ncclResult_t amemMoeBuffers(ncclComm_t comm, int capacity_rows, int d, void** recv_x, void** y);
 ncclResult_t amemMoeDispatch(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
                              int* expert_offsets, int* send_pos, ncclComm_t comm, cudaStream_t stream);
+/* The same with one more output: *dropped_rows (device int, may be null) = rows routed to this rank
+ * that did not fit capacity_rows.  Such rows are not sent (send_pos -1, weight zero in the combine),
+ * the counts and offsets describe only stored rows, and the communicator stays usable. */
+ncclResult_t amemMoeDispatchCounted(const void* x, const int* topk_idx, int T, int k, int d, int E, int capacity_rows, int* expert_counts,
+                                    int* expert_offsets, int* send_pos, int* dropped_rows, ncclComm_t comm, cudaStream_t stream);
 ncclResult_t amemMoeCombine(const int* topk_idx, const float* topk_w, const int* send_pos, void* out, int T, int k, int d, int E,
                             int capacity_rows, ncclComm_t comm, cudaStream_t stream);
 /* 1 if the communicator's ranks share one GPU and run as one cooperative grid; 1 if NVLS is in use. */

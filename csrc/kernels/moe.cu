@@ -71,16 +71,20 @@ __device__ void plan_body(const MoeArgs& a, int segments, int* s_abort) {
     a.send_off[e] = off;
   }
   if (threadIdx.x == 0) {
+    // rows land expert after expert, so the ones beyond the capacity are exactly the tail of
+    // this sequence: clamping the running total gives the counts of the rows actually stored
+    const int cap = a.capacity_rows;
     int run = 0;
     for (int el = 0; el < El; ++el) {
       int c = 0;
       for (int s = 0; s < n; ++s) c += cnt[s][r * El + el];
-      a.expert_counts[el] = c;
-      a.expert_offsets[el] = run;
+      const int lo = min(run, cap), hi = min(run + c, cap);
+      a.expert_counts[el] = hi - lo;
+      a.expert_offsets[el] = lo;
       run += c;
     }
-    a.expert_offsets[El] = run;
-    if (run > a.capacity_rows) dev::report_error(a.coll.status, kDevBadArgs, r, r, 0, (uint32_t)run);
+    a.expert_offsets[El] = min(run, cap);
+    if (a.dropped_rows) *a.dropped_rows = max(0, run - cap);
   }
   dev::proto_end(p);
 }
@@ -123,7 +127,7 @@ __device__ void scatter_body(const MoeArgs& a, int seg, int segments, int* s_abo
       }
       __syncthreads();
     }
-    if (pos >= a.capacity_rows) pos = -1;  // the plan kernel has flagged the overflow
+    if (pos >= a.capacity_rows) pos = -1;  // no room at the owner: not sent (the plan kernel counted it)
     if (i < hi) a.send_pos[i] = pos;
     c_pos[threadIdx.x] = pos;
     c_exp[threadIdx.x] = e;

@@ -38,7 +38,14 @@ struct MoeArgs {
   int* send_pos;            // [T*k] destination row of each pair (-1: dropped for capacity)
   int* expert_counts;       // [E / nranks] rows received per local expert
   int* expert_offsets;      // [E / nranks + 1] exclusive scan of expert_counts (last = total rows)
+  int* dropped_rows;        // optional, one int: rows routed to this rank that did not fit capacity_rows
 };
+
+// Capacity.  A rank can be sent more rows than its buffers hold (routing is data dependent).
+// That is a result of the call, not an error of the communicator: the rows that would land at
+// or beyond capacity_rows are not sent (their send_pos is -1 and combine gives them weight 0),
+// expert_counts / expert_offsets describe only the rows that were stored (so offsets never
+// point past the buffer), and *dropped_rows says how many were left out on this rank.
 
 Status launch_moe_dispatch(const MoeArgs& a, cudaStream_t stream);
 Status launch_moe_combine(const MoeArgs& a, cudaStream_t stream);

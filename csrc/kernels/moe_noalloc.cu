@@ -14,6 +14,9 @@
 namespace amem {
 namespace {
 
+// the kernels size their shared-memory tables and the control block's exchange rows for kMoeMaxExperts
+static_assert(kNoAllocMaxExperts <= kMoeMaxExperts, "the built-in scratch must not promise more experts than the kernels handle");
+
 struct NoAllocScratch {
   CtrlBlock ctrl;                                       // protocol words of the one-rank run
   uint32_t status[kStatusWords];                        // error words (device memory here)
@@ -22,7 +25,8 @@ struct NoAllocScratch {
   int send_off[kNoAllocMaxExperts];                     // first row of every expert
 };
 
-// ~330 KB per GPU, held from library load to process exit.
+// ~330 KB per GPU, held from the moment the CUDA module of this library is loaded on that GPU (its
+// first use there) to process exit.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
 
 std::mutex g_mu;

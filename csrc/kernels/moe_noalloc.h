@@ -16,8 +16,12 @@
 //   * at most kNoAllocMaxExperts experts; more is rejected with ncclInvalidArgument and a
 //     message (amemLastError) -- the array is sized for exactly that many;
 //   * the caller passes every input and output buffer, including recv_x (bf16
-//     [capacity_rows, d]); rows beyond capacity_rows are dropped and get send_pos = -1,
-//     expert_offsets[E] still reports the number of rows that were routed;
+//     [capacity_rows, d]); rows that would land at or beyond capacity_rows are not written and
+//     get send_pos = -1, and expert_counts / expert_offsets describe the rows that were stored
+//     (expert_offsets[E] <= capacity_rows), so nothing indexed by them reaches past recv_x; a
+//     caller that needs to know how many rows were left out counts the -1 entries of send_pos.
+//     Nothing else can go wrong on the device in a one-rank run (there is no peer to wait for),
+//     which is why the entry point has no device-side status to read back;
 //   * every GPU that loads the library holds the array until the process exits;
 //   * all calls on a device share the array and it keeps the previous call's contents; the
 //     entry point clears what has to start at zero itself, but two calls that overlap on the

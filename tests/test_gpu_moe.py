@@ -152,3 +152,54 @@ def test_moe_layer_autograd_one_rank():
     torch.testing.assert_close(g_w2.float(), B2.grad, rtol=8e-2, atol=5e-2)
     torch.testing.assert_close(g_w13.float(), A.grad, rtol=8e-2, atol=5e-2)
     torch.testing.assert_close(g_router.float(), R.grad, rtol=1e-1, atol=1e-1)
+
+
+def test_capacity_overflow_is_a_result_not_an_error():
+    """A rank that is routed more rows than its buffers hold keeps the head of the sequence and
+    reports the rest as dropped; counts and offsets stay inside the buffer, the combine gives the
+    dropped choices weight zero, and the communicator keeps working afterwards."""
+    from asystem_amem_b200.ops import MoeDispatcher
+    world, E, k, T, d = 4, 8, 2, 128, 64
+    El = E // world
+    g = torch.Generator().manual_seed(77)
+    xs = [torch.randn(T, d, generator=g).to(torch.bfloat16) for _ in range(world)]
+    # every token picks expert 0 (rank 0) and one other expert: rank 0 is routed world * T rows plus its share
+    idx = [torch.stack([torch.zeros(T, dtype=torch.int64), torch.randint(1, E, (T,), generator=g)], 1).to(torch.int32) for _ in range(world)]
+    ws = [torch.full((T, k), 0.5) for _ in range(world)]
+    cap = T * k                                     # rank 0 is sent at least world * T = 2 * cap rows
+
+    def fn(rank, world, comm, stream):
+        disp = MoeDispatcher(comm, E, d, cap)
+        res = disp.dispatch(xs[rank].cuda(), idx[rank].cuda())
+        stream.synchronize()
+        offs, counts = res.expert_offsets.cpu(), res.expert_counts.cpu()
+        total = int(offs[-1])
+        disp.y[:total] = res.recv_x[:total]          # identity experts
+        out = disp.combine(idx[rank].cuda(), ws[rank].cuda(), res.send_pos)
+        stream.synchronize()
+        first = (int(res.dropped.item()), offs.tolist(), counts.tolist(), res.send_pos.cpu(), out.cpu(), comm.async_error())
+        # the communicator is still usable: a collective and a second dispatch go through
+        t = torch.full((1000,), float(rank + 1), device="cuda")
+        comm.all_reduce(t)
+        res2 = disp.dispatch(xs[rank].cuda(), idx[rank].cuda())
+        stream.synchronize()
+        return first, float(t[0].item()), torch.equal(res2.send_pos.cpu(), first[3])
+
+    res = run_emulated(world, fn)
+    routed = [0] * world
+    for src in range(world):
+        for e in idx[src].reshape(-1).tolist():
+            routed[e // El] += 1
+    for rank, (first, summed, again) in enumerate(res):
+        dropped, offs, counts, send_pos, out, err = first
+        assert err == 0 and summed == sum(range(1, world + 1)) and again
+        assert dropped == max(0, routed[rank] - cap)
+        assert offs[-1] == min(routed[rank], cap) and sum(counts) == offs[-1] and max(offs) <= cap
+        # a dropped choice contributes nothing; a kept one contributes 0.5 * x
+        kept = (send_pos >= 0).float()
+        exp = (xs[rank].float().unsqueeze(1) * (0.5 * kept).unsqueeze(2)).sum(1)
+        torch.testing.assert_close(out.float(), exp, rtol=2e-2, atol=2e-2)
+    assert res[0][0][0] > 0                          # the case really overflowed rank 0
+    # every choice that went to rank 0 beyond its capacity is marked on the sender
+    lost = sum(int((r[0][3] < 0).sum()) for r in res)
+    assert lost == sum(max(0, routed[r] - cap) for r in range(world))

@@ -108,7 +108,8 @@ def test_process_wide_pause_with_emulated_ranks():
             f0, _ = torch.cuda.mem_get_info()
             pause_all()
             freed = torch.cuda.mem_get_info()[0] - f0
-            assert mem_stats()["live_bytes"] == world * world * (2 << 20)   # only the resident control blocks
+            live = mem_stats()["live_bytes"]    # only resident blocks: the ranks' control segments (and the plain GEMM's, if one ran)
+            assert world * world * (2 << 20) <= live <= world * world * (2 << 20) + (4 << 20)
             resume_all()
         barrier.wait()
         y = torch.full((4096,), float(rank + 1), device="cuda")

@@ -47,6 +47,23 @@ def _no_alloc(lib, x, idx, E, cap):
     return recv[:total], counts, offs, pos, free_before - torch.cuda.mem_get_info()[0]
 
 
+def _torch_oracle(x, idx, E, cap):
+    """The permutation written out in plain torch: rows grouped by expert, (token, choice) order
+    inside an expert; what does not fit in `cap` rows is left out."""
+    T, k = idx.shape
+    flat = idx.reshape(-1).long().cpu()
+    order = torch.argsort(flat, stable=True)
+    pos = torch.empty_like(flat)
+    pos[order] = torch.arange(flat.numel())
+    kept = order[:cap]
+    rows = x.cpu()[kept // k]
+    counts = torch.bincount(flat[kept], minlength=E).to(torch.int32)
+    offs = torch.zeros(E + 1, dtype=torch.int32)
+    offs[1:] = torch.cumsum(counts, 0)
+    pos = torch.where(pos < cap, pos, torch.full_like(pos, -1)).to(torch.int32).view(T, k)
+    return rows, counts, offs, pos
+
+
 def test_no_alloc_permute_matches_dispatch_twice():
     from asystem_amem_b200 import Communicator, get_unique_id, load_library
     lib = load_library()
@@ -63,7 +80,15 @@ def test_no_alloc_permute_matches_dispatch_twice():
         got = _no_alloc(lib, x, idx, E, cap)
         for a, b in zip(ref, got[:4]):
             assert torch.equal(a, b)
+        for a, b in zip(_torch_oracle(x, idx, E, cap), got[:4]):    # and against plain torch
+            assert torch.equal(a, b.cpu())
         took.append(got[4])
+        # a buffer that is too small: the tail is left out, the offsets stay inside the buffer
+        small = cap // 2 + 3
+        got = _no_alloc(lib, x, idx, E, small)
+        for a, b in zip(_torch_oracle(x, idx, E, small), got[:4]):
+            assert torch.equal(a, b.cpu())
+        assert int(got[2][-1]) == small and int((got[3] < 0).sum()) == cap - small
     # the second call found the library already set up: the device's free memory did not move
     assert took[1] <= 0
     # sizes beyond the built-in scratch are refused with a message, nothing is launched
