@@ -52,6 +52,54 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None,
     return out
 
 
+def interleave_gate_up(w13: torch.Tensor, ffn: int) -> torch.Tensor:
+    """[..., 2 * ffn, K] with the gate rows first and the up rows second  ->  the same rows in
+    alternating blocks of 32 gate rows and 32 up rows, the layout the SwiGLU epilogue of
+    :func:`grouped_gemm_bf16` expects (a column tile then holds a gate block next to its up
+    block).  ``ffn`` must be a multiple of 32.  Done once per weight, not per step."""
+    if ffn % 32 or w13.shape[-2] != 2 * ffn:
+        raise ValueError("ffn must be a multiple of 32 and w13 must have 2 * ffn rows")
+    lead, K = w13.shape[:-2], w13.shape[-1]
+    gate = w13[..., :ffn, :].reshape(*lead, ffn // 32, 1, 32, K)
+    up = w13[..., ffn:, :].reshape(*lead, ffn // 32, 1, 32, K)
+    return torch.cat([gate, up], dim=-3).reshape(*lead, 2 * ffn, K).contiguous()
+
+
+def grouped_gemm_bf16(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, out: torch.Tensor | None = None,
+                      rows_hint: int | None = None, swiglu: bool = False, stream=None) -> torch.Tensor:
+    """For every group e: out[offsets[e]:offsets[e+1]] = a[offsets[e]:offsets[e+1]] @ w[e].T, in ONE
+    launch of the tcgen05 kernel.  ``a`` is bf16 [rows_cap, K]; ``w`` is bf16 [groups, N, K];
+    ``offsets`` is an int32 CUDA tensor of groups + 1 row offsets that stays on the device (the
+    MoE dispatch's ``expert_offsets``: no host synchronisation).  Rows outside every group are
+    left untouched.  With ``swiglu`` the rows of each ``w[e]`` must be in the layout of
+    :func:`interleave_gate_up` and the result has N / 2 columns: silu(gate) * up, computed in the
+    epilogue on the fp32 accumulators."""
+    if not a.is_cuda:
+        offs = offsets.tolist()
+        N = w.shape[1]
+        res = torch.zeros(a.shape[0], N // 2 if swiglu else N, dtype=a.dtype) if out is None else out
+        for e in range(w.shape[0]):
+            h = a[offs[e]:offs[e + 1]].float() @ w[e].float().t()
+            if swiglu:
+                h = h.view(h.shape[0], N // 64, 2, 32)
+                h = (torch.nn.functional.silu(h[:, :, 0]) * h[:, :, 1]).reshape(h.shape[0], N // 2)
+            res[offs[e]:offs[e + 1]] = h.to(a.dtype)
+        return res
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or offsets.dtype != torch.int32:
+        raise TypeError("bf16 operands and int32 offsets expected")
+    if not (w.is_cuda and offsets.is_cuda and a.is_contiguous() and w.is_contiguous() and offsets.is_contiguous()):
+        raise ValueError("contiguous CUDA tensors expected")
+    groups, N, K = w.shape
+    if a.shape[1] != K or offsets.numel() != groups + 1:
+        raise ValueError(f"shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, {offsets.numel()} offsets")
+    rows_cap = a.shape[0]
+    out = torch.empty(rows_cap, N // 2 if swiglu else N, dtype=torch.bfloat16, device=a.device) if out is None else out
+    lib = B.load_library()
+    B.check(lib.amemGroupedGemmBf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), offsets.data_ptr(), groups, rows_cap,
+                                    int(rows_hint or 0), N, K, 1 if swiglu else 0, _stream(stream)), "amemGroupedGemmBf16")
+    return out
+
+
 def all_gather_gemm(comm, a_shard: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, stream=None) -> torch.Tensor:
     """out[M, N] = all_gather_rows(a_shard)[M, K] @ b[N, K].T in ONE kernel (column-parallel
     linear under sequence parallelism).  ``a_shard`` holds this rank's M / nranks rows."""

@@ -19,6 +19,7 @@ them from NCCL's bootstrap, which is not part of the plugin).
 """
 from __future__ import annotations
 
+import array
 import ctypes
 import os
 import socket
@@ -138,7 +139,8 @@ class ReferenceArm:
             self._ck(self.h.rh_export(handle, ctypes.byref(fd)), "rh_export")
             for r in range(self.world):
                 if r != self.rank:
-                    socket.send_fds(out, [_MSG.pack(self.rank, idx, size, handle)], [fd.value], 0, path(r))
+                    # (socket.send_fds drops its address argument: sendmsg directly)
+                    out.sendmsg([_MSG.pack(self.rank, idx, size, handle)], [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array("i", [fd.value]))], 0, path(r))
             os.close(fd.value)
         th.join()
         out.close()

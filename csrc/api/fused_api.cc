@@ -114,6 +114,38 @@ GemmPlan plan_gemm(int M, int N, int K, int sms, bool can_split) {
 }
 }  // namespace
 
+namespace {
+// A communicator-free launch still needs protocol words (epoch, operation counter) and status
+// words the host can read: one small block of each per device, made on first use.  The device
+// block is a tracked RESIDENT allocation: the plain and grouped GEMMs stay usable while
+// everything else of the process is paused.
+Status gemm_process_words(int dev, CtrlBlock** ctrl_out, uint32_t** status_out) {
+  static std::mutex init_mu;
+  static CtrlBlock* ctrl[64] = {nullptr};
+  static uint32_t* status_dev[64] = {nullptr};
+  if (dev < 0 || dev >= 64) return fail(kInvalidArgument, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lk(init_mu);
+  if (!ctrl[dev]) {
+    uint64_t va = 0;
+    VmmBackend* be = cuda_backend();
+    cudaFree(0);
+    if (!be) return fail(kInvalidUsage, "no CUDA memory backend");
+    AMEM_TRY(tracked_alloc(be, 0, dev, sizeof(CtrlBlock) + sizeof(FusedFlags), kResident, kTagDefault, &va, nullptr));
+    cudaMemset((void*)va, 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
+    ctrl[dev] = (CtrlBlock*)va;
+  }
+  if (!status_dev[dev]) {
+    uint32_t* st = nullptr;
+    if (cudaHostAlloc((void**)&st, kStatusWords * 4, cudaHostAllocMapped) != cudaSuccess) return fail(kCudaError, "cudaHostAlloc of the status words failed");
+    memset(st, 0, kStatusWords * 4);
+    status_dev[dev] = st;
+  }
+  *ctrl_out = ctrl[dev];
+  *status_out = status_dev[dev];
+  return kSuccess;
+}
+}  // namespace
+
 extern "C" {
 
 // The tiling amemGemmBf16 would use on a GPU with `sms` SMs (no GPU needed: planning is host
@@ -132,34 +164,11 @@ ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* til
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
   Status s = check_shape(M, N, K);
   if (s != kSuccess) return R(s);
-  // A communicator-free launch still needs protocol words (epoch, operation counter) and status
-  // words the host can read: one small block of each per device, made on first use.
-  static std::mutex init_mu;
-  static CtrlBlock* ctrl[64] = {nullptr};
-  static uint32_t* status_dev[64] = {nullptr};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return R(fail(kInvalidArgument, "device ordinal %d out of range", dev));
-  {
-    std::lock_guard<std::mutex> lk(init_mu);
-    if (!ctrl[dev]) {
-      // tracked and RESIDENT: the plain GEMM stays usable while everything else is paused
-      uint64_t va = 0;
-      VmmBackend* be = cuda_backend();
-      cudaFree(0);
-      Status ts = be ? tracked_alloc(be, 0, dev, sizeof(CtrlBlock) + sizeof(FusedFlags), kResident, kTagDefault, &va, nullptr)
-                     : fail(kInvalidUsage, "no CUDA memory backend");
-      if (ts != kSuccess) return R(ts);
-      cudaMemset((void*)va, 0, sizeof(CtrlBlock) + sizeof(FusedFlags));
-      ctrl[dev] = (CtrlBlock*)va;
-    }
-    if (!status_dev[dev]) {
-      uint32_t* st = nullptr;
-      if (cudaHostAlloc((void**)&st, kStatusWords * 4, cudaHostAllocMapped) != cudaSuccess) return ncclUnhandledCudaError;
-      memset(st, 0, kStatusWords * 4);
-      status_dev[dev] = st;
-    }
-  }
+  CtrlBlock* ctrl_dev = nullptr;
+  uint32_t* status_words = nullptr;
+  if ((s = gemm_process_words(dev, &ctrl_dev, &status_words)) != kSuccess) return R(s);
   GemmLaunch g;
   memset(&g, 0, sizeof(g));
   g.p.M = M;
@@ -171,10 +180,10 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
   g.p.rows_per_rank = M;
   g.p.coll.rank = 0;
   g.p.coll.nranks = 1;
-  g.p.coll.ctrl[0] = ctrl[dev];
-  g.p.coll.status = status_dev[dev];
+  g.p.coll.ctrl[0] = ctrl_dev;
+  g.p.coll.status = status_words;
   g.p.coll.timeout_ns = 5ull * 1000000000ull;
-  g.p.fflags[0] = (FusedFlags*)(ctrl[dev] + 1);
+  g.p.fflags[0] = (FusedFlags*)(ctrl_dev + 1);
   int sms = gemm_default_grid(dev);
   // Split-K of the last wave needs a workspace (fp32 partial tiles + counters), kept per
   // (device, stream) so that launches on different streams never share one.  It is allocated on
@@ -200,11 +209,64 @@ ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, i
     g.p.sk_ctr = ws->counters;
   }
   s = launch_gemm(g, stream);
-  if (s == kSuccess && status_dev[dev][0]) {
+  if (s == kSuccess && status_words[0]) {
     // an earlier launch gave up on a wait: its split-K counters may be left mid-count
     if (ws) cudaMemsetAsync(ws->counters, 0, gemm_splitk_ctr_words(sms) * sizeof(uint32_t), stream);
-    s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_dev[dev][0]);
+    s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status_words[0]);
   }
+  return R(s);
+}
+
+// Grouped GEMM: C[rows of group e, :] = A[rows of group e, :] * B[e]^T for every group, one launch.
+// A: bf16 [rows_cap, K]; group_off: DEVICE int32 [groups + 1] (row offsets, e.g. expert_offsets of
+// amemMoeDispatch — the host never reads them); B: bf16 [groups, N, K]; C: bf16 [rows_cap, N], or
+// [rows_cap, N / 2] with epilogue = 1 (SwiGLU of 32-column gate / up blocks, see GemmEpilogue).
+// rows_hint: the number of rows the caller expects (sizes the tile width; any value is correct).
+ncclResult_t amemGroupedGemmBf16(const void* A, const void* B, void* C, const int* group_off, int groups, int rows_cap, int rows_hint,
+                                 int N, int K, int epilogue, cudaStream_t stream) {
+  Status s = check_shape(rows_cap, N, K);
+  if (s != kSuccess) return R(s);
+  if (!A || !B || !C || !group_off) return R(fail(kInvalidArgument, "grouped GEMM: null buffer"));
+  if (groups <= 0 || groups > 256) return R(fail(kInvalidArgument, "grouped GEMM: %d groups (1..256)", groups));
+  if (epilogue != kEpiStore && epilogue != kEpiSwiGLU) return R(fail(kInvalidArgument, "grouped GEMM: unknown epilogue %d", epilogue));
+  if (epilogue == kEpiSwiGLU && N % 64) return R(fail(kInvalidArgument, "grouped GEMM: the SwiGLU epilogue needs N to be a multiple of 64, got %d", N));
+  if ((long long)groups * N > 0x7fffffffLL) return R(fail(kInvalidArgument, "grouped GEMM: groups * N does not fit 31 bits"));
+  int dev = 0;
+  cudaGetDevice(&dev);
+  CtrlBlock* ctrl = nullptr;
+  uint32_t* status = nullptr;
+  if ((s = gemm_process_words(dev, &ctrl, &status)) != kSuccess) return R(s);
+  GemmLaunch g;
+  memset(&g, 0, sizeof(g));
+  g.p.M = rows_cap;
+  g.p.N = N;
+  g.p.K = K;
+  g.p.mode = kGemmGrouped;
+  g.p.C = C;
+  g.p.ldc = epilogue == kEpiSwiGLU ? N / 2 : N;
+  g.p.rows_per_rank = rows_cap;
+  g.p.group_off = group_off;
+  g.p.groups = groups;
+  g.p.epilogue = epilogue;
+  g.p.coll.rank = 0;
+  g.p.coll.nranks = 1;
+  g.p.coll.ctrl[0] = ctrl;
+  g.p.coll.status = status;
+  g.p.coll.timeout_ns = 5ull * 1000000000ull;
+  g.p.fflags[0] = (FusedFlags*)(ctrl + 1);
+  const int sms = gemm_default_grid(dev);
+  // every group ends in a partly filled row tile: count about half a tile of waste per group
+  const int hint = rows_hint > 0 ? rows_hint : rows_cap;
+  const int row_tiles = (hint + kGemmBM - 1) / kGemmBM + groups / 2;
+  int bn = gemm_pick_bn(row_tiles, N, sms);
+  if (epilogue == kEpiSwiGLU) bn = bn >= 224 ? 256 : (bn >= 160 ? 192 : 128);
+  g.p.bn = bn;
+  if ((s = make_tensor_map_bf16(&g.map_a, A, rows_cap, K, K, kGemmBM)) != kSuccess) return R(s);
+  g.map_a_local = g.map_a;
+  if ((s = make_tensor_map_bf16(&g.map_b, B, (uint64_t)groups * N, K, K, g.p.bn)) != kSuccess) return R(s);
+  g.grid = sms;
+  s = launch_gemm(g, stream);
+  if (s == kSuccess && status[0]) s = fail(kInternalError, "tcgen05 GEMM reported a device-side wait timeout (code %u)", status[0]);
   return R(s);
 }
 

@@ -218,6 +218,13 @@ ncclResult_t amemAlltoAllv(const void* sendbuff, const size_t* sendcounts, const
                            const size_t* recvcounts, const size_t* rdispls, ncclDataType_t datatype, ncclComm_t comm, cudaStream_t stream);
 ncclResult_t amemCheckCanary(ncclComm_t comm);
 ncclResult_t amemDebugDirtyCanary(ncclComm_t comm); /* test hook: dirties the guard */
+/* Grouped GEMM (one launch for all experts of a rank): for every group e,
+ * C[group_off[e] .. group_off[e+1], :] = A[same rows, :] * B[e]^T.  group_off is a DEVICE array of
+ * groups + 1 int32 row offsets (amemMoeDispatch's expert_offsets), B is bf16 [groups, N, K].
+ * epilogue 0: C is bf16 [rows_cap, N]; epilogue 1 (SwiGLU): B[e]'s rows alternate in blocks of 32
+ * gate rows and 32 up rows and C is bf16 [rows_cap, N / 2] = silu(gate) * up. */
+ncclResult_t amemGroupedGemmBf16(const void* A, const void* B, void* C, const int* group_off, int groups, int rows_cap, int rows_hint,
+                                 int N, int K, int epilogue, cudaStream_t stream);
 ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices);
 /* One kernel: C[M,N] = allgather_rows(a_shard)[M,K] * B[N,K]^T.  a_shard holds this rank's
  * M/nranks rows; the transfer of the other ranks' rows overlaps the tensor-core work. */

@@ -62,10 +62,40 @@ struct __align__(8) SmemCtl {
 };
 
 struct Tile {
-  int shard;      // owner rank of the rows (0 when not fused)
-  int m_in;       // row-block index inside the shard
+  int shard;      // owner rank of the rows (0 when not fused); grouped: the group
+  int m_in;       // row-block index inside the shard / group
   int n_blk;
+  int row0;       // grouped: first row of the tile in A and C
+  int rows;       // grouped: rows of the tile that belong to its group
 };
+
+// Grouped mode: tiles of all groups in one sequence, group after group, row blocks fastest.
+__device__ __forceinline__ int grouped_total_tiles(const GemmParams& p, int tiles_n) {
+  int total = 0;
+  for (int e = 0; e < p.groups; ++e) total += ((p.group_off[e + 1] - p.group_off[e] + BM - 1) / BM) * tiles_n;
+  return total;
+}
+__device__ __forceinline__ Tile grouped_tile_of(const GemmParams& p, int t, int tiles_n) {
+  Tile o;
+  o.shard = o.m_in = o.n_blk = o.row0 = o.rows = 0;
+  int acc = 0, first = p.group_off[0];
+  for (int e = 0; e < p.groups; ++e) {
+    const int next = p.group_off[e + 1];
+    const int rows = next - first, tm = (rows + BM - 1) / BM, cnt = tm * tiles_n;
+    if (t < acc + cnt) {
+      const int v = t - acc;
+      o.shard = e;
+      o.m_in = v % tm;
+      o.n_blk = v / tm;
+      o.row0 = first + o.m_in * BM;
+      o.rows = min(BM, rows - o.m_in * BM);
+      return o;
+    }
+    acc += cnt;
+    first = next;
+  }
+  return o;
+}
 
 // One unit of work of a compute CTA: a whole tile, or (tail split) a range of K blocks of one.
 struct Work {
@@ -101,7 +131,9 @@ __device__ __forceinline__ Work work_of(int i, int g, int G, int total_tiles, in
 // owners first (rank+1, rank+2, ...), my own rows last.
 __device__ __forceinline__ Tile tile_of(const GemmParams& p, int t, int tiles_m, int tiles_n) {
   const int n = p.coll.nranks, r = p.coll.rank;
+  if (p.mode == kGemmGrouped) return grouped_tile_of(p, t, tiles_n);
   Tile o;
+  o.row0 = o.rows = 0;
   if (p.mode == kGemmAllGather && n > 1) {
     int own = tiles_m * tiles_n;
     if (t < own) {
@@ -339,7 +371,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   const int BN = p.bn;
   const int tiles_n = (p.N + BN - 1) / BN;
   const int shards = (p.mode == kGemmPlain || n == 1) ? 1 : n;
-  const int total_tiles = tiles_m * tiles_n * shards;
+  const int total_tiles = p.mode == kGemmGrouped ? grouped_total_tiles(p, tiles_n) : tiles_m * tiles_n * shards;
   const int num_kb = (p.K + BK - 1) / BK;
   const int g = cta - comm_ctas, G = nctas - comm_ctas;  // compute CTA index / count
   const uint32_t idesc = make_idesc_bf16(BM, BN);
@@ -373,12 +405,17 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         }
         const CUtensorMap* ma = (p.mode == kGemmAllGather && fused && !remote) ? map_a_local : map_a;
         int row0 = tl.m_in * TM + ((p.mode == kGemmAllGather && fused && !remote) ? 0 : tl.shard * p.rows_per_rank);
+        int b_row0 = tl.n_blk * BN;
+        if (p.mode == kGemmGrouped) {
+          row0 = tl.row0;
+          b_row0 += tl.shard * p.N;   // group e's matrix starts at row e * N of the stacked B
+        }
         for (int kb = wk.kb0; kb < wk.kb1 && ok; ++kb) {
           ok = mbar_wait(&ctl->empty[stage], phase ^ 1u, p.coll.timeout_ns, abort);
           if (!ok) break;
           mbar_expect_tx(&ctl->full[stage], (uint32_t)(a_bytes + BN * BK * 2));
           tma_load_2d(ring + (size_t)stage * stage_bytes, ma, &ctl->full[stage], kb * BK, row0);  // box of TM rows
-          tma_load_2d(ring + (size_t)stage * stage_bytes + a_bytes, map_b, &ctl->full[stage], kb * BK, tl.n_blk * BN);
+          tma_load_2d(ring + (size_t)stage * stage_bytes + a_bytes, map_b, &ctl->full[stage], kb * BK, b_row0);
           issued |= 1u << stage;
           issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
           if (++stage == n_stages) {
@@ -584,9 +621,31 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       } else {
         {
           const int h = my_h;
-          const int row_in = tl.m_in * TM + h * BM + lane_grp * 32 + lane;  // row inside the shard
-          const bool row_ok = row_in < p.rows_per_rank;
-          __nv_bfloat16* dst_row = (__nv_bfloat16*)p.C + ((size_t)tl.shard * p.rows_per_rank + row_in) * p.ldc;
+          const bool grouped = p.mode == kGemmGrouped;
+          const int row_local = h * BM + lane_grp * 32 + lane;
+          const int row_in = tl.m_in * TM + row_local;  // row inside the shard
+          const bool row_ok = grouped ? row_local < tl.rows : row_in < p.rows_per_rank;
+          __nv_bfloat16* dst_row = (__nv_bfloat16*)p.C + (grouped ? (size_t)(tl.row0 + row_local) : (size_t)tl.shard * p.rows_per_rank + row_in) * p.ldc;
+          const bool swiglu = grouped && p.epilogue == kEpiSwiGLU;
+          // SwiGLU: chunk c holds 32 gate columns, chunk c + 1 the matching 32 up columns
+          auto store_swiglu = [&](const uint32_t* gate, const uint32_t* up, int c) {
+            const int col = (tl.n_blk * BN + c * 32) / 2;   // output column of the pair's first element
+            if (row_ok) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (col + j * 8 < p.N / 2) {
+                  alignas(16) __nv_bfloat162 h2[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    const float g0 = __uint_as_float(gate[j * 8 + 2 * q]), g1 = __uint_as_float(gate[j * 8 + 2 * q + 1]);
+                    const float u0 = __uint_as_float(up[j * 8 + 2 * q]), u1 = __uint_as_float(up[j * 8 + 2 * q + 1]);
+                    h2[q] = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                  }
+                  *(uint4*)(dst_row + col + j * 8) = *(const uint4*)h2;
+                }
+              }
+            }
+          };
           // two register buffers: the TMEM load of the next 32 columns is in flight while the
           // current ones are converted and stored
           auto store_chunk = [&](const uint32_t* v, int c) {
@@ -612,6 +671,12 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           for (int c = 0; c < nchunks; c += 2) {
             tmem_ld_wait();
             if (c + 1 < nchunks) tmem_ld_32x32(t_half + (uint32_t)((c + 1) * 32), vb);
+            if (swiglu) {   // the tile width is a multiple of 64 in this mode: chunks come in pairs
+              tmem_ld_wait();
+              store_swiglu(va, vb, c);
+              if (c + 2 < nchunks) tmem_ld_32x32(t_half + (uint32_t)((c + 2) * 32), va);
+              continue;
+            }
             store_chunk(va, c);
             if (c + 1 < nchunks) {
               tmem_ld_wait();

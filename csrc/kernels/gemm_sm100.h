@@ -16,7 +16,16 @@ static const int kGemmThreads = 192;       // warp 0: TMA producer, warp 1: MMA 
 static const int kAgUnitRows = 32;         // rows of A announced by one all-gather ready flag
 static const int kMaxUnits = 256;          // flag slots per source rank
 
-enum GemmMode : int { kGemmPlain = 0, kGemmAllGather = 1, kGemmReduceScatter = 2 };
+// kGemmGrouped: A [rows, K] holds `groups` runs of rows, run e = [group_off[e], group_off[e+1]) with
+// group_off in DEVICE memory (the MoE dispatch produces it there, nothing comes back to the host);
+// B stacks one [N, K] matrix per group as [groups * N, K]; C has A's rows.  Row tiles start at the
+// group's first row, whatever its alignment (TMA has no alignment rule on the row coordinate), and
+// the rows a tile has beyond its group are computed and not stored.
+enum GemmMode : int { kGemmPlain = 0, kGemmAllGather = 1, kGemmReduceScatter = 2, kGemmGrouped = 3 };
+// Epilogue of the grouped mode: plain store, or SwiGLU of column pairs — B's rows are then laid out
+// in alternating blocks of 32 gate rows and 32 up rows, the output has N / 2 columns and
+// out[:, 32 j + i] = silu(acc[:, 64 j + i]) * acc[:, 64 j + 32 + i].
+enum GemmEpilogue : int { kEpiStore = 0, kEpiSwiGLU = 1 };
 
 // Flags of the fused kernels; lives in every rank's control segment right after CtrlBlock,
 // so it is saved and restored by pause/resume like the rest of the protocol state.
@@ -42,6 +51,9 @@ struct GemmParams {
   void* rs_buf[kMaxRanks];  // reduce-scatter: every rank's partial buffer, tile-major [nranks][row blocks][col blocks][128 x 256]
   void* rs_out;             // reduce-scatter: bf16 [rows_per_rank, N]
   FusedFlags* fflags[kMaxRanks];
+  const int* group_off;     // grouped: device array of groups + 1 row offsets
+  int groups;               // grouped: number of groups (<= 256)
+  int epilogue;             // grouped: GemmEpilogue
   // Split-K of the last, partly filled wave of tiles (plain mode): each of its tiles is cut in
   // sk_slices ranges of K that run on different CTAs; partial accumulators meet in sk_ws
   // (fp32, [tile][slice][32-column chunk][128 rows][32]) and are summed in slice order.

@@ -290,25 +290,50 @@ class CudaBackend : public VmmBackend {
     return kSuccess;
   }
 
+  // Host shadows.  First choice: a VMM allocation of pinned host memory on the NUMA node the GPU
+  // hangs off (CU_MEM_LOCATION_TYPE_HOST_NUMA), mapped for the device and for the CPU, so the
+  // save / restore copies stay on the local socket's memory controller — what the reference does
+  // (amem_nccl_plugin/amem_nccl.h:237-283, with its fallback to node 0).  Where the driver or
+  // the machine refuses that (no NUMA id, old driver, cgroup limits), plain cudaHostAlloc.
+  // AMEM_HOST_NUMA=0 goes straight to cudaHostAlloc.
   Status host_alloc(size_t size, void** out) override {
     if (should_fail("host_alloc")) return fail(kSystemError, "cudaHostAlloc: injected failure");
-    RT(cudaHostAlloc(out, size ? size : 1, cudaHostAllocPortable), "cudaHostAlloc");
+    if (size == 0) size = 1;
+    static const long want_numa = env_long("AMEM_HOST_NUMA", 1);
+    if (want_numa && numa_host_alloc(size, out)) return kSuccess;
+    RT(cudaHostAlloc(out, size, cudaHostAllocPortable), "cudaHostAlloc");
     return kSuccess;
   }
   Status host_free(void* p, size_t) override {
+    HostVmm hv;
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      auto it = host_vmm_.find(p);
+      if (it == host_vmm_.end()) hv.handle = 0;
+      else {
+        hv = it->second;
+        host_vmm_.erase(it);
+      }
+    }
+    if (hv.handle) {
+      drv().MemUnmap((CUdeviceptr)p, hv.size);
+      drv().MemRelease((CUmemGenericAllocationHandle)hv.handle);
+      drv().MemAddressFree((CUdeviceptr)p, hv.size);
+      return kSuccess;
+    }
     RT(cudaFreeHost(p), "cudaFreeHost");
     return kSuccess;
   }
   Status copy_to_host_async(void* dst, uint64_t src_va, size_t size, int dev) override {
     cudaStream_t s;
     AMEM_TRY(side_stream(dev, &s));
-    RT(cudaMemcpyAsync(dst, (const void*)src_va, size, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync(D2H)");
+    RT(cudaMemcpyAsync(dst, (const void*)src_va, size, cudaMemcpyDefault, s), "cudaMemcpyAsync(D2H)");
     return kSuccess;
   }
   Status copy_to_device_async(uint64_t dst_va, const void* src, size_t size, int dev) override {
     cudaStream_t s;
     AMEM_TRY(side_stream(dev, &s));
-    RT(cudaMemcpyAsync((void*)dst_va, src, size, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync(H2D)");
+    RT(cudaMemcpyAsync((void*)dst_va, src, size, cudaMemcpyDefault, s), "cudaMemcpyAsync(H2D)");
     return kSuccess;
   }
   Status copies_sync(int dev) override {
@@ -379,6 +404,67 @@ class CudaBackend : public VmmBackend {
   size_t live_mappings() override { return (size_t)mappings_.load(); }
 
  private:
+  struct HostVmm {
+    uint64_t handle = 0;
+    size_t size = 0;
+  };
+  // Pinned host memory from the VMM allocator on the current device's NUMA node (node 0 as the
+  // second try).  Any failure leaves nothing behind and returns false.
+  bool numa_host_alloc(size_t size, void** out) {
+    int dev = 0, node = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    if (drv().DeviceGetAttribute(&node, CU_DEVICE_ATTRIBUTE_HOST_NUMA_ID, dev) != CUDA_SUCCESS || node < 0) node = 0;
+    CUmemAllocationProp prop;
+    memset(&prop, 0, sizeof(prop));
+    prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+    prop.location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
+    prop.location.id = node;
+    size_t gran = 0;
+    if (drv().MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM) != CUDA_SUCCESS || gran == 0) return false;
+    size_t sz = (size + gran - 1) / gran * gran;
+    CUmemGenericAllocationHandle h = 0;
+    if (drv().MemCreate(&h, sz, &prop, 0) != CUDA_SUCCESS) {
+      if (node == 0) return false;
+      prop.location.id = node = 0;
+      if (drv().MemCreate(&h, sz, &prop, 0) != CUDA_SUCCESS) return false;
+    }
+    CUdeviceptr va = 0;
+    if (drv().MemAddressReserve(&va, sz, gran, 0, 0) != CUDA_SUCCESS) {
+      drv().MemRelease(h);
+      return false;
+    }
+    if (drv().MemMap(va, sz, 0, h, 0) != CUDA_SUCCESS) {
+      drv().MemAddressFree(va, sz);
+      drv().MemRelease(h);
+      return false;
+    }
+    CUmemAccessDesc acc[2];
+    memset(acc, 0, sizeof(acc));
+    acc[0].location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+    acc[0].location.id = dev;
+    acc[0].flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    acc[1].location.type = CU_MEM_LOCATION_TYPE_HOST_NUMA;
+    acc[1].location.id = node;
+    acc[1].flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+    if (drv().MemSetAccess(va, sz, acc, 2) != CUDA_SUCCESS) {
+      drv().MemUnmap(va, sz);
+      drv().MemAddressFree(va, sz);
+      drv().MemRelease(h);
+      return false;
+    }
+    {
+      std::lock_guard<std::mutex> g(mu_);
+      HostVmm hv;
+      hv.handle = (uint64_t)h;
+      hv.size = sz;
+      host_vmm_[(void*)va] = hv;
+    }
+    *out = (void*)va;
+    return true;
+  }
   bool should_fail(const char* op) {
     std::lock_guard<std::mutex> g(mu_);
     auto it = inject_.find(op);
@@ -422,6 +508,7 @@ class CudaBackend : public VmmBackend {
   std::map<int, cudaStream_t> streams_;
   std::map<uint64_t, size_t> sizes_;
   std::map<std::string, int> inject_;
+  std::map<void*, HostVmm> host_vmm_;
   size_t live_bytes_ = 0;
   std::atomic<long> mappings_{0};
 };

@@ -105,3 +105,52 @@ def test_gemm_reduce_scatter(world, m_local, N, K):
         for out in outs:
             assert (out.float() - exact).abs().max().item() <= tol
         assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("counts,N,K", [([128, 256], 256, 64), ([5, 0, 300, 1, 129, 77], 264, 328), ([1000, 3, 0, 0, 2000, 511, 640, 130], 3072, 512),
+                                          ([0, 0, 0], 128, 64)])
+def test_grouped_gemm_reads_device_offsets(counts, N, K):
+    """One launch multiplies every group's rows by that group's matrix; groups start at rows of any
+    alignment, some are empty, the offsets never leave the device, rows past the last group stay
+    as they were."""
+    from asystem_amem_b200.ops import grouped_gemm_bf16
+    groups, total = len(counts), sum(counts)
+    cap = total + 200
+    a = _rand((cap, K), 5).cuda()
+    w = _rand((groups, N, K), 6, 0.05).cuda()
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32).cuda()
+    out = torch.full((cap, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    grouped_gemm_bf16(a, w, offs, out=out, rows_hint=total)
+    again = torch.full((cap, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    grouped_gemm_bf16(a, w, offs, out=again)
+    torch.cuda.synchronize()
+    lo = 0
+    for e, c in enumerate(counts):
+        ref = a[lo:lo + c].float() @ w[e].float().t()
+        if c:
+            err = (out[lo:lo + c].float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-2, (e, err)
+        lo += c
+    assert bool((out[total:] == 7.0).all())          # nothing stored outside the groups
+    assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("counts,ffn,K", [([200, 0, 57], 64, 128), ([300, 129, 1, 640], 1536, 512)])
+def test_grouped_gemm_swiglu_epilogue(counts, ffn, K):
+    """gate / up projection with silu(gate) * up computed in the epilogue on the fp32 accumulators."""
+    from asystem_amem_b200.ops import grouped_gemm_bf16, interleave_gate_up
+    groups, total = len(counts), sum(counts)
+    a = _rand((total + 10, K), 8).cuda()
+    w13 = _rand((groups, 2 * ffn, K), 9, 0.05).cuda()
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32).cuda()
+    out = grouped_gemm_bf16(a, interleave_gate_up(w13, ffn), offs, rows_hint=total, swiglu=True)
+    torch.cuda.synchronize()
+    assert out.shape == (total + 10, ffn)
+    lo = 0
+    for e, c in enumerate(counts):
+        h = a[lo:lo + c].float() @ w13[e].float().t()
+        ref = torch.nn.functional.silu(h[:, :ffn]) * h[:, ffn:]
+        if c:
+            err = (out[lo:lo + c].float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 1e-2, (e, err)
+        lo += c
