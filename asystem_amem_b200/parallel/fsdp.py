@@ -5,7 +5,10 @@ Each rank keeps only its 1/n shard (plus an fp32 master copy for the optimizer).
 forward all-gathers the flat buffer, runs, and frees it; its backward all-gathers again,
 recomputes the unit (activation checkpointing at unit granularity), back-propagates, and
 reduce-scatters the flat gradient with the averaging scale and the bf16 -> fp32 cast fused into
-the reduce-scatter kernel.  All communicator memory is pausable: ``pause_all()`` between steps
+the reduce-scatter kernel.  The all-gather of the NEXT unit (forward: i + 1, backward: i - 1) is
+issued on a side stream before the current unit computes, so it runs under that compute; and the
+parameters' ``.grad`` are views into one flat buffer, so the reduce-scatter reads what autograd
+wrote, without a packing pass.  All communicator memory is pausable: ``pause_all()`` between steps
 gives the staging memory back and ``resume_all()`` restores it without re-initialisation.
 
 Reference parity: none to match -- the reference implements no parallelism strategy, it pauses
@@ -43,13 +46,41 @@ class _ShardedUnit:
         for p in self.params:                                       # free the replicated storage
             p.data = torch.empty(0, dtype=p.dtype, device=dev)
         self.full = None
+        self._prefetched = None       # (buffer, event) of an all-gather issued ahead of time
+        self._gflat = None
+
+    def prefetch(self, side) -> None:
+        """Starts this unit's all-gather on ``side`` (CUDA stream); ``gather`` picks it up."""
+        if self._prefetched is not None or self.full is not None or side is None:
+            return
+        with torch.cuda.stream(side):
+            buf = torch.empty(self.padded, dtype=torch.bfloat16, device=self.shard.device)
+            self.comm.all_gather(self.shard, buf, stream=side)
+            ev = torch.cuda.Event()
+            ev.record(side)
+        self._prefetched = (buf, ev)
 
     def gather(self) -> None:
-        self.full = torch.empty(self.padded, dtype=torch.bfloat16, device=self.shard.device)
-        self.comm.all_gather(self.shard, self.full)
+        if self._prefetched is not None:
+            self.full, ev = self._prefetched
+            self._prefetched = None
+            torch.cuda.current_stream().wait_event(ev)
+            self.full.record_stream(torch.cuda.current_stream())
+        else:
+            self.full = torch.empty(self.padded, dtype=torch.bfloat16, device=self.shard.device)
+            self.comm.all_gather(self.shard, self.full)
         off = 0
         for p, k, shp in zip(self.params, self.numels, self._shapes):
             p.data = self.full[off:off + k].view(shp)
+            off += k
+
+    def attach_flat_grads(self) -> None:
+        """``.grad`` of every parameter becomes a zeroed view into one flat bf16 buffer: autograd
+        accumulates straight into what the reduce-scatter will read."""
+        self._gflat = torch.zeros(self.padded, dtype=torch.bfloat16, device=self.shard.device)
+        off = 0
+        for p, k, shp in zip(self.params, self.numels, self._shapes):
+            p.grad = self._gflat[off:off + k].view(shp)
             off += k
 
     def release(self) -> None:
@@ -59,13 +90,17 @@ class _ShardedUnit:
         self.full = None
 
     def reduce_grads(self) -> None:
-        flat = torch.zeros(self.padded, dtype=torch.bfloat16, device=self.shard.device)
-        off = 0
-        for p, k in zip(self.params, self.numels):
-            if p.grad is not None:
-                flat[off:off + k] = p.grad.reshape(-1)
-                p.grad = None
-            off += k
+        flat = self._gflat
+        if flat is None:                      # gradients were not attached: pack them
+            flat = torch.zeros(self.padded, dtype=torch.bfloat16, device=self.shard.device)
+            off = 0
+            for p, k in zip(self.params, self.numels):
+                if p.grad is not None:
+                    flat[off:off + k] = p.grad.reshape(-1)
+                off += k
+        for p in self.params:
+            p.grad = None
+        self._gflat = None
         out = torch.empty(self.shard_len, dtype=torch.float32, device=flat.device)
         # sum over ranks, times 1/n, bf16 -> fp32: one kernel
         self.comm.reduce_scatter(flat, out, scale=1.0 / self.comm.nranks)
@@ -79,6 +114,8 @@ class _UnitFn(torch.autograd.Function):
         ctx.unit, ctx.extras = unit, extras
         ctx.save_for_backward(x)
         unit.gather()
+        if unit.next_unit is not None:
+            unit.next_unit.prefetch(unit.side)      # runs under this unit's compute
         with torch.no_grad():
             y = unit.module(x, *extras)
         unit.release()
@@ -89,6 +126,9 @@ class _UnitFn(torch.autograd.Function):
         unit = ctx.unit
         (x,) = ctx.saved_tensors
         unit.gather()
+        if unit.prev_unit is not None:
+            unit.prev_unit.prefetch(unit.side)      # the backward pass visits the units in reverse
+        unit.attach_flat_grads()
         with torch.enable_grad():
             xin = x.detach().requires_grad_(x.is_floating_point())
             y = unit.module(xin, *ctx.extras)
@@ -104,6 +144,12 @@ class FSDP:
     def __init__(self, model: nn.Module, comm):
         self.model, self.comm = model, comm
         self.units = [_ShardedUnit(u, comm, f"unit{i}") for i, u in enumerate(model.units)]
+        dev = self.units[0].shard.device
+        side = torch.cuda.Stream(device=dev) if dev.type == "cuda" else None
+        for i, u in enumerate(self.units):
+            u.side = side
+            u.next_unit = self.units[i + 1] if i + 1 < len(self.units) else None
+            u.prev_unit = self.units[i - 1] if i > 0 else None
         self._anchor = torch.zeros(1, device=self.units[0].shard.device, requires_grad=True)
 
     def forward_units(self, x, *extras):

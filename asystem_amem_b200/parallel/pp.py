@@ -86,6 +86,64 @@ class PipelineStage:
         return outs if self.stage == self.n - 1 else None
 
 
+    def run_1f1b(self, stage_fn, micro_batches, act_like: torch.Tensor, loss_fn=None):
+        """One-forward-one-backward training schedule (PipeDream-flush / Megatron's non-interleaved
+        1F1B).  Stage s runs ``n - 1 - s`` warm-up forwards, then alternates one forward with one
+        backward, then drains its remaining backwards; at most ``n - s`` micro-batches are alive
+        on a stage at any time (GPipe keeps all of them).
+
+        ``stage_fn(x)`` is this stage's differentiable forward; parameter gradients accumulate in
+        ``.grad`` over the micro-batches.  ``micro_batches``: on stage 0 the inputs, elsewhere
+        only its length matters.  ``loss_fn(y, i)`` (last stage) returns the scalar loss of
+        micro-batch ``i``.  Returns the list of losses on the last stage, None elsewhere.
+        Every transfer is a send or receive of ``act_like``'s shape and dtype with the
+        neighbouring stage, issued in the same order on both sides."""
+        m = len(micro_batches)
+        first, last = self.stage == 0, self.stage == self.n - 1
+        warm = min(self.n - 1 - self.stage, m)
+        live = []          # (input that needs a gradient or None, output) of forwards awaiting their backward
+        losses = []
+        done_f = done_b = 0
+
+        def forward():
+            nonlocal done_f
+            i = done_f
+            done_f += 1
+            x = micro_batches[i] if first else self.recv_forward(act_like)
+            xin = x if first else x.detach().requires_grad_(True)
+            y = stage_fn(xin)
+            if last:
+                loss = loss_fn(y, i)
+                losses.append(loss.detach())
+                live.append((xin, loss))
+            else:
+                self.send_forward(y.detach())
+                live.append((xin, y))
+
+        def backward():
+            nonlocal done_b
+            done_b += 1
+            xin, y = live.pop(0)
+            if last:
+                y.backward()
+            else:
+                g = self.recv_backward(act_like)
+                y.backward(g)
+            if not first:
+                self.send_backward(xin.grad)
+
+        for _ in range(warm):
+            forward()
+        for _ in range(m - warm):
+            forward()
+            backward()
+        while done_b < m:
+            backward()
+        if self.side is not None:
+            torch.cuda.current_stream().wait_stream(self.side)
+        return losses if last else None
+
+
 def _is_cpu_comm(comm) -> bool:
     from ..comm import backend_usage
     return backend_usage()["backend"] != "cuda"

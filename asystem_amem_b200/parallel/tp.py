@@ -3,7 +3,7 @@
 Activations between the two linears of a block are sharded by rows (tokens).  The
 column-parallel linear all-gathers them inside its GEMM kernel; the row-parallel linear
 reduce-scatters its output from the GEMM epilogue.  Backward uses the mirrored fused kernels
-for the activation gradients and a library GEMM for the weight gradients.
+for the activation gradients and the library's own tcgen05 GEMM for the weight gradients.
 
 Reference parity: none to match -- tensor parallelism appears in the reference only as
 integration text (README.md:279-293, SGLang's tensor-model-parallel group); its users run
@@ -14,7 +14,17 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..ops.gemm import all_gather_gemm, gemm_reduce_scatter
+from ..ops.gemm import all_gather_gemm, gemm_bf16, gemm_reduce_scatter
+
+
+def _wgrad(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """gw[N, K] = gy[M, N].T @ x[M, K] on the library's tcgen05 GEMM, whose operands are both
+    K-major: A = gy.T [N, M], B = x.T [K, M] (two transposing copies, then one tensor-core pass
+    with fp32 accumulation over the M tokens).  Token counts that are not a multiple of 8 (the
+    16-byte row rule of the TMA loads) fall back to a PyTorch matmul."""
+    if gy.is_cuda and gy.shape[0] % 8 == 0 and gy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16:
+        return gemm_bf16(gy.t().contiguous(), x.t().contiguous())
+    return gy.t() @ x
 
 
 class _ColumnFn(torch.autograd.Function):
@@ -35,7 +45,7 @@ class _ColumnFn(torch.autograd.Function):
         gx = gemm_reduce_scatter(comm, gy, w.t().contiguous())
         x_full = torch.empty(x_shard.shape[0] * comm.nranks, x_shard.shape[1], dtype=x_shard.dtype, device=x_shard.device)
         comm.all_gather(x_shard.contiguous(), x_full)
-        gw = gy.t() @ x_full
+        gw = _wgrad(gy, x_full)
         return gx, gw, None
 
 
@@ -57,7 +67,7 @@ class _RowFn(torch.autograd.Function):
         gx = all_gather_gemm(comm, gy_shard, w.t().contiguous())
         gy_full = torch.empty(gy_shard.shape[0] * comm.nranks, gy_shard.shape[1], dtype=gy_shard.dtype, device=gy_shard.device)
         comm.all_gather(gy_shard, gy_full)
-        gw = gy_full.t() @ x
+        gw = _wgrad(gy_full, x)
         return gx, gw, None
 
 

@@ -225,6 +225,7 @@ def main() -> None:
     def step(i: int, record: bool):
         """One cycle.  Returns (pause_ms, resume_ms, allreduce_ms, freed_bytes, e2e_ms)."""
         nonlocal bad_words
+        host_barrier()      # every rank has finished checking the previous step (ranks read each other's memory there)
         touch(i)
         torch.cuda.synchronize()
         host_barrier()

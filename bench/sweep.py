@@ -4,7 +4,8 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29520 bench/sweep.py [--max-bytes 8589934592] [--colls allreduce,allgather,...]
 
-For every collective, dtype (bf16, fp32) and message size (8 B doubling up to --max-bytes) it
+Collectives: allreduce, allgather, reducescatter, alltoall, broadcast (the reference's run.sh:22 set plus
+reduce-scatter).  For every collective, dtype (bf16, fp32) and message size (8 B doubling up to --max-bytes) it
 times this library and NCCL with CUDA events on the launching stream (3 warm-ups, L2 flushed
 between iterations, max over ranks) and, like the reference's patched nccl-tests, calls
 ncclPause()/ncclResume() once between sizes.  busBW follows nccl-tests: all-reduce
@@ -34,6 +35,9 @@ def main():
     ap.add_argument("--colls", default="allreduce,allgather,reducescatter,alltoall")
     ap.add_argument("--dtypes", default="bf16,fp32")
     ap.add_argument("--no-pause", action="store_true")
+    ap.add_argument("--window", action="store_true",
+                    help="all-reduce between two registered windows (ncclMemAlloc + ncclCommWindowRegister): in place on the peers' "
+                         "memory, no staging; NCCL gets buffers from its own registered memory pool as the like-for-like arm")
     ap.add_argument("--out", default="bench_results/sweep.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
@@ -48,6 +52,20 @@ def main():
         os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
     out_f = open(args.out, "a") if rank == 0 else None
     dts = {"bf16": torch.bfloat16, "fp32": torch.float32}
+    win_a = win_b = None
+    nccl_pool = None
+    if args.window:
+        win_a, win_b = comm.window_alloc(args.max_bytes), comm.window_alloc(args.max_bytes)
+        try:   # NCCL's user-buffer registration: tensors from a pool backed by ncclMemAlloc, registered with the communicator
+            backend = dist.distributed_c10d._get_default_group()._get_backend(torch.device("cuda"))
+            nccl_pool = torch.cuda.MemPool(backend.mem_allocator)
+            with torch.cuda.use_mem_pool(nccl_pool):
+                nccl_buf = torch.empty(args.max_bytes, dtype=torch.uint8, device="cuda")
+            backend.register_mem_pool(nccl_pool)
+        except Exception as e:  # noqa: BLE001
+            nccl_pool = None
+            if rank == 0:
+                print(json.dumps({"nccl_registered_pool": f"unavailable: {type(e).__name__}: {e}"}), flush=True)
 
     def timed(fn, iters):
         for _ in range(3):
@@ -80,10 +98,23 @@ def main():
                 iters = 20 if nbytes <= (64 << 20) else 5
                 x = torch.randn(n, device="cuda", dtype=torch.float32).to(dt)
                 y = torch.empty_like(x)
+                ref_reg = None
                 if coll == "allreduce":
-                    ours = lambda: comm.all_reduce(x, y)
+                    if args.window:
+                        xw, yw = win_a.tensor(dt, n), win_b.tensor(dt, n)
+                        xw.copy_(x)
+                        ours = lambda: comm.all_reduce(xw, yw)
+                        if nccl_pool is not None:
+                            yr = nccl_buf[:nbytes].view(dt)
+                            ref_reg = lambda: dist.all_reduce(yr)
+                    else:
+                        ours = lambda: comm.all_reduce(x, y)
                     ref = lambda: dist.all_reduce(y)
                     factor = 2 * (world - 1) / world
+                elif coll == "broadcast":
+                    ours = lambda: comm.broadcast(x, y, root=0)
+                    ref = lambda: dist.broadcast(y, src=0)
+                    factor = 1.0
                 elif coll == "allgather":
                     ours = lambda: comm.all_gather(x[: n // world], y)
                     ref = lambda: dist.all_gather_into_tensor(y, x[: n // world])
@@ -103,6 +134,12 @@ def main():
                        "amem_busbw_gbs": round(nbytes / (t_ours * 1e-3) * factor / 1e9, 2),
                        "nccl_busbw_gbs": round(nbytes / (t_ref * 1e-3) * factor / 1e9, 2),
                        "speedup": round(t_ref / t_ours, 3)}
+                if args.window and coll == "allreduce":
+                    row["window"] = True
+                    if ref_reg is not None:
+                        t_reg = timed(ref_reg, iters)
+                        row["nccl_registered_us"] = round(t_reg * 1e3, 2)
+                        row["nccl_registered_busbw_gbs"] = round(nbytes / (t_reg * 1e-3) * factor / 1e9, 2)
                 if not args.no_pause:
                     pause_all()
                     resume_all()
@@ -119,6 +156,9 @@ def main():
     err = comm.async_error()
     if rank == 0:
         print(json.dumps({"device_errors": err}), flush=True)
+    if win_a is not None:
+        win_b.free()
+        win_a.free()
     comm.destroy()
     dist.destroy_process_group()
 

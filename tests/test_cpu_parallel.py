@@ -108,6 +108,48 @@ def test_pipeline_forward_schedule():
     assert res[2] == [((2 * (i + 1) + 0) * 2 + 1) * 2 + 2 for i in range(3)]
 
 
+def _pipeline_1f1b(rank, world, uid):
+    """Three stages, five micro-batches, one linear layer per stage: losses and every stage's
+    accumulated weight gradient must equal those of the same three layers run in one process."""
+    import torch
+    from asystem_amem_b200 import Communicator
+    from asystem_amem_b200.parallel import PipelineStage
+    comm = Communicator(world, rank, uid)
+    torch.manual_seed(0)
+    layers = [torch.nn.Linear(8, 8) for _ in range(world)]        # same on every rank (same seed)
+    g = torch.Generator().manual_seed(1)
+    mbs = [torch.randn(4, 8, generator=g) for _ in range(5)]
+    targets = [torch.randn(4, 8, generator=g) for _ in range(5)]
+    mine = layers[rank]
+    stage = PipelineStage(comm, rank, world)
+    losses = stage.run_1f1b(lambda x: torch.tanh(mine(x)), mbs, torch.empty(4, 8),
+                            loss_fn=lambda y, i: ((y - targets[i]) ** 2).mean())
+    got_grad = mine.weight.grad.clone()
+    # reference: the whole pipeline in this process
+    ref_layers = [torch.nn.Linear(8, 8) for _ in range(world)]
+    for a, b in zip(ref_layers, layers):
+        a.load_state_dict(b.state_dict())
+    ref_losses = []
+    for x, t in zip(mbs, targets):
+        h = x
+        for layer in ref_layers:
+            h = torch.tanh(layer(h))
+        loss = ((h - t) ** 2).mean()
+        loss.backward()
+        ref_losses.append(float(loss))
+    comm.destroy()
+    err = float((got_grad - ref_layers[rank].weight.grad).abs().max())
+    return err, None if losses is None else [float(v) for v in losses], ref_losses
+
+
+def test_pipeline_1f1b_matches_single_process_gradients():
+    res = run_ranks(_pipeline_1f1b, 3)
+    for err, _losses, _ref in res:
+        assert err < 1e-5, res
+    assert res[0][1] is None and res[1][1] is None
+    assert all(abs(a - b) < 1e-5 for a, b in zip(res[2][1], res[2][2])), res[2]
+
+
 def _context_parallel(rank, world, uid, causal):
     import torch
     from asystem_amem_b200 import Communicator
