@@ -251,9 +251,32 @@ Status pause_scopes(Registry& reg, VmmBackend* be, std::vector<EngineScope>& sco
       }
     }
   }
-  {  // 3. saves done -> drop the local physical memory, keep the addresses
+  {  // 3. drop the local physical memory, keep the addresses: first what needs no save (it goes
+     //    while the copies of the rest still run), then, once the saves are done, the rest
     Phase p("amem.pause.release_local");
     add_slot(p, ws, &PauseResumeStats::release_local_us);
+    auto release_one = [&](Work& w, Allocation& a) {
+      Status s = kSuccess;
+      if (a.mc_handle) s = be->mc_unbind(a.mc_handle, a.dev, a.mc_offset, a.size);
+      if (s == kSuccess) s = be->unmap(a.va, a.size);
+      if (s == kSuccess) s = be->release(a.handle);
+      if (s != kSuccess) {
+        w.note(s);
+        a.state = kMemAlloc;
+        reg.update(a);
+        return;
+      }
+      a.handle = 0;
+      a.state = kMemHole;
+      reg.update(a);
+      if (w.stats()) {
+        w.stats()->bytes_released_local += a.size;
+        w.stats()->n_release_local++;
+      }
+    };
+    for (auto& w : ws)
+      for (auto& a : w.recs)
+        if (is_local(a) && a.state == kMemAlloc && a.category != kResident) release_one(w, a);
     Status copies = kSuccess;
     std::string copies_err;
     for (int d : devs) {
@@ -269,29 +292,13 @@ Status pause_scopes(Registry& reg, VmmBackend* be, std::vector<EngineScope>& sco
         w.note(copies);
       }
       for (auto& a : w.recs) {
-        if (!is_local(a) || (a.state != kMemAlloc && a.state != kMemOffloading) || a.category == kResident) continue;
-        if (copies != kSuccess && a.state == kMemOffloading) {  // its save did not finish: the memory stays
+        if (!is_local(a) || a.state != kMemOffloading) continue;
+        if (copies != kSuccess) {  // its save did not finish: the memory stays
           a.state = kMemAlloc;
           reg.update(a);
           continue;
         }
-        Status s = kSuccess;
-        if (a.mc_handle) s = be->mc_unbind(a.mc_handle, a.dev, a.mc_offset, a.size);
-        if (s == kSuccess) s = be->unmap(a.va, a.size);
-        if (s == kSuccess) s = be->release(a.handle);
-        if (s != kSuccess) {
-          w.note(s);
-          a.state = kMemAlloc;
-          reg.update(a);
-          continue;
-        }
-        a.handle = 0;
-        a.state = kMemHole;
-        reg.update(a);
-        if (w.stats()) {
-          w.stats()->bytes_released_local += a.size;
-          w.stats()->n_release_local++;
-        }
+        release_one(w, a);
       }
     }
   }
