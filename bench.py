@@ -243,11 +243,11 @@ def main() -> None:
         t1 = time.perf_counter()
         pause()
         t2 = time.perf_counter()
-        free1 = mem_free()                                       # instrumentation, outside every timed window
-        t2a = time.perf_counter()
         if args.impl == "reference":
             host_barrier()                                       # the reference leaves this barrier to its caller (README.md:160-171):
-        t2b = time.perf_counter()                                # counted in e2e, not in pause / resume
+        t2a = time.perf_counter()                                # counted in e2e, not in pause / resume
+        free1 = mem_free()                                       # instrumentation, outside every timed window (pages of shared
+        t2b = time.perf_counter()                                # memory return once every rank has let go: after the barrier)
         resume()
         t3 = time.perf_counter()
         collective()
@@ -256,7 +256,7 @@ def main() -> None:
         t4 = time.perf_counter()
         ar_ms = ev[0].elapsed_time(ev[1])
         bad_words += verify(i)
-        return (t2 - t1) * 1e3, (t3 - t2b) * 1e3, ar_ms, free1 - free0, (t4 - t0 - (t2a - t2)) * 1e3
+        return (t2 - t1) * 1e3, (t3 - t2b) * 1e3, ar_ms, free1 - free0, (t4 - t0 - (t2b - t2a)) * 1e3
 
     # NVML comes up here, before any timed step; clocks are read once per step while the timed
     # all-reduce runs on the GPU (never across pause / resume, which such queries slow down)

@@ -121,6 +121,7 @@ Status Comm::init(const UniqueId& id, int nranks, int rank, const CommConfig& cf
     AMEM_TRY(be_->memset_zero(stage_.va[rank_] + stage_.size - canary_bytes_, canary_bytes_, dev_));
     AMEM_TRY(be_->copies_sync(dev_));
   }
+  AMEM_TRY(clear_ll_area());
   int want_nvls = cfg.nvls >= 0 ? cfg.nvls : (int)env_long("AMEM_NVLS", 1);
   if (device && !emulate && nranks > 1 && all_mc && want_nvls) {
     Status st = setup_multicast(&stage_, stage_.va[rank_]);
@@ -226,6 +227,24 @@ Status Comm::fused_segment(int which, size_t bytes, Segment** out) {
   AMEM_TRY(sym_alloc(bytes, kScratch, kTagSymm, &s));
   if (nranks_ > 1) AMEM_TRY(mesh_->barrier());
   *out = &s;
+  return kSuccess;
+}
+
+// The flag-in-data slots must never hold a word that looks like a packet of a coming operation:
+// fresh physical memory (at creation and after every resume) is cleared, flags start at 1.
+Status Comm::clear_ll_area() {
+  const size_t layout = stage_.size - canary_bytes_;
+  const size_t ll = ll_area_bytes(p2p_slot_bytes_);
+  AMEM_TRY(be_->memset_zero(stage_.va[rank_] + layout - ll, ll, dev_));
+  AMEM_TRY(be_->copies_sync(dev_));
+  // and again whenever resume maps new memory here (the engine does it before its closing
+  // agreement, so no peer can be writing packets yet); the guard granule behind it likewise
+  Allocation rec;
+  if (Registry::instance().find(stage_.va[rank_], &rec)) {
+    rec.clear_offset = layout - ll;
+    rec.clear_bytes = ll + canary_bytes_;
+    AMEM_TRY(Registry::instance().update(rec));
+  }
   return kSuccess;
 }
 

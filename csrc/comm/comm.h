@@ -147,6 +147,7 @@ class Comm {
   // `local_va`), binds every rank's memory and maps it; on failure the segment simply has none.
   Status setup_multicast(Segment* seg, uint64_t local_va);
   Status drop_window(Window* w, bool collective);
+  Status clear_ll_area();
   Status flush_p2p(cudaStream_t stream);
   Status after_resume(Status engine_result);   // caller holds mu_
   Status run(const CollArgs& a, const LaunchPlan& plan, cudaStream_t stream);

@@ -24,6 +24,7 @@ static const int kMaxRanks = 8;        // one NVLink/NVSwitch domain
 static const int kMaxBlocks = 512;     // flag rows available to one launch
 static const int kP2PBlocks = 32;      // blocks of a send/recv launch, per peer
 static const int kStatusWords = 16;
+static const int kLLBlocks = 8;        // blocks of a flag-in-data (small message) launch
 
 // Collective kinds (values are part of the host<->kernel contract only).
 enum CollKind : int {
@@ -39,7 +40,9 @@ enum CollKind : int {
 // Allreduce variants chosen by the tuner.
 // kAlgoWindow: both buffers lie in registered windows, the all-reduce works on them in place
 // (through the windows' multicast mapping when there is one, by peer loads and stores otherwise).
-enum Algo : int { kAlgoAuto = 0, kAlgoOneShot = 1, kAlgoTwoShot = 2, kAlgoNvls = 3, kAlgoWindow = 4 };
+// kAlgoLL: small messages travel as 8-byte packets {4 bytes of data, 4-byte flag}; the receiver polls
+// the packets themselves, so there is no barrier and no fence between the data and its signal.
+enum Algo : int { kAlgoAuto = 0, kAlgoOneShot = 1, kAlgoTwoShot = 2, kAlgoNvls = 3, kAlgoWindow = 4, kAlgoLL = 5 };
 
 // ncclDataType_t / ncclRedOp_t numbering.
 // 8-bit floats are carried by the copy collectives (all-gather, all-to-all, broadcast, send/recv);
@@ -76,6 +79,11 @@ struct alignas(128) CtrlBlock {
   uint32_t cseq[kMaxBlocks];
   uint32_t ready[kMaxBlocks][kMaxRanks];
   uint32_t freed[kMaxBlocks][kMaxRanks];
+  // flag-in-data protocol, per block: ll_seq = such operations this block has done (mine, also the
+  // flag value of the next one); ll_ack[b][s] = written by rank s: it has consumed my operation N.
+  // A slot is rewritten two operations later, after the receiver's ack for the earlier one.
+  uint32_t ll_seq[kLLBlocks];
+  uint32_t ll_ack[kLLBlocks][kMaxRanks];
 };
 
 enum DeviceError : uint32_t { kDevOk = 0, kDevBarrierTimeout = 1, kDevP2PTimeout = 2, kDevBadArgs = 3, kDevGemmTimeout = 4 };
@@ -132,7 +140,15 @@ struct LaunchPlan {
 #else
 #define AMEM_HD inline
 #endif
-AMEM_HD size_t p2p_area_bytes(size_t p2p_slot_bytes) { return (size_t)kMaxRanks * 2 * kP2PBlocks * p2p_slot_bytes; }
+// [ half 0 | half 1 | p2p slots | flag-in-data slots ]: the last two form the reserved tail.
+// A flag-in-data slot holds one source rank's packets of one operation (two parities alternate):
+// twice the bytes of a p2p slot, i.e. p2p_slot_bytes of payload per peer.
+AMEM_HD size_t ll_slot_bytes(size_t p2p_slot_bytes) { return 2 * p2p_slot_bytes; }
+AMEM_HD size_t ll_area_bytes(size_t p2p_slot_bytes) { return (size_t)kMaxRanks * 2 * ll_slot_bytes(p2p_slot_bytes); }
+AMEM_HD size_t p2p_area_bytes(size_t p2p_slot_bytes) { return (size_t)kMaxRanks * 2 * kP2PBlocks * p2p_slot_bytes + ll_area_bytes(p2p_slot_bytes); }
+AMEM_HD size_t ll_slot_offset(size_t stage_bytes, size_t p2p_slot_bytes, int src, uint32_t parity) {
+  return stage_bytes - ll_area_bytes(p2p_slot_bytes) + (size_t)(src * 2 + (int)(parity & 1u)) * ll_slot_bytes(p2p_slot_bytes);
+}
 AMEM_HD size_t quarter_bytes(size_t stage_bytes, size_t p2p_slot_bytes) {
   size_t q = (stage_bytes - p2p_area_bytes(p2p_slot_bytes)) / 4;
   return q & ~(size_t)4095;

@@ -172,6 +172,76 @@ AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
     });
 }
 
+// Small all-to-all without a barrier: every 4 bytes travel in an 8-byte packet together with the
+// operation's flag, straight into the receiver's flag-in-data slot for this source; the receiver
+// polls the packets and copies the payload out.  Nothing orders "data" before "signal" because they
+// are the same store.  Slots alternate between two parities; a slot is rewritten two operations
+// later, and only after the receiver has acknowledged the earlier one (CtrlBlock::ll_ack), an
+// acknowledgement that normally arrived long before it is looked at.  The flag is the block's
+// operation count, which starts at 1: zeroed memory never looks like a packet.
+template <typename TI, typename TO, int OP>
+AMEM_FN void body_alltoall_ll(const CollArgs& a, Proto& p) {
+  const int n = a.nranks, r = a.rank;
+  const size_t B = a.count * sizeof(TI);          // bytes exchanged with each peer
+  const size_t words = (B + 3) / 4;
+  const uint32_t L = ld_volatile(&p.me->ll_seq[p.block]) + 1u;
+  const int tid = thread_index();
+  const Lane ln = full_lane();
+  // words [w0, w1) of every peer's block are this block's share
+  const size_t per = (words + p.nblocks - 1) / p.nblocks;
+  size_t w0 = (size_t)p.block * per, w1 = w0 + per;
+  if (w0 > words) w0 = words;
+  if (w1 > words) w1 = words;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  if (L > 2u) {  // my operation L-2 used the slots I am about to overwrite
+    for (int q = tid; q < n; q += ln.nt) {
+      if (q == r) continue;
+      if (*(volatile int*)p.abort_flag == 0 && !wait_flag_ge(&p.me->ll_ack[p.block][q], L - 2u, a.timeout_ns)) {
+        report_error(a.status, kDevBarrierTimeout, a.rank, q, p.block, L);
+        *(volatile int*)p.abort_flag = 1;
+      }
+    }
+    block_sync();
+  }
+  auto word_of = [&](const char* base, size_t w) -> uint32_t {
+    if (w * 4 + 4 <= B && (((uintptr_t)base) & 3) == 0) return *(const uint32_t*)(base + w * 4);
+    uint32_t v = 0;
+    for (size_t b = 0; b < 4 && w * 4 + b < B; ++b) v |= (uint32_t)(unsigned char)base[w * 4 + b] << (8 * b);
+    return v;
+  };
+  for (int k = 1; k < n; ++k) {
+    const int q = peer_at(r, n, k, p.block);
+    char* dst = a.stage[q] + ll_slot_offset(a.stage_bytes, a.p2p_slot_bytes, r, L);
+    const char* src = send + (size_t)q * B;
+    for (size_t w = w0 + tid; w < w1; w += ln.nt) ll_store(dst + w * 8, word_of(src, w), L);
+  }
+  if (send != recv) copy_span(recv + (size_t)r * B + w0 * 4, send + (size_t)r * B + w0 * 4, (w1 * 4 < B ? w1 * 4 : B) - (w0 * 4 < B ? w0 * 4 : B), ln);
+  for (int k = 1; k < n; ++k) {
+    const int q = peer_at(r, n, k, p.block);
+    const char* src = a.stage[r] + ll_slot_offset(a.stage_bytes, a.p2p_slot_bytes, q, L);
+    char* dst = recv + (size_t)q * B;
+    for (size_t w = w0 + tid; w < w1; w += ln.nt) {
+      uint32_t v = 0;
+      if (*(volatile int*)p.abort_flag != 0) break;
+      if (!ll_wait(src + w * 8, L, &v, a.timeout_ns)) {
+        report_error(a.status, kDevBarrierTimeout, a.rank, q, p.block, L);
+        *(volatile int*)p.abort_flag = 1;
+        break;
+      }
+      if (w * 4 + 4 <= B && (((uintptr_t)dst) & 3) == 0) {
+        *(uint32_t*)(dst + w * 4) = v;
+      } else {
+        for (size_t b = 0; b < 4 && w * 4 + b < B; ++b) dst[w * 4 + b] = (char)(v >> (8 * b));
+      }
+    }
+  }
+  block_sync();  // every thread has taken its packets out of the slots
+  for (int q = tid; q < n; q += ln.nt)
+    if (q != r) st_release_sys(&a.ctrl[q]->ll_ack[p.block][r], L);
+  if (tid == 0) p.me->ll_seq[p.block] = L;
+}
+
 // Reduce-scatter with the optional fused scale and output-type cast (gradient averaging and
 // fp32 <-> bf16 conversion happen in the same pass that reduces).
 template <typename TI, typename TO, int OP>
@@ -590,7 +660,10 @@ AMEM_FN void run_body(const CollArgs& a, int block, int nblocks, int* s_abort, s
     switch (a.kind) {
       case kCollAllGather: body_allgather<TI, TO, OP>(a, p, chunk_elems); break;
       case kCollBroadcast: body_broadcast<TI, TO, OP>(a, p, chunk_elems); break;
-      case kCollAllToAll: body_alltoall<TI, TO, OP>(a, p, chunk_elems); break;
+      case kCollAllToAll:
+        if (a.algo == kAlgoLL) body_alltoall_ll<TI, TO, OP>(a, p);
+        else body_alltoall<TI, TO, OP>(a, p, chunk_elems);
+        break;
       default: break;
     }
   }

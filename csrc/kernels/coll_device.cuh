@@ -28,6 +28,14 @@ __device__ __forceinline__ uint32_t ld_volatile(const uint32_t* p) {
   asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// One flag-in-data packet: 4 bytes of payload and the operation's flag in ONE 8-byte store / load,
+// so the two can never be seen apart.
+__device__ __forceinline__ void ll_store(void* p, uint32_t data, uint32_t flag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(data), "r"(flag) : "memory");
+}
+__device__ __forceinline__ void ll_load(const void* p, uint32_t* data, uint32_t* flag) {
+  asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(*data), "=r"(*flag) : "l"(p) : "memory");
+}
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -54,6 +62,22 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t want
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+    }
+    if (globaltimer_ns() - t0 > timeout_ns) return false;
+  }
+}
+
+// Polls one packet until it carries `flag` or the time budget is spent (false).
+__device__ __forceinline__ bool ll_wait(const void* p, uint32_t flag, uint32_t* data, unsigned long long timeout_ns) {
+  uint32_t f;
+  ll_load(p, data, &f);
+  if (f == flag) return true;
+  unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      ll_load(p, data, &f);
+      if (f == flag) return true;
     }
     if (globaltimer_ns() - t0 > timeout_ns) return false;
   }

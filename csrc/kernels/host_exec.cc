@@ -17,6 +17,14 @@ namespace hostx {
 inline uint32_t ld_acquire_sys(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_ACQUIRE); }
 inline void st_release_sys(uint32_t* p, uint32_t v) { __atomic_store_n(p, v, __ATOMIC_RELEASE); }
 inline uint32_t ld_volatile(const uint32_t* p) { return __atomic_load_n(p, __ATOMIC_RELAXED); }
+inline void ll_store(void* p, uint32_t data, uint32_t flag) {
+  __atomic_store_n((uint64_t*)p, (uint64_t)data | ((uint64_t)flag << 32), __ATOMIC_RELEASE);
+}
+inline void ll_load(const void* p, uint32_t* data, uint32_t* flag) {
+  uint64_t v = __atomic_load_n((const uint64_t*)p, __ATOMIC_ACQUIRE);
+  *data = (uint32_t)v;
+  *flag = (uint32_t)(v >> 32);
+}
 inline void block_sync() {}
 inline int thread_index() { return 0; }
 inline void fence_system() { __atomic_thread_fence(__ATOMIC_SEQ_CST); }
@@ -36,6 +44,19 @@ inline bool wait_flag_ge(const uint32_t* flag, uint32_t want, unsigned long long
   double t0 = now_ms();
   for (unsigned spins = 0;; ++spins) {
     if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+    if ((spins & 63) == 63) {
+      if ((now_ms() - t0) * 1e6 > (double)timeout_ns) return false;
+      sched_yield();
+    }
+  }
+}
+
+inline bool ll_wait(const void* p, uint32_t flag, uint32_t* data, unsigned long long timeout_ns) {
+  uint32_t f;
+  double t0 = now_ms();
+  for (unsigned spins = 0;; ++spins) {
+    ll_load(p, data, &f);
+    if (f == flag) return true;
     if ((spins & 63) == 63) {
       if ((now_ms() - t0) * 1e6 > (double)timeout_ns) return false;
       sched_yield();

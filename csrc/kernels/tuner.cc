@@ -67,6 +67,11 @@ LaunchPlan plan_collective(const TunerInput& in) {
     static const long ag_nvls = env_long("AMEM_AG_NVLS", 0);
     if (ag_nvls || env_algo() == kAlgoNvls || in.forced_algo == kAlgoNvls) p.algo = kAlgoNvls;
   }
+  // Small all-to-all: flag-in-data packets, no barrier (AMEM_LL=0 turns it off).  The payload of one
+  // peer must fit half a flag-in-data slot.
+  static const long ll_on = env_long("AMEM_LL", 1);
+  const bool ll = in.kind == kCollAllToAll && n > 1 && ll_on && in.count * es <= ll_slot_bytes(in.p2p_slot_bytes) / 2;
+  if (ll) p.algo = kAlgoLL;
   // Grid: one block per 32 KiB of work up to the communicator's cap; latency-bound sizes use
   // few blocks because every block waits on its own set of peer flags.
   size_t per_block = 32 << 10;
@@ -81,7 +86,10 @@ LaunchPlan plan_collective(const TunerInput& in) {
     long want_b = (long)((bytes / (size_t)n + (64 << 10) - 1) / (64 << 10));
     blocks = std::max<long>(1, std::min<long>(want_b, win_blocks > 0 ? win_blocks : in.max_blocks));
   }
-  if (blocks_env > 0) blocks = std::min<long>(blocks_env, in.max_blocks);
+  // always the same number of blocks: the blocks' operation counts (the packets' flag) then move in
+  // lockstep, so a word's flag depends on the operation only, never on which block wrote it
+  if (ll) blocks = std::min<long>(4, in.max_blocks);
+  if (blocks_env > 0 && !ll) blocks = std::min<long>(blocks_env, in.max_blocks);
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   p.blocks = (int)blocks;
   // Chunk: messages that span several chunks overlap their NVLink and HBM phases (see

@@ -382,6 +382,10 @@ Status resume_scopes(Registry& reg, VmmBackend* be, std::vector<EngineScope>& sc
         a.state = kMemPreloading;
         reg.update(a);
         w.made.push_back(a);
+        if (a.clear_bytes) {  // queued on the side stream, finished before this rank votes in step 5
+          mine = be->memset_zero(a.va + a.clear_offset, a.clear_bytes, a.dev);
+          if (mine != kSuccess) break;
+        }
         bool restore = a.shadow && a.category == kStateful && a.tag != w.sc->opt.offload_free_tag;
         if (restore) {
           mine = be->copy_to_device_async(a.va, a.shadow, a.size, a.dev);

@@ -50,6 +50,9 @@ struct Allocation {
   uint32_t importers = 0;   // local records: bitmap of owner-comm ranks that mapped it
   uint64_t mc_handle = 0;   // multicast object this allocation is bound to (0 = none)
   size_t mc_offset = 0;
+  // [clear_offset, clear_offset + clear_bytes) must read zero whenever fresh physical memory is
+  // mapped here (protocol areas whose stale contents could be mistaken for signals)
+  size_t clear_offset = 0, clear_bytes = 0;
   void* shadow = nullptr;   // pinned host copy, allocated at first pause, kept afterwards
   int state = kMemInvalid;
 };
