@@ -55,6 +55,33 @@ def main():
         for _ in range(reps):
             gemm_bf16(a, b, out)
         torch.cuda.synchronize()
+    elif args.case == "grouped_gemm":
+        from asystem_amem_b200.ops import grouped_gemm_bf16, interleave_gate_up
+        El, d, ffn, rows = 8, 4096, 1536, 32768
+        counts = torch.tensor([5000, 3000, 4097, 4000, 1, 6670, 4000, 6000])
+        offs = torch.zeros(El + 1, dtype=torch.int32)
+        offs[1:] = counts.cumsum(0)
+        offs = offs.cuda()
+        x = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+        w13 = interleave_gate_up((torch.randn(El, 2 * ffn, d, device="cuda") * 0.02).to(torch.bfloat16), ffn)
+        act = torch.empty(rows, ffn, device="cuda", dtype=torch.bfloat16)
+        for _ in range(reps):
+            grouped_gemm_bf16(x, w13, offs, out=act, rows_hint=rows, swiglu=True)
+        torch.cuda.synchronize()
+    elif args.case == "window_allreduce":
+        world = 4
+        n = 32 << 20  # bf16 elements: 64 MiB per rank
+
+        def fn(rank, comm):
+            win = comm.window_alloc(n * 2)
+            x = win.tensor(torch.bfloat16, n)
+            x.normal_()
+            torch.cuda.synchronize()
+            for _ in range(reps):
+                comm.all_reduce(x, algo="window")
+            torch.cuda.synchronize()
+            win.free()
+        emulated(world, fn)
     elif args.case == "cublas":
         a = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
         b = (torch.randn(3584, 8192, device="cuda") * 0.02).to(torch.bfloat16)

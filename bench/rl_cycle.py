@@ -3,9 +3,9 @@
 
 One process per GPU holds TWO communicators over the same ranks: a training communicator
 (sharded data-parallel Llama-3-8B-architecture step, seq 4096, micro-batch 1 per GPU, fused
-gradient reduce-scatter + parameter all-gather) and an inference communicator (tensor-parallel
-forward of a 64 x 2048-token random-id batch with all-reduces after the attention and MLP row-
-parallel projections).  The cycle is
+gradient reduce-scatter + parameter all-gather) and an inference communicator (tensor-parallel,
+sequence-parallel forward of a 64 x 2048-token random-id batch on the fused kernels: every
+projection is one all-gather -> GEMM or one GEMM -> reduce-scatter launch).  The cycle is
 
     train step -> pause(train comm) -> TP inference batch -> pause(infer comm) -> resume(train comm)
     -> (next cycle) ... resume(infer comm) before its next use
@@ -14,7 +14,7 @@ and the script reports, as max over ranks, the switch latencies and the device m
 returns.  `--layers` shrinks the model for small boxes (default: the full 32 layers).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        --master-port 29550 bench/rl_cycle.py --cycles 3
+        --master-port 29550 bench/rl_cycle.py --cycles 10
 
 Reference parity: the use case the reference is built for (README.md:1-60, 'offload + reload <
 1 s per step'): two process groups share the GPUs and take turns.
@@ -33,6 +33,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from asystem_amem_b200 import Communicator  # noqa: E402
 from asystem_amem_b200.models import LlamaConfig, LlamaDecoder  # noqa: E402
 from asystem_amem_b200.models.llama import RMSNorm, apply_rope, rope_tables  # noqa: E402
+from asystem_amem_b200.ops import all_gather_gemm, gemm_reduce_scatter  # noqa: E402
 from asystem_amem_b200.parallel import FSDP, ShardedAdamW  # noqa: E402
 
 
@@ -53,35 +54,45 @@ class TPInferenceLlama:
         for _ in range(cfg.n_layers):
             self.layers.append(dict(
                 an=RMSNorm(cfg.dim, cfg.norm_eps).cuda().bfloat16(), mn=RMSNorm(cfg.dim, cfg.norm_eps).cuda().bfloat16(),
-                wq=w(self.h * self.hd, cfg.dim), wk=w(self.kv * self.hd, cfg.dim), wv=w(self.kv * self.hd, cfg.dim),
-                wo=w(cfg.dim, self.h * self.hd), w1=w(cfg.ffn_dim // n, cfg.dim), w3=w(cfg.ffn_dim // n, cfg.dim),
-                w2=w(cfg.dim, cfg.ffn_dim // n)))
+                wqkv=w((self.h + 2 * self.kv) * self.hd, cfg.dim), wo=w(cfg.dim, self.h * self.hd),
+                w13=w(2 * (cfg.ffn_dim // n), cfg.dim), w2=w(cfg.dim, cfg.ffn_dim // n)))
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, chunk: int = 8) -> torch.Tensor:
-        """ids [B, S]; sequences are processed `chunk` at a time to bound activation memory."""
-        cfg = self.cfg
+        """ids [B, S]; sequences are processed `chunk` at a time to bound activation memory.
+        Activations between the blocks are sharded by token rows (sequence parallel): every
+        projection into a block is ONE all-gather -> GEMM kernel, every projection out of it ONE
+        GEMM -> reduce-scatter kernel; no separate collective is launched."""
+        cfg, comm = self.cfg, self.comm
+        n, r = comm.nranks, comm.rank
         cos, sin = rope_tables(ids.shape[1], self.hd, cfg.rope_theta, ids.device)
         outs = []
         for b0 in range(0, ids.shape[0], chunk):
-            x = self.embed[ids[b0:b0 + chunk]]
-            B, S, _ = x.shape
+            sub = ids[b0:b0 + chunk]
+            B, S = sub.shape
+            T = B * S
+            assert T % n == 0
+            rows = T // n
+            x = self.embed[sub.reshape(-1)[r * rows:(r + 1) * rows]]           # my token rows [T / n, d]
             for L in self.layers:
                 hN = L["an"](x)
-                q = (hN @ L["wq"].t()).view(B, S, self.h, self.hd).transpose(1, 2)
-                k = (hN @ L["wk"].t()).view(B, S, self.kv, self.hd).transpose(1, 2)
-                v = (hN @ L["wv"].t()).view(B, S, self.kv, self.hd).transpose(1, 2)
+                qkv = all_gather_gemm(comm, hN.contiguous(), L["wqkv"])          # [T, (h + 2 kv) * hd] for my heads
+                q, k, v = qkv.split([self.h * self.hd, self.kv * self.hd, self.kv * self.hd], dim=1)
+                q = q.reshape(B, S, self.h, self.hd).transpose(1, 2)
+                k = k.reshape(B, S, self.kv, self.hd).transpose(1, 2)
+                v = v.reshape(B, S, self.kv, self.hd).transpose(1, 2)
                 q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
                 o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=self.kv != self.h)
-                part = (o.transpose(1, 2).reshape(B, S, -1) @ L["wo"].t()).contiguous()
-                self.comm.all_reduce(part)                       # row-parallel projection
-                x = x + part
+                x = x + gemm_reduce_scatter(comm, o.transpose(1, 2).reshape(T, -1).contiguous(), L["wo"])
                 hN = L["mn"](x)
-                part = ((F.silu(hN @ L["w1"].t()) * (hN @ L["w3"].t())) @ L["w2"].t()).contiguous()
-                self.comm.all_reduce(part)
-                x = x + part
-            outs.append(x[:, -1].float().mean())
-        return torch.stack(outs).mean()
+                h13 = all_gather_gemm(comm, hN.contiguous(), L["w13"])           # gate | up for my slice of the FFN
+                f = h13.shape[1] // 2
+                act = (F.silu(h13[:, :f].float()) * h13[:, f:].float()).to(torch.bfloat16)
+                x = x + gemm_reduce_scatter(comm, act, L["w2"])
+            outs.append(x.float().mean())
+        score = torch.stack(outs).mean().reshape(1)
+        comm.all_reduce(score)
+        return score[0] / n
 
 
 def main():
@@ -90,7 +101,7 @@ def main():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--infer-batch", type=int, default=64)
     ap.add_argument("--infer-seq", type=int, default=2048)
-    ap.add_argument("--cycles", type=int, default=3)
+    ap.add_argument("--cycles", type=int, default=10)
     ap.add_argument("--out", default="bench_results/rl_cycle.jsonl")
     args = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])

@@ -171,6 +171,39 @@ Status Comm::collective(int kind, const void* send, void* recv, size_t count, in
       ti.window_mc = nranks_ > 2 && ws->seg.mc_va && wr->seg.mc_va && (count * es) % 16 == 0 && so % 16 == 0 && ro % 16 == 0;
     }
   }
+  // Reduce-scatter FROM a window and all-gather INTO a window go through the window's multicast
+  // mapping (sum of fp32 / fp16 / bf16 without a cast for the former); three ranks or more.
+  if (nranks_ > 2 && !windows_.empty() && (algo == kAlgoAuto || algo == kAlgoWindow)) {
+    if (kind == kCollReduceScatter && dtype == out_dtype && (redop == kSum || redop == kAvg) && (dtype == kF32 || dtype == kBF16 || dtype == kF16)) {
+      Window* w = find_window(send, count * es * nranks_);
+      size_t so = w ? (uint64_t)send - w->base : 0;
+      if (w && w->seg.mc_va && (count * es) % 16 == 0 && so % 16 == 0 && ((uint64_t)recv & 15) == 0 && count * es >= (256u << 10)) {
+        a.algo = kAlgoWindow;
+        a.mc_send = (const char*)w->seg.mc_va + so;
+        LaunchPlan wp;
+        wp.algo = kAlgoWindow;
+        wp.threads = 512;
+        wp.chunk_elems = count;
+        wp.blocks = (int)std::max<size_t>(1, std::min<size_t>((size_t)max_blocks_, count * es / (64u << 10)));
+        return run(a, wp, stream);
+      }
+    }
+    if (kind == kCollAllGather) {
+      Window* w = find_window(recv, count * es * nranks_);
+      size_t ro = w ? (uint64_t)recv - w->base : 0;
+      if (w && w->seg.mc_va && (count * es) % 16 == 0 && ro % 16 == 0 && ((uint64_t)send & 15) == 0 && count * es >= (256u << 10)) {
+        // (in place works too: the multicast store also lands in this rank's own copy)
+        a.algo = kAlgoWindow;
+        a.mc_recv = (char*)w->seg.mc_va + ro;
+        LaunchPlan wp;
+        wp.algo = kAlgoWindow;
+        wp.threads = 512;
+        wp.chunk_elems = a.count;
+        wp.blocks = (int)std::max<size_t>(1, std::min<size_t>((size_t)max_blocks_, count * es / (64u << 10)));
+        return run(a, wp, stream);
+      }
+    }
+  }
   LaunchPlan plan = plan_collective(ti);
   if (plan.algo == kAlgoWindow) {
     size_t so = (uint64_t)send - ws->base, ro = (uint64_t)recv - wr->base;
@@ -230,7 +263,6 @@ Status Comm::group_simulate_end(float* est_us) {
 Status Comm::p2p(bool is_send, const void* src, void* dst, size_t bytes, int peer, cudaStream_t stream) {
   AMEM_TRY(check_usable(is_send ? "ncclSend" : "ncclRecv"));
   if (peer < 0 || peer >= nranks_) return fail(kInvalidArgument, "peer %d out of range", peer);
-  if (pending_.size() >= 2 * kMaxRanks) return fail(kInvalidUsage, "more than %d point-to-point operations in one group", 2 * kMaxRanks);
   CollArgs::P2P e;
   e.peer = peer;
   e.is_send = is_send ? 1 : 0;
@@ -272,18 +304,34 @@ Status Comm::flush_p2p(cudaStream_t stream) {
   // Zero-byte transfers carry no credit traffic on either side.
   net.erase(std::remove_if(net.begin(), net.end(), [](const CollArgs::P2P& e) { return e.bytes == 0; }), net.end());
   if (net.empty() && !emu_) return kSuccess;
-  CollArgs a;
-  fill_args(&a);
-  a.kind = kCollSendRecv;
-  a.dtype = a.out_dtype = kU8;
-  a.n_p2p = (int)net.size();
-  for (size_t i = 0; i < net.size(); ++i) a.p2p[i] = net[i];
-  LaunchPlan plan;
-  plan.algo = 0;
-  plan.blocks = 1;
-  plan.threads = 512;
-  plan.chunk_elems = 0;
-  return run(a, plan, stream);
+  // One launch carries at most one send and one receive per peer (their credit counters are per
+  // peer and direction).  A group with more runs in rounds: round k holds every peer's k-th send
+  // and k-th receive.  Operations between two ranks match in call order on both sides, so the
+  // k-th send to a peer meets that peer's k-th receive in ITS round k: every round is a complete
+  // matched set and no round waits for a later one.  Any number of operations per group.
+  std::vector<std::vector<CollArgs::P2P>> rounds;
+  std::vector<int> n_send(nranks_, 0), n_recv(nranks_, 0);
+  for (auto& e : net) {
+    int k = e.is_send ? n_send[e.peer]++ : n_recv[e.peer]++;
+    if ((int)rounds.size() <= k) rounds.resize(k + 1);
+    rounds[k].push_back(e);
+  }
+  if (rounds.empty()) rounds.resize(1);   // emulated ranks still meet when this rank has nothing to move
+  for (auto& ops_k : rounds) {
+    CollArgs a;
+    fill_args(&a);
+    a.kind = kCollSendRecv;
+    a.dtype = a.out_dtype = kU8;
+    a.n_p2p = (int)ops_k.size();
+    for (size_t i = 0; i < ops_k.size(); ++i) a.p2p[i] = ops_k[i];
+    LaunchPlan plan;
+    plan.algo = 0;
+    plan.blocks = 1;
+    plan.threads = 512;
+    plan.chunk_elems = 0;
+    AMEM_TRY(run(a, plan, stream));
+  }
+  return kSuccess;
 }
 
 Status Comm::split(int color, int key, const CommConfig& cfg, Comm** out) {

@@ -261,6 +261,70 @@ __device__ __forceinline__ void body_allreduce_window_nvls(const CollArgs& a, Pr
   block_barrier(p);
 }
 
+// Reduce-scatter whose INPUT lies in a registered window with a multicast mapping: rank r asks the
+// switch for the sum of everybody's slice r and stores it (scaled if asked) into its own output.
+// Nothing is staged and nothing is pushed: each rank receives one slice instead of n - 1.
+template <typename T>
+__device__ __forceinline__ void body_reducescatter_window_nvls(const CollArgs& a, Proto& p) {
+  const int r = a.rank;
+  const size_t es = sizeof(T);
+  const size_t R = a.count;   // elements each rank receives
+  size_t lo, hi;
+  block_range(R * es, p.block, p.nblocks, &lo, &hi);
+  block_barrier(p);           // every rank's input is complete
+  const size_t nvec = (hi - lo) / 16;
+  const char* src = a.mc_send + (size_t)r * R * es + lo;
+  char* dst = (char*)a.recv + lo;
+  const size_t nt = blockDim.x;
+  size_t i = threadIdx.x;
+  constexpr int U = 8;
+  for (; i + (U - 1) * nt < nvec; i += U * nt) {
+    uint4 v[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) v[j] = Multimem<T>::ld_reduce(src + (i + j * nt) * 16);
+    if (a.has_scale) {
+#pragma unroll
+      for (int j = 0; j < U; ++j) v[j] = Multimem<T>::scale(v[j], a.scale);
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) *(uint4*)(dst + (i + j * nt) * 16) = v[j];
+  }
+  for (; i < nvec; i += nt) {
+    uint4 v = Multimem<T>::ld_reduce(src + i * 16);
+    if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
+    *(uint4*)(dst + i * 16) = v;
+  }
+  block_barrier(p);           // nobody overwrites its input while a peer's reduction still reads it
+}
+
+// All-gather whose OUTPUT lies in a registered window with a multicast mapping: ONE store per 16
+// bytes, replicated by the switch into every rank's output, instead of one store per peer.
+__device__ __forceinline__ void body_allgather_window_nvls(const CollArgs& a, Proto& p) {
+  const int r = a.rank;
+  const size_t B = a.count;   // bytes contributed by each rank (the copy collectives run on bytes)
+  size_t lo, hi;
+  block_range(B, p.block, p.nblocks, &lo, &hi);
+  block_barrier(p);           // every rank is done with the previous contents of its output
+  copy_span_mc(a.mc_recv + (size_t)r * B + lo, (const char*)a.send + lo, hi - lo, full_lane());
+  block_barrier(p);           // everybody's piece has landed everywhere
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) nvls_window_reducescatter_kernel(const __grid_constant__ CollArgs a) {
+  __shared__ int s_abort;
+  Proto p;
+  proto_begin(p, a, blockIdx.x, gridDim.x, &s_abort);
+  body_reducescatter_window_nvls<T>(a, p);
+  proto_end(p);
+}
+__global__ void __launch_bounds__(512) nvls_window_allgather_kernel(const __grid_constant__ CollArgs a) {
+  __shared__ int s_abort;
+  Proto p;
+  proto_begin(p, a, blockIdx.x, gridDim.x, &s_abort);
+  body_allgather_window_nvls(a, p);
+  proto_end(p);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) nvls_window_allreduce_kernel(const __grid_constant__ CollArgs a) {
   __shared__ int s_abort;
@@ -354,6 +418,16 @@ Status launch_collective(const CollArgs& a, const LaunchPlan& plan, cudaStream_t
     else if (a.dtype == kBF16) dev::nvls_window_allreduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a);
     else dev::nvls_window_allreduce_kernel<__half><<<grid, block, 0, stream>>>(a);
     return check_launch("window allreduce (nvls)");
+  }
+  if (a.kind == kCollReduceScatter && a.algo == kAlgoWindow && a.nranks > 1 && a.mc_send) {
+    if (a.dtype == kF32) dev::nvls_window_reducescatter_kernel<float><<<grid, block, 0, stream>>>(a);
+    else if (a.dtype == kBF16) dev::nvls_window_reducescatter_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a);
+    else dev::nvls_window_reducescatter_kernel<__half><<<grid, block, 0, stream>>>(a);
+    return check_launch("window reduce-scatter (nvls)");
+  }
+  if (a.kind == kCollAllGather && a.algo == kAlgoWindow && a.nranks > 1 && a.mc_recv) {
+    dev::nvls_window_allgather_kernel<<<grid, block, 0, stream>>>(a);
+    return check_launch("window all-gather (nvls)");
   }
   bool reducing = a.kind == kCollAllReduce || a.kind == kCollReduceScatter || a.kind == kCollReduce;
   if (reducing) {

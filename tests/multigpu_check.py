@@ -155,6 +155,30 @@ def main():
         report(f"window allreduce {str(dtype)[6:]} n={n} + pause x3", ok and freed_w >= n * es, freed_mib=freed_w >> 20)
         win.free()
 
+    # ---- reduce-scatter out of a window / all-gather into a window (multicast forms: three ranks or more)
+    n_w = 1 << 20                                              # elements per rank
+    win_s = comm.window_alloc(n_w * world * 4)
+    win_r = comm.window_alloc(n_w * world * 4)
+    src = win_s.tensor(torch.float32, n_w * world)
+    g = torch.Generator().manual_seed(900 + rank)
+    mine = torch.randn(n_w * world, generator=g)
+    src.copy_(mine.cuda())
+    torch.cuda.synchronize()
+    dist.barrier()
+    out_rs = torch.empty(n_w, device="cuda")
+    comm.reduce_scatter(src, out_rs)
+    torch.cuda.synchronize()
+    exp = sum(t[rank * n_w:(rank + 1) * n_w] for t in gather_cpu(mine))
+    report("reducescatter from a window", torch.allclose(out_rs.cpu(), exp, rtol=1e-5, atol=1e-4))
+    dst = win_r.tensor(torch.float32, n_w * world)
+    piece = (torch.arange(n_w, dtype=torch.float32) + 1000.0 * rank).cuda()
+    comm.all_gather(piece, dst)
+    torch.cuda.synchronize()
+    report("allgather into a window", torch.equal(dst.cpu(), torch.cat(gather_cpu(piece.cpu()))))
+    dist.barrier()
+    win_r.free()
+    win_s.free()
+
     # ---- fused tensor-parallel GEMMs
     from asystem_amem_b200.ops import MoeDispatcher, all_gather_gemm, gemm_reduce_scatter
     m_local, N, K = 512, 1024, 2048

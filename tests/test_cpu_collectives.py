@@ -94,6 +94,34 @@ def test_sendrecv_ring():
     assert all(run_ranks(_sendrecv_ring, 3))
 
 
+def _big_group(rank, world, uid):
+    """More point-to-point operations in one group than one launch carries (a pipeline stage that
+    also does an all-to-all-v): several messages per peer and direction, 24 operations in all."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator, group_end, group_start
+    comm = Communicator(world, rank, uid)
+    per_peer = 4
+    sends, recvs = {}, {}
+    group_start()
+    for q in range(world):
+        if q == rank:
+            continue
+        for j in range(per_peer):
+            n = 100 + 5000 * j
+            sends[(q, j)] = np.full(n, 1000 * rank + 10 * q + j, dtype=np.float32)
+            recvs[(q, j)] = np.zeros(n, dtype=np.float32)
+            comm.send(sends[(q, j)], q)
+            comm.recv(recvs[(q, j)], q)
+    group_end()
+    ok = all(bool(np.all(buf == 1000 * q + 10 * rank + j)) for (q, j), buf in recvs.items())
+    comm.destroy()
+    return ok and len(recvs) == per_peer * (world - 1)
+
+
+def test_group_with_more_operations_than_one_launch_carries():
+    assert all(run_ranks(_big_group, 4))
+
+
 def _multi_chunk(rank, world, uid):
     """Messages several times larger than a staging slot: the chunked credit protocol."""
     import numpy as np
