@@ -189,14 +189,12 @@ Status Comm::sym_alloc(size_t size, int category, int tag, Segment* out) {
       close(pfd);
       AMEM_TRY(st);
       st = be_->map(s.va[r], s.size, ph, dev_);
-      if (st != kSuccess) {
-        be_->release(ph);
-        return st;
-      }
+      be_->release(ph);   // the mapping keeps the peer's memory alive; one driver call less on every pause
+      if (st != kSuccess) return st;
       Allocation imp;
       imp.va = s.va[r];
       imp.size = s.size;
-      imp.handle = ph;
+      imp.handle = 0;
       imp.dev = dev_;
       imp.type = kPeerPosix;
       imp.category = category;
@@ -273,7 +271,7 @@ Status Comm::sym_free(Segment* seg) {
     if (a.state != kMemHole) {
       if (a.mc_handle && r == rank_) be_->mc_unbind(a.mc_handle, dev_, a.mc_offset, a.size);
       be_->unmap(a.va, a.size);
-      be_->release(a.handle);
+      if (a.handle) be_->release(a.handle);
     }
     if (a.shadow) be_->host_free(a.shadow, a.size);
     reg.remove(a.va);
@@ -430,14 +428,12 @@ Status Comm::window_register(void* buff, size_t size, Window** out) {
       close(pfd);
       AMEM_TRY(st);
       st = be_->map(s.va[r], s.size, ph, dev_);
-      if (st != kSuccess) {
-        be_->release(ph);
-        return st;
-      }
+      be_->release(ph);   // the mapping keeps the peer's memory alive
+      if (st != kSuccess) return st;
       Allocation imp;
       imp.va = s.va[r];
       imp.size = s.size;
-      imp.handle = ph;
+      imp.handle = 0;
       imp.dev = dev_;
       imp.type = kPeerSymm;
       imp.category = kStateful;
@@ -471,7 +467,7 @@ Status Comm::drop_window(Window* w, bool collective) {
     if (!reg.find(s.va[r], &a)) continue;
     if (a.state != kMemHole) {
       be_->unmap(a.va, a.size);
-      be_->release(a.handle);
+      if (a.handle) be_->release(a.handle);
     }
     reg.remove(a.va);
   }

@@ -67,9 +67,10 @@ LaunchPlan plan_collective(const TunerInput& in) {
     static const long ag_nvls = env_long("AMEM_AG_NVLS", 0);
     if (ag_nvls || env_algo() == kAlgoNvls || in.forced_algo == kAlgoNvls) p.algo = kAlgoNvls;
   }
-  // Small all-to-all: flag-in-data packets, no barrier (AMEM_LL=0 turns it off).  The payload of one
-  // peer must fit half a flag-in-data slot.
-  static const long ll_on = env_long("AMEM_LL", 1);
+  // Small all-to-all as flag-in-data packets, no barrier: opt-in with AMEM_LL=1.  Measured on 8 GPUs it
+  // lost to the barrier form at every size (2 KiB: 38 vs 27 us; 512 KiB: 72 vs 36 us): 8-byte packets
+  // polled word by word cost more than one barrier saves.  The payload of one peer must fit half a slot.
+  static const long ll_on = env_long("AMEM_LL", 0);
   const bool ll = in.kind == kCollAllToAll && n > 1 && ll_on && in.count * es <= ll_slot_bytes(in.p2p_slot_bytes) / 2;
   if (ll) p.algo = kAlgoLL;
   // Grid: one block per 32 KiB of work up to the communicator's cap; latency-bound sizes use

@@ -87,6 +87,13 @@ struct Work {
   PauseResumeStats* stats() { return sc->stats; }
 };
 
+// Ring distance from this rank to the rank that owns an imported record (1 = right-hand neighbour).
+int peer_distance(const Work& w, const Allocation& a) {
+  if (!w.sc->px || a.exporter_rank < 0) return 0;
+  const int n = w.sc->px->nranks();
+  return (a.exporter_rank - w.sc->px->rank() + n) % n;
+}
+
 void add_slot(Phase& p, std::vector<Work>& ws, double PauseResumeStats::*field) {
   for (auto& w : ws)
     if (w.sc->stats) p.slots.push_back(&(w.sc->stats->*field));
@@ -107,7 +114,7 @@ void rollback(Registry& reg, VmmBackend* be, Work& w) {
   for (size_t i : w.mapped) {
     Allocation& a = w.recs[i];
     be->unmap(a.va, a.size);
-    be->release(a.handle);
+    if (a.handle) be->release(a.handle);
     a.handle = 0;
     a.state = kMemHole;
     reg.update(a);
@@ -228,11 +235,14 @@ Status pause_scopes(Registry& reg, VmmBackend* be, std::vector<EngineScope>& sco
     for (auto& w : ws)
       for (auto& a : w.recs)
         if (!is_local(a) && a.state == kMemAlloc && a.category != kResident) jobs.push_back({&w, &a, kSuccess, ""});
+    // every rank starts with a different peer (its right-hand neighbour), so that at any moment
+    // the ranks' driver calls concern different GPUs' memory instead of all queueing on one
+    std::stable_sort(jobs.begin(), jobs.end(), [](const Job& x, const Job& y) { return peer_distance(*x.w, *x.a) < peer_distance(*y.w, *y.a); });
     parallel_each(jobs.size(), [&](size_t i, bool helper) {
       Job& j = jobs[i];
       Status s = helper ? be->thread_init(j.a->dev) : kSuccess;
       if (s == kSuccess) s = be->unmap(j.a->va, j.a->size);
-      if (s == kSuccess) s = be->release(j.a->handle);
+      if (s == kSuccess && j.a->handle) s = be->release(j.a->handle);   // (imports normally gave their handle back right after mapping)
       j.st = s;
       if (s != kSuccess) j.err = last_error_slot();
     });
@@ -476,7 +486,11 @@ Status resume_scopes(Registry& reg, VmmBackend* be, std::vector<EngineScope>& sc
         if (s == kSuccess) jobs.push_back({&w, i, fd, kSuccess, "", 0, false});
       }
     }
-    // ... then every peer's memory goes back where it used to be, side by side
+    // ... then every peer's memory goes back where it used to be; every rank starts with a
+    // different peer (see pause)
+    std::stable_sort(jobs.begin(), jobs.end(), [](const Job& x, const Job& y) {
+      return peer_distance(*x.w, x.w->recs[x.idx]) < peer_distance(*y.w, y.w->recs[y.idx]);
+    });
     parallel_each(jobs.size(), [&](size_t k, bool helper) {
       Job& j = jobs[k];
       Allocation& a = j.w->recs[j.idx];
@@ -486,11 +500,10 @@ Status resume_scopes(Registry& reg, VmmBackend* be, std::vector<EngineScope>& sc
         if (s == kSuccess) s = be->import_fd(j.fd, a.size, &j.handle);
         if (s == kSuccess) {
           s = be->map_deferred(a.va, a.size, j.handle, a.dev, &j.needs_access);
-          if (s != kSuccess) {
-            std::string keep = last_error_slot();
-            be->release(j.handle);
-            last_error_slot() = keep;
-          }
+          std::string keep = last_error_slot();
+          be->release(j.handle);   // mapped or not, the handle is not needed again: the mapping holds the memory
+          j.handle = 0;
+          last_error_slot() = keep;
         }
         j.st = s;
         if (s != kSuccess) j.err = last_error_slot();

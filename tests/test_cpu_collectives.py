@@ -73,6 +73,31 @@ def test_collectives_match_numpy(world):
         assert not bad, f"rank {r}: mismatch in {bad}"
 
 
+def _flag_in_data_alltoall(rank, world, uid):
+    """The opt-in small-message all-to-all (8-byte packets that carry their own flag): odd byte
+    counts, repeated operations (slots alternate and are reused after the receiver's ack), a
+    pause in between (fresh staging memory must not look like packets)."""
+    import numpy as np
+    from asystem_amem_b200 import Communicator
+    comm = Communicator(world, rank, uid)
+    ok = True
+    for it, n in enumerate([1, 3, 7, 250, 1001, 250, 1, 1777, 64, 5]):
+        send = np.concatenate([np.full(n, 16 * rank + q + it, dtype=np.uint8) for q in range(world)])
+        recv = np.zeros_like(send)
+        comm.all_to_all(send, recv)
+        exp = np.concatenate([np.full(n, 16 * q + rank + it, dtype=np.uint8) for q in range(world)])
+        ok = ok and bool(np.array_equal(recv, exp))
+        if it == 4:
+            comm.pause()
+            comm.resume()
+    comm.destroy()
+    return ok
+
+
+def test_flag_in_data_alltoall():
+    assert all(run_ranks(_flag_in_data_alltoall, 4, env={"AMEM_LL": "1"}))
+
+
 def _sendrecv_ring(rank, world, uid):
     import numpy as np
     from asystem_amem_b200 import Communicator, group_end, group_start
