@@ -126,6 +126,33 @@ def main():
     res["dispatch_frac_of_770"] = res["dispatch_link_gbs"] / 770.0
     res["combine_frac_of_770"] = res["combine_link_gbs"] / 770.0
 
+    # the whole layer without gradients: routing, dispatch, two grouped tcgen05 GEMMs over all local
+    # experts (group boundaries stay on the device), combine; against the same layer with the experts
+    # as a per-expert loop of cuBLAS calls that reads the boundaries on the host
+    import torch.nn.functional as F
+    import time
+
+    def layer_fused():
+        with torch.no_grad():
+            layer(x)
+
+    def layer_loop():
+        with torch.no_grad():
+            lg = (x @ layer.router.t()).float()
+            tp_ = lg.topk(K, dim=1)
+            li, lw = tp_.indices.to(torch.int32), torch.softmax(tp_.values, dim=1)
+            r_ = disp.dispatch(x, li)
+            offs = r_.expert_offsets.tolist()
+            for el in range(layer.El):
+                lo, hi = offs[el], offs[el + 1]
+                if hi > lo:
+                    h = r_.recv_x[lo:hi] @ layer.w13[el].t()
+                    a_ = (F.silu(h[:, : args.ffn].float()) * h[:, args.ffn:].float()).to(torch.bfloat16)
+                    disp.y[lo:hi] = a_ @ layer.w2[el].t()
+            disp.combine(li, lw, r_.send_pos)
+
+    res["layer_forward_fused_ms"] = timed(layer_fused, iters=5)
+    res["layer_forward_expert_loop_ms"] = timed(layer_loop, iters=5)
     # all communicators paused and resumed together
     with torch.no_grad():
         first = layer(x).clone()
@@ -133,10 +160,15 @@ def main():
     dist.barrier(group=gloo)
     used0 = torch.cuda.mem_get_info()[0]
     same, drift, freed = True, 0, 0
+    cycle_ms = []
     for c in range(args.cycles):
+        t0 = time.perf_counter()
         pause_all()
+        t1 = time.perf_counter()
         freed = torch.cuda.mem_get_info()[0] - used0
+        t2 = time.perf_counter()
         resume_all()
+        cycle_ms.append((t1 - t0 + time.perf_counter() - t2) * 1e3)
         if c % 10 == 9 or c == args.cycles - 1:
             with torch.no_grad():
                 out = layer(x)
@@ -145,6 +177,9 @@ def main():
         drift = max(drift, abs(torch.cuda.mem_get_info()[0] - used0))
     flag = torch.tensor([1 if same else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=gloo)
+    cyc = torch.tensor(cycle_ms, dtype=torch.float64)
+    dist.all_reduce(cyc, op=dist.ReduceOp.MAX, group=gloo)
+    res["pause_resume_all_comms_median_ms"] = float(cyc.median())    # world + TP + EP communicators in ONE engine pass
     res["cycles"] = args.cycles
     res["bitwise_equal_after_cycles"] = bool(flag.item())
     res["gib_freed_per_gpu_on_pause"] = freed / 2**30
