@@ -56,7 +56,7 @@ def max_over_ranks(value: float, group=None) -> float:
 
 
 def load_measured_peaks(root: str | None = None) -> dict:
-    """Measured copy bandwidth / cuBLAS throughput of this pool's B200s, or the documented
+    """Measured copy bandwidth / cuBLAS throughput of the B200s at hand (MEASURED_PEAKS.json), or the documented
     fallback (6.65 TB/s, 1.59 PFLOP/s) when the file is absent."""
     root = root or os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     p = os.path.join(root, "MEASURED_PEAKS.json")

@@ -154,3 +154,31 @@ def test_grouped_gemm_swiglu_epilogue(counts, ffn, K):
             err = (out[lo:lo + c].float() - ref).abs().max().item()
             assert err <= 2e-2 * ref.abs().max().item() + 1e-2, (e, err)
         lo += c
+
+
+def test_grouped_linear_gradients():
+    """GroupedLinear (forward and input gradient on the grouped kernel, weight gradient per group)
+    against autograd on a per-group loop in fp32."""
+    from asystem_amem_b200.models.moe_layer import GroupedLinear
+    counts, N, K = [130, 0, 77, 300], 192, 256
+    groups, total = len(counts), sum(counts)
+    rows = _rand((total, K), 11).cuda().requires_grad_(True)
+    w = _rand((groups, N, K), 12, 0.05).cuda().requires_grad_(True)
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32).cuda()
+    gout = _rand((total, N), 13).cuda()
+    out = GroupedLinear.apply(rows, w, offs)
+    out.backward(gout)
+    torch.cuda.synchronize()
+    r32 = rows.detach().float().requires_grad_(True)
+    w32 = w.detach().float().requires_grad_(True)
+    lo = 0
+    pieces = []
+    for e, c in enumerate(counts):
+        pieces.append(r32[lo:lo + c] @ w32[e].t())
+        lo += c
+    ref = torch.cat(pieces)
+    ref.backward(gout.float())
+    scale = lambda t: 2e-2 * t.abs().max().item() + 2e-2  # noqa: E731
+    assert (out.float() - ref).abs().max().item() <= scale(ref)
+    assert (rows.grad.float() - r32.grad).abs().max().item() <= scale(r32.grad)
+    assert (w.grad.float() - w32.grad).abs().max().item() <= scale(w32.grad)

@@ -121,3 +121,41 @@ def test_process_wide_pause_with_emulated_ranks():
     assert all(r[0] for r in res)
     stage_total = res[0][1]
     assert stage_total is not None and stage_total > (world * 200 << 20)
+
+
+def test_work_memory_of_the_fused_kernels_is_tracked_and_returned():
+    """The split-K workspace of the plain GEMM and the MoE work area are tracked allocations:
+    ncclMemStats accounts for them, ncclPause(NULL) returns them, and the kernels work again after
+    ncclResume (the GEMM also runs while paused, without its workspace)."""
+    from asystem_amem_b200 import Communicator, get_unique_id, mem_stats, pause_all, resume_all
+    from asystem_amem_b200.ops import MoeDispatcher, gemm_bf16
+    torch.cuda.set_device(0)
+    comm = Communicator(1, 0, get_unique_id())
+    a = torch.randn(1000, 4096, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(264, 4096, device="cuda") * 0.05).to(torch.bfloat16)
+    before = mem_stats()
+    ref = gemm_bf16(a, b)                                   # a shape whose last wave is split along K
+    disp = MoeDispatcher(comm, 8, 64, 256)
+    idx = torch.randint(0, 8, (64, 2), device="cuda", dtype=torch.int32)
+    x = torch.randn(64, 64, device="cuda").to(torch.bfloat16)
+    res = disp.dispatch(x, idx)
+    torch.cuda.synchronize()
+    first_pos = res.send_pos.clone()
+    mid = mem_stats()
+    grown = (mid["stateful_bytes"] + mid["scratch_bytes"]) - (before["stateful_bytes"] + before["scratch_bytes"])
+    assert grown >= (20 << 20), (before, mid)               # workspace (about 28 MB) + counters + MoE buffers
+    f0 = torch.cuda.mem_get_info()[0]
+    pause_all()
+    freed = torch.cuda.mem_get_info()[0] - f0
+    assert freed >= comm.info()["stage_bytes"] + grown - (4 << 20), (freed, grown)
+    while_paused = gemm_bf16(a, b)                          # no workspace now: same product, unsplit
+    torch.cuda.synchronize()
+    resume_all()
+    again = gemm_bf16(a, b)
+    res2 = disp.dispatch(x, idx)
+    torch.cuda.synchronize()
+    full = a.float() @ b.float().t()
+    tol = 2e-2 * full.abs().max().item() + 1e-2
+    assert (while_paused.float() - full).abs().max().item() <= tol
+    assert torch.equal(again, ref) and torch.equal(res2.send_pos, first_pos)
+    comm.destroy()
