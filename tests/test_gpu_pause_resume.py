@@ -133,7 +133,6 @@ def test_work_memory_of_the_fused_kernels_is_tracked_and_returned():
     comm = Communicator(1, 0, get_unique_id())
     a = torch.randn(1000, 4096, device="cuda").to(torch.bfloat16)
     b = (torch.randn(264, 4096, device="cuda") * 0.05).to(torch.bfloat16)
-    before = mem_stats()
     ref = gemm_bf16(a, b)                                   # a shape whose last wave is split along K
     disp = MoeDispatcher(comm, 8, 64, 256)
     idx = torch.randint(0, 8, (64, 2), device="cuda", dtype=torch.int32)
@@ -142,12 +141,13 @@ def test_work_memory_of_the_fused_kernels_is_tracked_and_returned():
     torch.cuda.synchronize()
     first_pos = res.send_pos.clone()
     mid = mem_stats()
-    grown = (mid["stateful_bytes"] + mid["scratch_bytes"]) - (before["stateful_bytes"] + before["scratch_bytes"])
-    assert grown >= (20 << 20), (before, mid)               # workspace (about 28 MB) + counters + MoE buffers
+    # everything mapped now: staging + control, the split-K workspace (about 28 MB; an earlier test of
+    # this process may have made it already) + its counters, the MoE buffers and work area
+    assert mid["live_bytes"] >= comm.info()["stage_bytes"] + (24 << 20), mid
     f0 = torch.cuda.mem_get_info()[0]
     pause_all()
     freed = torch.cuda.mem_get_info()[0] - f0
-    assert freed >= comm.info()["stage_bytes"] + grown - (4 << 20), (freed, grown)
+    assert freed >= mid["live_bytes"] - (8 << 20), (freed, mid)    # all but the small resident blocks came back
     while_paused = gemm_bf16(a, b)                          # no workspace now: same product, unsplit
     torch.cuda.synchronize()
     resume_all()
