@@ -514,6 +514,11 @@ AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_
   if (thread_index() == 0) p.me->cseq[p.block] = base + nch;
 }
 
+// Broadcast.  The root's data goes into every rank's staging — through the multicast mapping when
+// there is one (ONE multimem.st per 16 bytes, replicated by the switch: the root's link carries the
+// message once, not n - 1 times), by one store per peer otherwise — and every other rank drains its
+// staging into its buffer.  Chunks run on the same credits as all-gather: the root's next chunk is
+// on the wire while the previous one is drained.
 template <typename TI, typename TO, int OP>
 AMEM_FN void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
@@ -526,22 +531,35 @@ AMEM_FN void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
   if (cb == 0) cb = 256;
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
-  uint32_t c = 0;
-  for (size_t off = 0; off < B; off += cb, ++c) {
-    size_t len = B - off < cb ? B - off : cb;
-    size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
-    size_t lo, hi;
-    block_range(len, p.block, p.nblocks, &lo, &hi);
-    if (r == a.root) {
-      for (int k = 1; k < n; ++k) {
-        int q = peer_at(r, n, k, p.block);
-        copy_span(a.stage[q] + qoff + lo, send + off + lo, hi - lo, full_lane());
+  const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
+  run_chunks(a, p, nch, 8,
+    [&](uint32_t t, Lane ln) {
+      if (r != a.root) return;
+      size_t off = (size_t)t * cb;
+      size_t len = B - off < cb ? B - off : cb;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
+      size_t lo, hi;
+      block_range(len, p.block, p.nblocks, &lo, &hi);
+      char* mc = (n > 2 && a.mc_stage) ? a.mc_stage + qoff + lo : nullptr;
+      if (mc_copy_ok(mc, send + off + lo, hi - lo)) {
+        copy_span_mc(mc, send + off + lo, hi - lo, ln);
+      } else {
+        for (int k = 1; k < n; ++k) {
+          int q = peer_at(r, n, k, p.block);
+          copy_span(a.stage[q] + qoff + lo, send + off + lo, hi - lo, ln);
+        }
       }
-      if (send != recv) copy_span(recv + off + lo, send + off + lo, hi - lo, full_lane());
-    }
-    block_barrier(p);
-    if (r != a.root) copy_span(recv + off + lo, a.stage[r] + qoff + lo, hi - lo, full_lane());
-  }
+      if (send != recv) copy_span(recv + off + lo, send + off + lo, hi - lo, ln);
+    },
+    [&](uint32_t t, Lane ln) {
+      if (r == a.root) return;
+      size_t off = (size_t)t * cb;
+      size_t len = B - off < cb ? B - off : cb;
+      size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
+      size_t lo, hi;
+      block_range(len, p.block, p.nblocks, &lo, &hi);
+      copy_span(recv + off + lo, a.stage[r] + qoff + lo, hi - lo, ln);
+    });
 }
 
 template <typename TI, typename TO, int OP>

@@ -309,6 +309,59 @@ __device__ __forceinline__ void body_allgather_window_nvls(const CollArgs& a, Pr
   block_barrier(p);           // everybody's piece has landed everywhere
 }
 
+// Reduce to a root through the switch: every rank copies its chunk into its own staging (a local
+// HBM copy, nothing crosses NVLink yet), the root then asks the switch for the sum of everybody's
+// copy (multimem.ld_reduce) and stores it into its output.  The root's link carries the message
+// once, not n - 1 times as when every rank pushes its contribution to the root.
+template <typename T>
+__device__ __forceinline__ void body_reduce_nvls(const CollArgs& a, Proto& p, size_t chunk_elems) {
+  const int r = a.rank;
+  const size_t es = sizeof(T), vi = 16 / es;
+  const size_t N = a.count;
+  const size_t H = 2 * quarter_bytes(a.stage_bytes, a.p2p_slot_bytes);
+  const size_t hoff = half_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq);
+  size_t ce = chunk_elems;
+  if (ce * es > H) ce = H / es;
+  ce = ce / vi * vi;
+  if (ce == 0) ce = vi;
+  const char* send = (const char*)a.send;
+  char* recv = (char*)a.recv;
+  for (size_t off = 0; off < N; off += ce) {
+    const size_t len = N - off < ce ? N - off : ce;
+    size_t lo, hi;
+    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    copy_span(a.stage[r] + hoff + lo, send + off * es + lo, hi - lo, full_lane());
+    block_barrier(p);   // everybody's chunk is staged
+    if (r == a.root) {
+      // whole vectors: the staging tail beyond the chunk holds stale but mapped bytes
+      const size_t nvec = (hi - lo + 15) / 16, nt = blockDim.x;
+      const char* src = a.mc_stage + hoff + lo;
+      char* dst = recv + off * es + lo;
+      const bool dst_vec = (((uintptr_t)dst) & 15) == 0;
+      for (size_t i = threadIdx.x; i < nvec; i += nt) {
+        uint4 v = Multimem<T>::ld_reduce(src + i * 16);
+        if (a.has_scale) v = Multimem<T>::scale(v, a.scale);
+        const size_t left = (hi - lo) - i * 16;
+        if (dst_vec && left >= 16) {
+          *(uint4*)(dst + i * 16) = v;
+        } else {
+          const char* vb = (const char*)&v;
+          for (size_t b = 0; b < 16 && b < left; ++b) dst[i * 16 + b] = vb[b];
+        }
+      }
+    }
+    block_barrier(p);   // the root has read the chunk: staging may be overwritten
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(512) nvls_reduce_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {
+  __shared__ int s_abort;
+  Proto p;
+  proto_begin(p, a, blockIdx.x, gridDim.x, &s_abort);
+  body_reduce_nvls<T>(a, p, chunk_elems);
+  proto_end(p);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) nvls_window_reducescatter_kernel(const __grid_constant__ CollArgs a) {
   __shared__ int s_abort;
@@ -418,6 +471,12 @@ Status launch_collective(const CollArgs& a, const LaunchPlan& plan, cudaStream_t
     else if (a.dtype == kBF16) dev::nvls_window_allreduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a);
     else dev::nvls_window_allreduce_kernel<__half><<<grid, block, 0, stream>>>(a);
     return check_launch("window allreduce (nvls)");
+  }
+  if (a.kind == kCollReduce && a.algo == kAlgoNvls && a.nranks > 2 && a.mc_stage) {
+    if (a.dtype == kF32) dev::nvls_reduce_kernel<float><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+    else if (a.dtype == kBF16) dev::nvls_reduce_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+    else dev::nvls_reduce_kernel<__half><<<grid, block, 0, stream>>>(a, plan.chunk_elems);
+    return check_launch("reduce (nvls)");
   }
   if (a.kind == kCollReduceScatter && a.algo == kAlgoWindow && a.nranks > 1 && a.mc_send) {
     if (a.dtype == kF32) dev::nvls_window_reducescatter_kernel<float><<<grid, block, 0, stream>>>(a);

@@ -73,6 +73,11 @@ LaunchPlan plan_collective(const TunerInput& in) {
   static const long ll_on = env_long("AMEM_LL", 0);
   const bool ll = in.kind == kCollAllToAll && n > 1 && ll_on && in.count * es <= ll_slot_bytes(in.p2p_slot_bytes) / 2;
   if (ll) p.algo = kAlgoLL;
+  // Reduce to a root: from 1 MiB up, through the switch (the root pulls one reduced stream) instead of
+  // n - 1 pushes into the root.  Sum of fp32 / fp16 / bf16, three ranks or more, 16-byte aligned counts.
+  if (in.kind == kCollReduce && in.nvls && n > 2 && (in.redop == kSum || in.redop == kAvg) &&
+      (in.dtype == kF32 || in.dtype == kBF16 || in.dtype == kF16) && in.count * es >= (1u << 20) && env_algo() != kAlgoTwoShot)
+    p.algo = kAlgoNvls;
   // Grid: one block per 32 KiB of work up to the communicator's cap; latency-bound sizes use
   // few blocks because every block waits on its own set of peer flags.
   size_t per_block = 32 << 10;
@@ -131,8 +136,8 @@ LaunchPlan plan_collective(const TunerInput& in) {
       }
       else p.chunk_elems = pick(in.count * es, 64u << 20, 32u << 20, (slot_bytes_of(H / 2, n)) * (size_t)n) / es;
       break;
-    case kCollBroadcast: p.chunk_elems = Q / es; break;
-    case kCollReduce: p.chunk_elems = slot / es; break;
+    case kCollBroadcast: p.chunk_elems = pick(in.count * es, 16u << 20, 8u << 20, Q) / es; break;  // one chunk up to 16 MiB, then about eight
+    case kCollReduce: p.chunk_elems = (p.algo == kAlgoNvls ? H : slot) / es; break;
     default: p.chunk_elems = pick(in.count * es, 64u << 20, 32u << 20, slot) / es; break;  // per-rank bytes
   }
   if (p.chunk_elems == 0) p.chunk_elems = 1;
