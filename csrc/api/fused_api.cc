@@ -281,7 +281,6 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
   int n = c->nranks();
   if (M % n) return R(fail(kInvalidArgument, "M=%d is not divisible by %d ranks", M, n));
   int rpr = M / n;
-  if ((rpr + kAgUnitRows - 1) / kAgUnitRows > kMaxUnits) return R(fail(kInvalidArgument, "more than %d rows per rank", kAgUnitRows * kMaxUnits));
   if ((s = c->prepare_stream(stream)) != kSuccess) return R(s);
   GemmLaunch g;
   memset(&g, 0, sizeof(g));
@@ -293,29 +292,43 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
   g.p.ldc = N;
   g.p.rows_per_rank = rpr;
   g.p.a_local = a_shard;
+  g.p.ag_unit_rows = gemm_ag_unit_rows(rpr, K);
+  // Every CTA computes (one extra warp of each moves data), so the tiling is planned like the plain
+  // GEMM's: tile height, tile width and the split of the last wave along K.  The emulation runs all
+  // ranks in one grid on one stream: they would share the split workspace, so it runs unsplit.
+  g.grid = c->emulated() ? emu_grid(n) : gemm_default_grid(c->device());
+  SplitKWs* ws = nullptr;
+  if (n > 1 && !c->emulated() && env_long("AMEM_GEMM_SPLITK", 1) && !Registry::instance().is_paused(0))
+    ws = splitk_workspace(c->device(), stream, g.grid);
+  GemmPlan plan = plan_gemm(M, N, K, g.grid, ws != nullptr);
+  if (rpr <= kGemmBM && plan.tall) {
+    plan.tall = 0;
+    plan.bn = gemm_pick_bn(n * ((rpr + kGemmBM - 1) / kGemmBM), N, g.grid, ws ? (K + kGemmBK - 1) / kGemmBK : 0, &plan.slices);
+  }
+  const int tile_rows = plan.tall ? 2 * kGemmBM : kGemmBM;
+  g.p.tall = plan.tall;
+  g.p.bn = plan.bn;
+  if (ws && plan.slices > 1) {
+    g.p.sk_slices = plan.slices;
+    g.p.sk_ws = ws->partials;
+    g.p.sk_ctr = ws->counters;
+  }
   if (n == 1) {
     g.p.mode = kGemmPlain;
-    if ((s = make_tensor_map_bf16(&g.map_a, a_shard, M, K, K, kGemmBM)) != kSuccess) return R(s);
+    if ((s = make_tensor_map_bf16(&g.map_a, a_shard, M, K, K, tile_rows)) != kSuccess) return R(s);
     g.map_a_local = g.map_a;
   } else {
     g.p.mode = kGemmAllGather;
     Segment* seg = nullptr;
     if ((s = c->fused_segment(0, (size_t)M * K * 2, &seg)) != kSuccess) return R(s);
     for (int r = 0; r < n; ++r) g.p.ag_buf[r] = (void*)seg->va[r];
-    if ((s = make_tensor_map_bf16(&g.map_a, g.p.ag_buf[c->rank()], M, K, K, kGemmBM)) != kSuccess) return R(s);
-    if ((s = make_tensor_map_bf16(&g.map_a_local, a_shard, rpr, K, K, kGemmBM)) != kSuccess) return R(s);
+    if ((s = make_tensor_map_bf16(&g.map_a, g.p.ag_buf[c->rank()], M, K, K, tile_rows)) != kSuccess) return R(s);
+    if ((s = make_tensor_map_bf16(&g.map_a_local, a_shard, rpr, K, K, tile_rows)) != kSuccess) return R(s);
   }
-  if (c->emulated()) {
-    g.grid = emu_grid(n);
-    g.p.comm_ctas = 1;
-  } else {
-    g.grid = gemm_default_grid(c->device());
-    g.p.comm_ctas = n > 1 ? (int)env_long("AMEM_AG_COMM_CTAS", 16) : 0;
-    if (g.p.comm_ctas > g.grid / 2) g.p.comm_ctas = g.grid / 2;
-  }
-  g.p.bn = gemm_pick_bn(n * ((rpr + kGemmBM - 1) / kGemmBM), N, g.grid - g.p.comm_ctas);
   if ((s = make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn)) != kSuccess) return R(s);
-  return R(run_gemm(c, g, stream));
+  s = run_gemm(c, g, stream);
+  if (s != kSuccess && ws) cudaMemsetAsync(ws->counters, 0, gemm_splitk_ctr_words(g.grid) * sizeof(uint32_t), stream);
+  return R(s);
 }
 
 // out[M/nranks, N] = reduce_scatter_rows(A[M, K] * B[N, K]^T): every rank holds a K-slice

@@ -91,7 +91,7 @@ AMEM_FN void run_chunks(const CollArgs& a, Proto& p, uint32_t nch, int push_sixt
 }
 
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
+AMEM_BODY void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t B = a.count * es;  // bytes contributed by each rank
@@ -135,7 +135,7 @@ AMEM_FN void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
 }
 
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
+AMEM_BODY void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t B = a.count * es;  // bytes exchanged with each peer
@@ -180,7 +180,7 @@ AMEM_FN void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
 // acknowledgement that normally arrived long before it is looked at.  The flag is the block's
 // operation count, which starts at 1: zeroed memory never looks like a packet.
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_alltoall_ll(const CollArgs& a, Proto& p) {
+AMEM_BODY void body_alltoall_ll(const CollArgs& a, Proto& p) {
   const int n = a.nranks, r = a.rank;
   const size_t B = a.count * sizeof(TI);          // bytes exchanged with each peer
   const size_t words = (B + 3) / 4;
@@ -245,7 +245,7 @@ AMEM_FN void body_alltoall_ll(const CollArgs& a, Proto& p) {
 // Reduce-scatter with the optional fused scale and output-type cast (gradient averaging and
 // fp32 <-> bf16 conversion happen in the same pass that reduces).
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems) {
+AMEM_BODY void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t R = a.count;  // elements each rank receives
@@ -284,7 +284,7 @@ AMEM_FN void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elems)
 }
 
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
+AMEM_BODY void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t B = a.count * es;
@@ -311,7 +311,7 @@ AMEM_FN void body_allreduce_oneshot(const CollArgs& a, Proto& p) {
 // complete: each rank's earlier kernels have finished once its block arrives) and one after (the
 // outputs are complete).  Safe in place: slice r is read and written by rank r only.
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_allreduce_window(const CollArgs& a, Proto& p) {
+AMEM_BODY void body_allreduce_window(const CollArgs& a, Proto& p) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI), vi = 16 / es;
   const size_t N = a.count;
@@ -335,13 +335,13 @@ AMEM_FN void body_allreduce_window(const CollArgs& a, Proto& p) {
 }
 
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch);
+AMEM_BODY void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch);
 
 // Two-shot: reduce-scatter of the chunk into region X, then all-gather of the reduced slices
 // through region Y; both regions live in the half selected by opseq, no quarter alternation
 // is needed because each chunk ends with a barrier of its own before Y is read.
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_elems) {
+AMEM_BODY void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t N = a.count;
@@ -425,7 +425,7 @@ AMEM_FN void body_allreduce_twoshot(const CollArgs& a, Proto& p, size_t chunk_el
 // safe (scatter of N waits for everybody's reduce of N-2; the reduce of N waits for everybody's
 // scatter of N, which each rank issues after its gather of N-2).
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch) {
+AMEM_BODY void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_t ce, uint32_t nch) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI), vi = 16 / es;
   const size_t N = a.count;
@@ -520,7 +520,7 @@ AMEM_FN void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, size_
 // staging into its buffer.  Chunks run on the same credits as all-gather: the root's next chunk is
 // on the wire while the previous one is drained.
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
+AMEM_BODY void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t B = a.count * es;
@@ -563,7 +563,7 @@ AMEM_FN void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
 }
 
 template <typename TI, typename TO, int OP>
-AMEM_FN void body_reduce(const CollArgs& a, Proto& p, size_t chunk_elems) {
+AMEM_BODY void body_reduce(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(TI);
   const size_t N = a.count;

@@ -264,13 +264,18 @@ __device__ __forceinline__ void copy_span_mc(char* dst_mc, const char* src, size
 // out[i] = cast(scale * OP_r(slot_r[i]))  for i in [0, n); reduction order is rank 0..nslots-1,
 // accumulated in Acc<TI> (fp32 for 16-bit floats) and rounded once.
 template <typename TI, typename TO, int OP>
-__device__ __noinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale, Lane ln) {
+__device__ __forceinline__ void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, float scale, bool has_scale, Lane ln) {
   using A = typename Acc<TI>::type;
   constexpr int VI = 16 / sizeof(TI);
   int t = ln.tid, nt = ln.nt;
   bool aligned = (((uintptr_t)out) % (VI * sizeof(TO)) == 0);
   for (int r = 0; r < nslots; ++r) aligned = aligned && (((uintptr_t)slots[r] & 15) == 0);
   size_t nvec = aligned ? n / VI : 0;
+  // The slot pointers sit in the caller's local memory and the stores to `out` could alias them as
+  // far as the compiler knows: copy them into registers once instead of re-reading them per vector.
+  const uint4* sp[kMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kMaxRanks; ++r) sp[r] = r < nslots ? (const uint4*)slots[r] : nullptr;
   auto one = [&](size_t i, const uint4* raw, auto nmax) {  // nmax: length of raw[], a compile-time constant
     constexpr int NM = decltype(nmax)::value;
     A acc[VI];
@@ -314,8 +319,8 @@ __device__ __noinline__ void reduce_span(TO* out, const TI* const* slots, int ns
 #pragma unroll
       for (int r = 0; r < kMaxRanks / 2; ++r) {
         if (r < nslots) {
-          ra[r] = ((const uint4*)slots[r])[i];
-          rb[r] = ((const uint4*)slots[r])[i + nt];
+          ra[r] = sp[r][i];
+          rb[r] = sp[r][i + nt];
         }
       }
       one(i, ra, std::integral_constant<int, kMaxRanks / 2>());
@@ -326,7 +331,7 @@ __device__ __noinline__ void reduce_span(TO* out, const TI* const* slots, int ns
     uint4 ra[kMaxRanks];
 #pragma unroll
     for (int r = 0; r < kMaxRanks; ++r)
-      if (r < nslots) ra[r] = ((const uint4*)slots[r])[i];
+      if (r < nslots) ra[r] = sp[r][i];
     one(i, ra, std::integral_constant<int, kMaxRanks>());
   }
   for (size_t i = nvec * VI + t; i < n; i += nt) {

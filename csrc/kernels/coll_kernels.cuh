@@ -14,8 +14,10 @@
 namespace amem {
 namespace dev {
 #define AMEM_FN __device__ __forceinline__
+#define AMEM_BODY __device__ __noinline__
 #include "coll_bodies.inl"
 #undef AMEM_FN
+#undef AMEM_BODY
 
 template <typename TI, typename TO, int OP, bool RED>
 __global__ void __launch_bounds__(512) coll_kernel(const __grid_constant__ CollArgs a, size_t chunk_elems) {

@@ -1,11 +1,12 @@
 // tcgen05 / TMEM / TMA GEMM for sm_100a, alone and fused with its neighbouring collective.
 //
 //   plain            C = A * B^T
-//   all-gather->GEMM  A's row shards live on different ranks.  A few CTAs of the same kernel
-//                    stream this rank's shard into every peer's gathered buffer with bulk
-//                    async copies (global -> shared once, shared -> each peer) and announce
-//                    every 32 rows with a flag; the compute CTAs start on the local shard at
-//                    once and pick up remote row blocks in the order they arrive.
+//   all-gather->GEMM  A's row shards live on different ranks.  One extra warp of EVERY CTA streams
+//                    a slice of this rank's shard into every peer's gathered buffer with bulk
+//                    async copies (global -> shared once, shared -> each peer; 8 KB pieces through
+//                    a small staging area beside the operand ring) and announces every few rows
+//                    with a flag, so all SMs compute: they start on the local shard at once and
+//                    pick up remote row blocks in the order they arrive.
 //   GEMM->reduce-scatter  each output row block belongs to one rank.  The epilogue stores
 //                    bf16 partial tiles straight into the owner's slot buffer over NVLink and
 //                    counts them in; when a CTA runs out of tiles it reduces finished row
@@ -17,7 +18,7 @@
 // use cluster multicast and only ever read this GPU's own memory; peers are reached with plain
 // or bulk stores.  Every wait is bounded and ends in an error status, not a hang.
 //
-// The plain mode has two more forms, chosen per problem by the host (gemm_tall_pays,
+// The plain and all-gather modes have two more forms, chosen per problem by the host (gemm_tall_pays,
 // gemm_tail_slices): tiles of 256 x 256 (template parameter MT = 2: two 128-row accumulators fill
 // all 512 TMEM columns and share one B tile, 3 stages of 64 KB, eight epilogue warps), and a
 // split of the partly filled last wave of tiles along K (its CTAs park fp32 partial accumulators
@@ -43,8 +44,12 @@ constexpr int BM = kGemmBM, BN_MAX = kGemmBN, BK = kGemmBK, STAGES = kGemmStages
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_MAX * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int UMMA_K = 16;
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy of the all-gather mover
+constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy when split-K partials are fetched into the ring
 constexpr int EPI_CHUNK_BYTES = BM * 32 * 2;  // one 32-column chunk of a tile in bf16
+// Staging beside the ring: two chunks for the reduce-scatter epilogue, or four pieces of the
+// all-gather mover (the two modes never run in one launch).
+constexpr int SIDE_BUFS = 4;
+static_assert(kAgPieceBytes == EPI_CHUNK_BYTES, "the mover's pieces use the epilogue's staging buffers");
 // A parked (split-K) accumulator: BN/4 column groups x (rows of every band padded to an odd
 // count) x 4 floats; bands x padded rows <= BM + 2 * slices <= BM + 64.
 constexpr int SK_MAX_SLICES = 32;
@@ -55,7 +60,8 @@ struct __align__(8) SmemCtl {
   uint64_t empty[STAGES];
   uint64_t tfull[2];
   uint64_t tempty[2];
-  uint64_t copy_full[STAGES];
+  uint64_t copy_full[STAGES];   // all-gather mover: a piece has landed in side buffer s
+  uint64_t sk_full;             // split-K fix-up: the bands of all slices have landed in the ring
   uint32_t tmem_base;
   int abort;
   int s_abort_coll;
@@ -188,66 +194,77 @@ __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// ---- all-gather mover: one thread per CTA drives bulk copies through the (otherwise unused)
-// operand ring; unit = kAgUnitRows rows of my shard, contiguous in memory.  Loads run two
-// pieces ahead of the stores; a piece is read from HBM once and stored to every peer.
+// ---- all-gather mover: one thread per CTA drives bulk copies through the side buffers; a unit
+// = p.ag_unit_rows rows of my shard, contiguous in memory; CTA c moves units c, c + nctas, ... so
+// the CTAs together deliver the shard roughly front to back.  Loads run two pieces ahead of the
+// stores; a piece is read from HBM once and stored to every peer.
 struct PieceIter {
   int u;        // current unit
   size_t o;     // byte offset inside the unit
   bool valid;
 };
 __device__ __forceinline__ size_t unit_bytes(const GemmParams& p, int u) {
-  int rows = min(kAgUnitRows, p.rows_per_rank - u * kAgUnitRows);
+  int rows = min(p.ag_unit_rows, p.rows_per_rank - u * p.ag_unit_rows);
   return (size_t)rows * (size_t)p.K * 2;
 }
-__device__ __forceinline__ void piece_next(const GemmParams& p, int units, PieceIter& it) {
-  it.o += COPY_PIECE;
+__device__ __forceinline__ void piece_next(const GemmParams& p, int units, int nctas, PieceIter& it) {
+  it.o += kAgPieceBytes;
   if (it.o >= unit_bytes(p, it.u)) {
     it.o = 0;
-    it.u += p.comm_ctas;
+    it.u += nctas;
     it.valid = it.u < units;
   }
 }
-__device__ void ag_mover(const GemmParams& p, char* ring, SmemCtl* ctl, int cta, uint32_t epoch) {
+__device__ void ag_mover(const GemmParams& p, char* bufs, SmemCtl* ctl, int cta, int nctas, uint32_t epoch) {
   const int n = p.coll.nranks, r = p.coll.rank;
   const size_t row_bytes = (size_t)p.K * 2;
-  const int units = (p.rows_per_rank + kAgUnitRows - 1) / kAgUnitRows;
+  const size_t unit_stride = (size_t)p.ag_unit_rows * row_bytes;
+  const int units = (p.rows_per_rank + p.ag_unit_rows - 1) / p.ag_unit_rows;
   const char* src = (const char*)p.a_local;
   const size_t shard_off = (size_t)r * p.rows_per_rank * row_bytes;
-  uint32_t phase_bits = 0;  // parity of copy_full[s], one bit per stage
+  uint32_t phase_bits = 0;  // parity of copy_full[s], one bit per buffer
   PieceIter ld{cta, 0, cta < units}, st = ld;
   auto issue_load = [&](const PieceIter& it, int k) {
     size_t ub = unit_bytes(p, it.u);
-    uint32_t len = (uint32_t)min((size_t)COPY_PIECE, ub - it.o);
-    int s = k % STAGES;
+    uint32_t len = (uint32_t)min((size_t)kAgPieceBytes, ub - it.o);
+    int s = k % SIDE_BUFS;
     mbar_expect_tx(&ctl->copy_full[s], len);
-    bulk_g2s(ring + (size_t)s * STAGE_BYTES, src + (size_t)it.u * kAgUnitRows * row_bytes + it.o, len, &ctl->copy_full[s]);
+    bulk_g2s(bufs + (size_t)s * kAgPieceBytes, src + (size_t)it.u * unit_stride + it.o, len, &ctl->copy_full[s]);
   };
   int loaded = 0;
   for (; loaded < 2 && ld.valid; ++loaded) {
     issue_load(ld, loaded);
-    piece_next(p, units, ld);
+    piece_next(p, units, nctas, ld);
   }
   for (int k = 0; st.valid; ++k) {
-    const int s = k % STAGES;
-    if (!mbar_wait(&ctl->copy_full[s], (phase_bits >> s) & 1u, p.coll.timeout_ns, &ctl->abort)) return;
+    const int s = k % SIDE_BUFS;
+    if (!mbar_wait(&ctl->copy_full[s], (phase_bits >> s) & 1u, p.coll.timeout_ns, &ctl->abort)) {
+      // gave up: let the loads already in flight land before the CTA exits
+      for (int k2 = k; k2 < loaded; ++k2) {
+        const int s2 = k2 % SIDE_BUFS;
+        for (int i = 0; i < 100000 && !mbar_try_wait(&ctl->copy_full[s2], (phase_bits >> s2) & 1u); ++i) {
+        }
+      }
+      break;
+    }
     phase_bits ^= 1u << s;
     const size_t ub = unit_bytes(p, st.u);
-    const uint32_t len = (uint32_t)min((size_t)COPY_PIECE, ub - st.o);
-    const size_t dst_off = shard_off + (size_t)st.u * kAgUnitRows * row_bytes + st.o;
-    char* buf = ring + (size_t)s * STAGE_BYTES;
+    const uint32_t len = (uint32_t)min((size_t)kAgPieceBytes, ub - st.o);
+    const size_t dst_off = shard_off + (size_t)st.u * unit_stride + st.o;
+    char* buf = bufs + (size_t)s * kAgPieceBytes;
     for (int q1 = 1; q1 < n; ++q1) bulk_s2g((char*)p.ag_buf[(r + q1) % n] + dst_off, buf, len);
     if (p.copy_own) bulk_s2g((char*)p.ag_buf[r] + dst_off, buf, len);
     bulk_commit();
     const bool unit_done = st.o + len >= ub;
     const int unit = st.u;
-    piece_next(p, units, st);
+    piece_next(p, units, nctas, st);
     if (ld.valid) {
       // the buffer of piece k+2 was last read by the stores of piece k-2: let all but the
       // newest store group finish reading, then refill it
       asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
       issue_load(ld, k + 2);
-      piece_next(p, units, ld);
+      loaded = k + 3;
+      piece_next(p, units, nctas, ld);
     }
     if (unit_done) {
       bulk_wait_all();  // this unit's bytes have been written
@@ -256,6 +273,7 @@ __device__ void ag_mover(const GemmParams& p, char* ring, SmemCtl* ctl, int cta,
       if (p.copy_own) dev::st_release_sys(&p.fflags[r]->ag_ready[r][unit], epoch);
     }
   }
+  bulk_wait_all();  // nothing of this CTA's shared memory is still being read when it exits
 }
 
 // ---- reduce phase of GEMM -> reduce-scatter: out = sum over source slots, fixed order.
@@ -317,13 +335,13 @@ __device__ void rs_reduce(const GemmParams& p, SmemCtl* ctl, int cta, int nctas,
 }
 
 // ---- the kernel body, shared by the one-rank-per-GPU kernel and the emulation kernel -------
-template <int MT>  // accumulators (128-row halves) per tile: 1, or 2 for the tall tiles of the plain mode
+template <int MT>  // accumulators (128-row halves) per tile: 1, or 2 for the tall tiles of the plain and all-gather modes
 __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const CUtensorMap* map_a_local, const CUtensorMap* map_b,
                           int cta, int nctas, char* smem_raw) {
   // operand ring first (1024-byte aligned for the 128-byte swizzle), control words after it
   char* ring = (char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  char* epi_stage = ring + (size_t)STAGES * STAGE_BYTES;  // 2 x 8 KB, reduce-scatter epilogue
-  SmemCtl* ctl = (SmemCtl*)(epi_stage + 2 * EPI_CHUNK_BYTES);
+  char* epi_stage = ring + (size_t)STAGES * STAGE_BYTES;  // 4 x 8 KB: reduce-scatter epilogue (2) or all-gather mover (4)
+  SmemCtl* ctl = (SmemCtl*)(epi_stage + SIDE_BUFS * EPI_CHUNK_BYTES);
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int n = p.coll.nranks, r = p.coll.rank;
   const bool fused = n > 1 && p.mode != kGemmPlain;
@@ -335,6 +353,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       mbar_init(&ctl->empty[s], 1);
       mbar_init(&ctl->copy_full[s], 1);
     }
+    mbar_init(&ctl->sk_full, 1);
     for (int b = 0; b < 2; ++b) {
       mbar_init(&ctl->tfull[b], 1);
       mbar_init(&ctl->tempty[b], 4 * MT);  // one arrival per epilogue warp
@@ -355,14 +374,18 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   const uint32_t tmem_base = ctl->tmem_base;
   const uint32_t epoch = proto.opseq + 1u;  // value of this launch's all-gather ready flags
 
-  const int comm_ctas = (p.mode == kGemmAllGather && fused) ? p.comm_ctas : 0;
-  const bool is_mover = cta < comm_ctas;
   // Cross-launch guard: before anything of this launch lands in a peer's buffer, the peer must
-  // have left the previous launch (it signals this barrier only after starting this one).
-  if (fused && (is_mover || p.mode == kGemmReduceScatter)) dev::block_barrier(proto);
+  // have left the previous launch (it signals this barrier only after starting this one).  The
+  // reduce-scatter epilogue writes to peers from every warp: the whole CTA waits.  In the all-gather
+  // mode only the mover warp writes to peers: it alone exchanges the flags (mover_barrier below,
+  // same flag words and epoch as block_barrier) and the compute warps start at once.
+  const bool ag = p.mode == kGemmAllGather && fused;
+  constexpr int MOVER_WARP = 2 + 4 * MT;
+  if (fused && p.mode == kGemmReduceScatter) dev::block_barrier(proto);
+  if (ag) proto.epoch += 1;
 
-  // Tall tiles (plain mode only): MT = 2 accumulators of 128 rows share one B tile; the ring
-  // then holds 3 stages of 64 KB (A 32 KB + B 32 KB) instead of 4 of 48 KB.
+  // Tall tiles (plain and all-gather modes): MT = 2 accumulators of 128 rows share one B tile; the
+  // ring then holds 3 stages of 64 KB (A 32 KB + B 32 KB) instead of 4 of 48 KB.
   constexpr int TM = BM * MT;                                   // rows of a tile
   constexpr int n_stages = MT == 2 ? 3 : STAGES;
   constexpr int a_bytes = A_BYTES * MT;
@@ -373,38 +396,59 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   const int shards = (p.mode == kGemmPlain || n == 1) ? 1 : n;
   const int total_tiles = p.mode == kGemmGrouped ? grouped_total_tiles(p, tiles_n) : tiles_m * tiles_n * shards;
   const int num_kb = (p.K + BK - 1) / BK;
-  const int g = cta - comm_ctas, G = nctas - comm_ctas;  // compute CTA index / count
+  const int g = cta, G = nctas;  // every CTA computes
   const uint32_t idesc = make_idesc_bf16(BM, BN);
-  const int S = (p.mode == kGemmPlain && p.sk_slices > 1 && p.sk_ws && p.sk_ctr) ? p.sk_slices : 1;
-  const int n_items = is_mover ? 0 : work_count(g, G, total_tiles, S);
+  const int S = ((p.mode == kGemmPlain || p.mode == kGemmAllGather) && p.sk_slices > 1 && p.sk_ws && p.sk_ctr) ? p.sk_slices : 1;
+  const int n_items = work_count(g, G, total_tiles, S);
 
-  if (is_mover) {
-    if (threadIdx.x == 0) ag_mover(p, ring, ctl, cta, epoch);
-  } else if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0, issued = 0, issued_phase = 0;
-      bool ok = true;
-      for (int i = 0; i < n_items && ok; ++i) {
-        const Work wk = work_of(i, g, G, total_tiles, S, num_kb);
-        Tile tl = tile_of(p, wk.t, tiles_m, tiles_n);
-        const bool remote = p.mode == kGemmAllGather && fused && tl.shard != r;
-        if (remote) {
-          // wait for every 32-row unit this 128-row tile covers
-          int u0 = tl.m_in * (BM / kAgUnitRows);
-          int u1 = min(u0 + BM / kAgUnitRows, (p.rows_per_rank + kAgUnitRows - 1) / kAgUnitRows);
-          for (int u = u0; u < u1 && ok; ++u) {
-            if (*abort || !dev::wait_flag_ge(&p.fflags[r]->ag_ready[tl.shard][u], epoch, p.coll.timeout_ns)) {
-              dev::report_error(p.coll.status, kDevGemmTimeout, r, tl.shard, u, epoch);
-              *abort = 1;
-              ok = false;
-            }
-          }
-          fence_proxy_async();  // peers' stores -> my TMA reads
+  if (warp == MOVER_WARP) {
+    // ------------------------------------------------------------ all-gather mover
+    if (ag) {
+      // the cross-launch guard, by this warp alone: lane t talks to rank t
+      bool go = true;
+      if (lane < n && lane != r) {
+        __threadfence_system();
+        dev::st_release_sys(&p.coll.ctrl[lane]->flags[cta][r], proto.epoch);
+        if (!dev::wait_flag_ge(&proto.me->flags[cta][lane], proto.epoch, p.coll.timeout_ns)) {
+          dev::report_error(p.coll.status, kDevBarrierTimeout, r, lane, cta, proto.epoch);
+          *abort = 1;
+          go = false;
         }
-        const CUtensorMap* ma = (p.mode == kGemmAllGather && fused && !remote) ? map_a_local : map_a;
-        int row0 = tl.m_in * TM + ((p.mode == kGemmAllGather && fused && !remote) ? 0 : tl.shard * p.rows_per_rank);
+      }
+      go = __all_sync(0xffffffffu, go);
+      if (go && lane == 0) ag_mover(p, epi_stage, ctl, cta, nctas, epoch);
+    }
+  } else if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (lane 0 issues;
+    // the whole warp polls the ready flags of a remote tile's rows)
+    int stage = 0;
+    uint32_t phase = 0, issued = 0, issued_phase = 0;
+    bool ok = true;
+    for (int i = 0; i < n_items && ok; ++i) {
+      const Work wk = work_of(i, g, G, total_tiles, S, num_kb);
+      Tile tl = tile_of(p, wk.t, tiles_m, tiles_n);
+      const bool remote = ag && tl.shard != r;
+      if (remote) {
+        const int ur = p.ag_unit_rows;
+        const int r0 = tl.m_in * TM, r1 = min(r0 + TM, p.rows_per_rank);
+        const int u0 = r0 / ur, u1 = (r1 + ur - 1) / ur;
+        bool mine = true;
+        for (int u = u0 + lane; u < u1 && mine; u += 32) {
+          if (*abort || !dev::wait_flag_ge(&p.fflags[r]->ag_ready[tl.shard][u], epoch, p.coll.timeout_ns)) {
+            dev::report_error(p.coll.status, kDevGemmTimeout, r, tl.shard, u, epoch);
+            *abort = 1;
+            mine = false;
+          }
+        }
+        ok = __all_sync(0xffffffffu, mine);
+        if (lane == 0) {
+          __threadfence_system();  // what the other lanes acquired is ordered before this lane's reads
+          fence_proxy_async();     // peers' stores -> my TMA reads
+        }
+      }
+      if (lane == 0 && ok) {
+        const CUtensorMap* ma = (ag && !remote) ? map_a_local : map_a;
+        int row0 = tl.m_in * TM + ((ag && !remote) ? 0 : tl.shard * p.rows_per_rank);
         int b_row0 = tl.n_blk * BN;
         if (p.mode == kGemmGrouped) {
           row0 = tl.row0;
@@ -424,13 +468,14 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           }
         }
       }
-      if (!ok) {
-        // gave up: let the copies already in flight land before the CTA exits
-        dev::report_error(p.coll.status, kDevGemmTimeout, r, r, cta, 0xdead0001u);
-        for (int s = 0; s < STAGES; ++s) {
-          if (!(issued & (1u << s))) continue;
-          for (int i = 0; i < 100000 && !mbar_try_wait(&ctl->full[s], (issued_phase >> s) & 1u); ++i) {
-          }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    }
+    if (lane == 0 && !ok) {
+      // gave up: let the copies already in flight land before the CTA exits
+      dev::report_error(p.coll.status, kDevGemmTimeout, r, r, cta, 0xdead0001u);
+      for (int s = 0; s < STAGES; ++s) {
+        if (!(issued & (1u << s))) continue;
+        for (int i = 0; i < 100000 && !mbar_try_wait(&ctl->full[s], (issued_phase >> s) & 1u); ++i) {
         }
       }
     }
@@ -580,15 +625,15 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
           asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");  // the ring is free: MMAs done (h = 0), sums of the first half done (h = 1)
           if (warp == 2 && lane == 0 && !*abort && r1 > r0) {
             fence_proxy_async();
-            mbar_expect_tx(&ctl->copy_full[0], band_bytes * (uint32_t)S);
+            mbar_expect_tx(&ctl->sk_full, band_bytes * (uint32_t)S);
             for (int s2 = 0; s2 < S; ++s2) {
               const char* src = (const char*)(p.sk_ws + (((size_t)j * S + s2) * MT + h) * part_elems + (size_t)wk.slice * band_vecs * 4);
               for (uint32_t o = 0; o < band_bytes; o += COPY_PIECE)
-                bulk_g2s(ring + (size_t)s2 * band_bytes + o, src + o, min((uint32_t)COPY_PIECE, band_bytes - o), &ctl->copy_full[0]);
+                bulk_g2s(ring + (size_t)s2 * band_bytes + o, src + o, min((uint32_t)COPY_PIECE, band_bytes - o), &ctl->sk_full);
             }
           }
           asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-          if (!*abort && r1 > r0 && mbar_wait(&ctl->copy_full[0], (uint32_t)h & 1u, p.coll.timeout_ns, abort)) {
+          if (!*abort && r1 > r0 && mbar_wait(&ctl->sk_full, (uint32_t)h & 1u, p.coll.timeout_ns, abort)) {
             const float4* sm = (const float4*)ring;
             const int total = (r1 - r0) * groups;
             for (int e = my_h * 128 + row; e < total; e += EPI_THREADS) {
@@ -720,7 +765,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
 }
 
 template <int MT>
-__global__ void __launch_bounds__(64 + 128 * MT, 1)  // TMA warp, MMA warp, 4 * MT epilogue warps
+__global__ void __launch_bounds__(96 + 128 * MT, 1)  // TMA warp, MMA warp, 4 * MT epilogue warps, mover warp
 gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
             const __grid_constant__ CUtensorMap map_a_local, const __grid_constant__ CUtensorMap map_b) {
   extern __shared__ char smem_raw[];
@@ -730,10 +775,11 @@ gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtens
 struct EmuGemmParams {
   GemmLaunch rank[kMaxRanks];
 };
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel_emu(const __grid_constant__ EmuGemmParams all) {
+template <int MT>
+__global__ void __launch_bounds__(96 + 128 * MT, 1) gemm_kernel_emu(const __grid_constant__ EmuGemmParams all) {
   extern __shared__ char smem_raw[];
   const GemmLaunch& g = all.rank[blockIdx.y];
-  gemm_body<1>(g.p, &g.map_a, &g.map_a_local, &g.map_b, blockIdx.x, gridDim.x, smem_raw);
+  gemm_body<MT>(g.p, &g.map_a, &g.map_a_local, &g.map_b, blockIdx.x, gridDim.x, smem_raw);
 }
 
 }  // namespace gemmk
@@ -772,7 +818,13 @@ Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, u
   return kSuccess;
 }
 
-size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + 2 * gemmk::EPI_CHUNK_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
+size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + gemmk::SIDE_BUFS * gemmk::EPI_CHUNK_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
+
+int gemm_ag_unit_rows(int rows_per_rank, int K) {
+  const int by_flags = (rows_per_rank + kMaxAgUnits - 1) / kMaxAgUnits;      // at most kMaxAgUnits flags per source
+  const int by_piece = (kAgPieceBytes + K * 2 - 1) / (K * 2);                // a unit is at least one piece of the mover
+  return std::max(1, std::max(by_flags, by_piece));
+}
 
 static double splitk_fixup_blocks() {
   const long v = env_long("AMEM_GEMM_SPLITK_COST", 24);  // in K blocks of main loop (measured: 20-35)
@@ -849,9 +901,9 @@ static Status prepare_kernel(const void* fn) {
 Status launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
   static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel<1>);
   static Status ready_tall = prepare_kernel((const void*)gemmk::gemm_kernel<2>);
-  const bool tall = g.p.mode == kGemmPlain && g.p.tall;
+  const bool tall = (g.p.mode == kGemmPlain || g.p.mode == kGemmAllGather) && g.p.tall;
   if ((tall ? ready_tall : ready) != kSuccess) return tall ? ready_tall : ready;
-  if (tall) gemmk::gemm_kernel<2><<<g.grid, 64 + 128 * 2, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
+  if (tall) gemmk::gemm_kernel<2><<<g.grid, kGemmThreadsTall, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
   else gemmk::gemm_kernel<1><<<g.grid, kGemmThreads, gemm_smem_bytes(), stream>>>(g.p, g.map_a, g.map_a_local, g.map_b);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(kCudaError, "gemm launch failed: %s", cudaGetErrorString(e));
@@ -859,13 +911,16 @@ Status launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
 }
 
 Status launch_gemm_emu(const GemmLaunch* ranks, int nranks, cudaStream_t stream) {
-  static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel_emu);
-  if (ready != kSuccess) return ready;
+  static Status ready = prepare_kernel((const void*)gemmk::gemm_kernel_emu<1>);
+  static Status ready_tall = prepare_kernel((const void*)gemmk::gemm_kernel_emu<2>);
+  const bool tall = ranks[0].p.mode == kGemmAllGather && ranks[0].p.tall;
+  if ((tall ? ready_tall : ready) != kSuccess) return tall ? ready_tall : ready;
   static gemmk::EmuGemmParams all;  // launches are serialised by the emulation rendez-vous
   for (int r = 0; r < nranks; ++r) all.rank[r] = ranks[r];
   void* params[] = {(void*)&all};
-  dim3 grid(ranks[0].grid, nranks), block(kGemmThreads);
-  cudaError_t e = cudaLaunchCooperativeKernel((const void*)gemmk::gemm_kernel_emu, grid, block, params, gemm_smem_bytes(), stream);
+  dim3 grid(ranks[0].grid, nranks), block(tall ? kGemmThreadsTall : kGemmThreads);
+  const void* fn = tall ? (const void*)gemmk::gemm_kernel_emu<2> : (const void*)gemmk::gemm_kernel_emu<1>;
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, grid, block, params, gemm_smem_bytes(), stream);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return fail(kCudaError, "emulated gemm cooperative launch (%d x %d CTAs) failed: %s", ranks[0].grid, nranks, cudaGetErrorString(e));

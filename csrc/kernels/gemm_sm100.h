@@ -12,9 +12,11 @@
 namespace amem {
 
 static const int kGemmBM = 128, kGemmBN = 256, kGemmBK = 64, kGemmStages = 4;
-static const int kGemmThreads = 192;       // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
-static const int kAgUnitRows = 32;         // rows of A announced by one all-gather ready flag
-static const int kMaxUnits = 256;          // flag slots per source rank
+static const int kGemmThreads = 224;       // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warp 6: all-gather mover
+static const int kGemmThreadsTall = 352;   // 256-row tiles: eight epilogue warps (2-9), mover warp 10
+static const int kMaxUnits = 256;          // reduce-scatter: row blocks (of 128 rows) per rank
+static const int kMaxAgUnits = 1024;       // all-gather: ready flags per source rank (a flag covers GemmParams::ag_unit_rows rows)
+static const int kAgPieceBytes = 8192;     // all-gather: bytes per bulk copy of the mover
 
 // kGemmGrouped: A [rows, K] holds `groups` runs of rows, run e = [group_off[e], group_off[e+1]) with
 // group_off in DEVICE memory (the MoE dispatch produces it there, nothing comes back to the host);
@@ -30,21 +32,22 @@ enum GemmEpilogue : int { kEpiStore = 0, kEpiSwiGLU = 1 };
 // Flags of the fused kernels; lives in every rank's control segment right after CtrlBlock,
 // so it is saved and restored by pause/resume like the rest of the protocol state.
 struct FusedFlags {
-  uint32_t ag_ready[kMaxRanks][kMaxUnits];   // written by source rank s: unit u of its shard has landed (value = epoch)
+  uint32_t ag_ready[kMaxRanks][kMaxAgUnits]; // written by source rank s: unit u of its shard has landed (value = epoch)
   uint32_t rs_done[kMaxRanks][kMaxUnits];    // incremented by source rank s: partial tiles of row block u delivered
   uint32_t rs_expect[kMaxRanks][kMaxUnits];  // my running total of deliveries to expect per (source, row block)
 };
+static_assert(sizeof(FusedFlags) <= (1u << 16) - 256, "FusedFlags must fit the room kept for it behind CtrlBlock in the control segment");
 
 struct GemmParams {
   int M, N, K;              // problem of this rank (M = all rows, gathered or to be scattered)
   int bn;                   // tile width in columns: multiple of 32, <= kGemmBN (see gemm_pick_bn)
-  int tall;                 // plain mode: 1 = tiles of 256 rows (two accumulators side by side in TMEM, one B tile
+  int tall;                 // plain / all-gather: 1 = tiles of 256 rows (two accumulators side by side in TMEM, one B tile
                             // feeds both: a third less shared-memory fill per FLOP; the epilogue is then not overlapped)
   int mode;
   void* C;                  // plain / all-gather: bf16 [M, N] row-major, leading dimension ldc
   int ldc;
   int rows_per_rank;        // M / nranks (M when nranks == 1)
-  int comm_ctas;            // all-gather: CTAs [0, comm_ctas) move data, the rest compute
+  int ag_unit_rows;         // all-gather: rows of a shard announced by one ready flag (see gemm_ag_unit_rows)
   int copy_own;             // all-gather: also place my own shard in the gathered buffer
   const void* a_local;      // all-gather: my shard, bf16 [rows_per_rank, K]
   void* ag_buf[kMaxRanks];  // all-gather: every rank's gathered-A buffer [M, K]; [rank] is mine
@@ -54,7 +57,7 @@ struct GemmParams {
   const int* group_off;     // grouped: device array of groups + 1 row offsets
   int groups;               // grouped: number of groups (<= 256)
   int epilogue;             // grouped: GemmEpilogue
-  // Split-K of the last, partly filled wave of tiles (plain mode): each of its tiles is cut in
+  // Split-K of the last, partly filled wave of tiles (plain and all-gather modes): each of its tiles is cut in
   // sk_slices ranges of K that run on different CTAs; partial accumulators meet in sk_ws
   // (fp32, [tile][slice][32-column chunk][128 rows][32]) and are summed in slice order.
   int sk_slices;            // 0 or 1: off
@@ -87,6 +90,9 @@ int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks = 0, int* slices =
 bool gemm_tall_pays(int M, int N, int k_blocks, int ctas, int bn_flat, int slices_flat, int bn_tall, int slices_tall);
 // Slices of the tail split for a given tiling, 1 when splitting does not pay.
 int gemm_tail_slices(long tiles, int ctas, int k_blocks);
+// Rows per ready flag of the all-gather mode: as few as the flag array and the mover's copy size allow,
+// so that rows become usable in the order they arrive.
+int gemm_ag_unit_rows(int rows_per_rank, int K);
 // Bytes of split-K workspace / number of counters that a launch on `ctas` CTAs may touch.
 size_t gemm_splitk_ws_bytes(int ctas);
 size_t gemm_splitk_ctr_words(int ctas);

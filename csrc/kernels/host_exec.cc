@@ -166,8 +166,10 @@ inline void reduce_span(TO* out, const TI* const* slots, int nslots, size_t n, f
 }
 
 #define AMEM_FN inline
+#define AMEM_BODY inline
 #include "coll_bodies.inl"
 #undef AMEM_FN
+#undef AMEM_BODY
 
 }  // namespace hostx
 

@@ -59,8 +59,10 @@ def test_gemm_split_k_tail(M, N, K, tile_height):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-@pytest.mark.parametrize("m_local,N,K", [(128, 256, 256), (200, 520, 328), (512, 1024, 1024)])
-def test_all_gather_gemm(world, m_local, N, K):
+@pytest.mark.parametrize("m_local,N,K", [(128, 256, 256), (200, 520, 328), (512, 1024, 1024), (300, 264, 4096)])
+def test_all_gather_gemm(world, m_local, N, K, tile_height):
+    """Both tile heights; shards whose row count is no multiple of the tile height or of the rows
+    one ready flag covers (a flag covers 16 rows at K = 256, 13 at K = 328, one at K = 4096)."""
     from asystem_amem_b200.ops import all_gather_gemm
     shards = [_rand((m_local, K), 10 + r) for r in range(world)]
     weights = [_rand((N, K), 50 + r, 0.05) for r in range(world)]
