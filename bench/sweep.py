@@ -4,7 +4,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29520 bench/sweep.py [--max-bytes 8589934592] [--colls allreduce,allgather,...]
 
-Collectives: allreduce, allgather, reducescatter, alltoall, broadcast (the reference's run.sh:22 set plus
+Collectives: allreduce, allgather, reducescatter, alltoall, broadcast, reduce (the reference's run.sh:22 set plus
 reduce-scatter).  For every collective, dtype (bf16, fp32) and message size (8 B doubling up to --max-bytes) it
 times this library and NCCL with CUDA events on the launching stream (3 warm-ups, L2 flushed
 between iterations, max over ranks) and, like the reference's patched nccl-tests, calls
@@ -114,6 +114,10 @@ def main():
                 elif coll == "broadcast":
                     ours = lambda: comm.broadcast(x, y, root=0)
                     ref = lambda: dist.broadcast(y, src=0)
+                    factor = 1.0
+                elif coll == "reduce":
+                    ours = lambda: comm.reduce(x, y, root=0)
+                    ref = lambda: dist.reduce(y, dst=0)
                     factor = 1.0
                 elif coll == "allgather":
                     ours = lambda: comm.all_gather(x[: n // world], y)

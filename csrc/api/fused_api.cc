@@ -293,6 +293,7 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
   g.p.rows_per_rank = rpr;
   g.p.a_local = a_shard;
   g.p.ag_unit_rows = gemm_ag_unit_rows(rpr, K);
+  g.p.ag_mover = (int)env_long("AMEM_AG_MOVER", 0);
   // Every CTA computes (one extra warp of each moves data), so the tiling is planned like the plain
   // GEMM's: tile height, tile width and the split of the last wave along K.  The emulation runs all
   // ranks in one grid on one stream: they would share the split workspace, so it runs unsplit.

@@ -48,7 +48,7 @@ constexpr int COPY_PIECE = 32 * 1024;  // bytes per bulk copy when split-K parti
 constexpr int EPI_CHUNK_BYTES = BM * 32 * 2;  // one 32-column chunk of a tile in bf16
 // Staging beside the ring: two chunks for the reduce-scatter epilogue, or four pieces of the
 // all-gather mover (the two modes never run in one launch).
-constexpr int SIDE_BUFS = 4;
+constexpr int SIDE_BUFS = 4;   // a power of two
 static_assert(kAgPieceBytes == EPI_CHUNK_BYTES, "the mover's pieces use the epilogue's staging buffers");
 // A parked (split-K) accumulator: BN/4 column groups x (rows of every band padded to an odd
 // count) x 4 floats; bands x padded rows <= BM + 2 * slices <= BM + 64.
@@ -276,6 +276,40 @@ __device__ void ag_mover(const GemmParams& p, char* bufs, SmemCtl* ctl, int cta,
   bulk_wait_all();  // nothing of this CTA's shared memory is still being read when it exits
 }
 
+// The same job with plain loads and stores by the whole mover warp: nothing of it goes through
+// the SM's bulk-copy engine, which the operand loads of the main loop depend on.
+__device__ void ag_mover_lsu(const GemmParams& p, int cta, int nctas, uint32_t epoch, int lane) {
+  const int n = p.coll.nranks, r = p.coll.rank;
+  const size_t row_bytes = (size_t)p.K * 2;
+  const size_t unit_stride = (size_t)p.ag_unit_rows * row_bytes;
+  const int units = (p.rows_per_rank + p.ag_unit_rows - 1) / p.ag_unit_rows;
+  const size_t shard_off = (size_t)r * p.rows_per_rank * row_bytes;
+  for (int u = cta; u < units; u += nctas) {
+    const size_t nvec = unit_bytes(p, u) / 16;
+    const uint4* src = (const uint4*)((const char*)p.a_local + (size_t)u * unit_stride);
+    const size_t dst_off = shard_off + (size_t)u * unit_stride;
+    for (size_t i0 = 0; i0 < nvec; i0 += 256) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const size_t i = i0 + (size_t)j * 32 + lane;
+        if (i < nvec) v[j] = __ldg(src + i);
+      }
+      for (int q1 = p.copy_own ? 0 : 1; q1 < n; ++q1) {
+        uint4* dst = (uint4*)((char*)p.ag_buf[(r + q1) % n] + dst_off);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const size_t i = i0 + (size_t)j * 32 + lane;
+          if (i < nvec) dst[i] = v[j];
+        }
+      }
+    }
+    __threadfence_system();  // every lane: its stores of this unit are visible before the flags
+    __syncwarp();
+    if (lane < n && (lane != 0 || p.copy_own)) dev::st_release_sys(&p.fflags[(r + lane) % n]->ag_ready[r][u], epoch);
+  }
+}
+
 // ---- reduce phase of GEMM -> reduce-scatter: out = sum over source slots, fixed order.
 // Partials sit tile-major: [slot][row block][column block][32-column chunk][128 rows][32 cols],
 // which is what lets the epilogue ship each 8 KB chunk with one bulk store.
@@ -416,7 +450,8 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         }
       }
       go = __all_sync(0xffffffffu, go);
-      if (go && lane == 0) ag_mover(p, epi_stage, ctl, cta, nctas, epoch);
+      if (go && p.ag_mover == 1) ag_mover_lsu(p, cta, nctas, epoch, lane);
+      else if (go && lane == 0) ag_mover(p, epi_stage, ctl, cta, nctas, epoch);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (lane 0 issues;
@@ -432,14 +467,34 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         const int ur = p.ag_unit_rows;
         const int r0 = tl.m_in * TM, r1 = min(r0 + TM, p.rows_per_rank);
         const int u0 = r0 / ur, u1 = (r1 + ur - 1) / ur;
+        // Up to eight flags per lane, all loaded before any is looked at (one trip to L2 when the
+        // rows are already here, which is the common case); relaxed loads, one fence at the end.
+        const uint32_t* fl = &p.fflags[r]->ag_ready[tl.shard][0];
         bool mine = true;
-        for (int u = u0 + lane; u < u1 && mine; u += 32) {
-          if (*abort || !dev::wait_flag_ge(&p.fflags[r]->ag_ready[tl.shard][u], epoch, p.coll.timeout_ns)) {
-            dev::report_error(p.coll.status, kDevGemmTimeout, r, tl.shard, u, epoch);
-            *abort = 1;
-            mine = false;
+        for (int base = u0; base < u1 && mine; base += 256) {
+          unsigned long long t0 = 0;
+          for (;;) {
+            uint32_t v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int u = base + j * 32 + lane;
+              v[j] = u < u1 ? dev::ld_relaxed_sys(fl + u) : epoch;
+            }
+            bool all = true;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) all = all && (int32_t)(v[j] - epoch) >= 0;
+            if (all) break;
+            const unsigned long long now = dev::globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            if (*abort || now - t0 > p.coll.timeout_ns) {
+              dev::report_error(p.coll.status, kDevGemmTimeout, r, tl.shard, base + lane, epoch);
+              *abort = 1;
+              mine = false;
+              break;
+            }
           }
         }
+        __threadfence_system();  // the relaxed loads that saw the flags + this fence = acquire
         ok = __all_sync(0xffffffffu, mine);
         if (lane == 0) {
           __threadfence_system();  // what the other lanes acquired is ordered before this lane's reads
@@ -539,15 +594,15 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       if (p.mode == kGemmReduceScatter && fused) {
         // Partial tile -> the owner's slot number r.  Each 32-column chunk (128 rows x 64 bytes
         // = 8 KB, contiguous at the destination) is staged in shared memory and shipped with
-        // ONE bulk store over NVLink; two staging buffers alternate.
+        // ONE bulk store over NVLink; four staging buffers take turns.
         const bool issuer = warp == 2 && lane == 0;
         const size_t tile_elems = (size_t)BM * BN;
         __nv_bfloat16* dst_tile = (__nv_bfloat16*)p.rs_buf[tl.shard] +
                                   (((size_t)r * tiles_m + tl.m_in) * tiles_n + tl.n_blk) * tile_elems;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
-          char* sbuf = epi_stage + (c & 1) * EPI_CHUNK_BYTES;
-          if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // store c-2 has read sbuf
+          char* sbuf = epi_stage + (c & (SIDE_BUFS - 1)) * EPI_CHUNK_BYTES;
+          if (issuer) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");  // store c-4 has read sbuf
           asm volatile("bar.sync 1, 128;" ::: "memory");
           uint32_t v[32];
           tmem_ld_32x32(t_row + (uint32_t)(c * 32), v);

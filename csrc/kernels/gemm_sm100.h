@@ -48,6 +48,8 @@ struct GemmParams {
   int ldc;
   int rows_per_rank;        // M / nranks (M when nranks == 1)
   int ag_unit_rows;         // all-gather: rows of a shard announced by one ready flag (see gemm_ag_unit_rows)
+  int ag_mover;             // all-gather: how the mover warp copies: 0 = bulk async copies through shared memory
+                            // (one thread), 1 = plain 16-byte loads and stores by all 32 lanes
   int copy_own;             // all-gather: also place my own shard in the gathered buffer
   const void* a_local;      // all-gather: my shard, bf16 [rows_per_rank, K]
   void* ag_buf[kMaxRanks];  // all-gather: every rank's gathered-A buffer [M, K]; [rank] is mine

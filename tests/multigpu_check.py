@@ -7,7 +7,7 @@
 Checks, on real peer memory over NVLink: every collective against a PyTorch reference, the
 all-reduce variants (one-shot, two-shot, NVLS when the multicast object could be built),
 pause / resume cycles (memory really returned, results bit-identical), the fused
-tensor-parallel GEMMs and the MoE dispatch / combine.  Prints one JSON line per check from
+tensor-parallel GEMMs, the MoE dispatch / combine and a pipeline 1F1B step.  Prints one JSON line per check from
 rank 0 and exits non-zero on the first failure.  NCCL (torch) is only used to cross-check.
 """
 import json
@@ -247,6 +247,33 @@ def main():
     h0, h1 = train(False), train(True)
     norms = gather_cpu(torch.tensor([h[1] for h in h0]))
     report("fsdp tiny llama, pause between steps", h0 == h1 and all(torch.equal(norms[0], t) for t in norms), losses=[round(h[0], 4) for h in h0])
+
+    # ---- pipeline 1F1B over the library's send / recv (rendez-vous transfers: grouped exchanges)
+    from asystem_amem_b200.parallel import PipelineStage
+    torch.manual_seed(5)
+    layers = [torch.nn.Linear(64, 64) for _ in range(world)]      # same on every rank (same seed)
+    gp = torch.Generator().manual_seed(6)
+    n_mb = 2 * world + 1
+    mbs = [torch.randn(16, 64, generator=gp) for _ in range(n_mb)]
+    tgt = [torch.randn(16, 64, generator=gp) for _ in range(n_mb)]
+    mine = torch.nn.Linear(64, 64).cuda()
+    mine.load_state_dict(layers[rank].state_dict())
+    pipe = PipelineStage(comm, rank, world)
+    losses = pipe.run_1f1b(lambda t: torch.tanh(mine(t)), [m.cuda() for m in mbs], torch.empty(16, 64, device="cuda"),
+                           loss_fn=lambda y, i: ((y - tgt[i].cuda()) ** 2).mean())
+    torch.cuda.synchronize()
+    ref_losses = []
+    for xb, tb in zip(mbs, tgt):
+        hcur = xb
+        for layer in layers:
+            hcur = torch.tanh(layer(hcur))
+        lref = ((hcur - tb) ** 2).mean()
+        lref.backward()
+        ref_losses.append(float(lref))
+    ok = float((mine.weight.grad.cpu() - layers[rank].weight.grad).abs().max()) < 1e-4
+    if rank == world - 1:
+        ok = ok and all(abs(float(a) - b) < 1e-4 for a, b in zip(losses, ref_losses))
+    report("pipeline 1F1B gradients equal the single-process run", ok, micro_batches=n_mb)
 
     err = comm.async_error()
     report("no device-side errors", err == 0)

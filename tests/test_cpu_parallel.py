@@ -150,6 +150,47 @@ def test_pipeline_1f1b_matches_single_process_gradients():
     assert all(abs(a - b) < 1e-5 for a, b in zip(res[2][1], res[2][2])), res[2]
 
 
+def test_1f1b_plan_completes_under_rendezvous_semantics():
+    """On the GPU a send completes only while the neighbour runs the matching receive.  Simulate
+    that: every stage walks its plan in order, and a transfer step completes only when the
+    neighbour's current step is its exact mirror (same micro-batches, both directions of a grouped
+    exchange at once).  Every (stages, micro-batches) pair must run to the end."""
+    from asystem_amem_b200.parallel.pp import plan_1f1b
+
+    def ops(s, st):
+        k = st[0]
+        return {"recv_f": lambda: {("r", s - 1, "f", st[1])}, "send_f": lambda: {("s", s + 1, "f", st[1])},
+                "recv_b": lambda: {("r", s + 1, "b", st[1])}, "send_b": lambda: {("s", s - 1, "b", st[1])},
+                "send_f_recv_b": lambda: {("s", s + 1, "f", st[1]), ("r", s + 1, "b", st[2])},
+                "send_b_recv_f": lambda: {("s", s - 1, "b", st[1]), ("r", s - 1, "f", st[2])}}[k]()
+
+    for n in range(1, 7):
+        for m in range(1, 13):
+            plans = [[st for st in plan_1f1b(s, n, m) if st[0] not in ("fwd", "bwd")] for s in range(n)]
+            for s in range(n):   # every micro-batch runs forward and backward exactly once, forward first
+                order = [st for st in plan_1f1b(s, n, m) if st[0] in ("fwd", "bwd")]
+                assert sorted(st[1] for st in order if st[0] == "fwd") == list(range(m))
+                assert [st[1] for st in order if st[0] == "bwd"] == list(range(m))
+                assert all(order.index(("fwd", i)) < order.index(("bwd", i)) for i in range(m))
+            pos = [0] * n
+            moved = True
+            while moved:
+                moved = False
+                for s in range(n):
+                    if pos[s] >= len(plans[s]):
+                        continue
+                    mine = ops(s, plans[s][pos[s]])
+                    (q,) = {o[1] for o in mine}
+                    if pos[q] >= len(plans[q]):
+                        continue
+                    mirror = {("r" if d == "s" else "s", s, t, i) for (d, _, t, i) in mine}
+                    if mirror == ops(q, plans[q][pos[q]]):
+                        pos[s] += 1
+                        pos[q] += 1
+                        moved = True
+            assert all(pos[s] == len(plans[s]) for s in range(n)), (n, m, pos)
+
+
 def _context_parallel(rank, world, uid, causal):
     import torch
     from asystem_amem_b200 import Communicator

@@ -58,9 +58,18 @@ def test_gemm_split_k_tail(M, N, K, tile_height):
         assert torch.equal(out, outs[0])
 
 
+@pytest.fixture(params=["0", "1"], ids=["bulk_mover", "lsu_mover"])
+def mover(request):
+    """The two ways the all-gather mover warp copies (read by the library at every call)."""
+    import os
+    os.environ["AMEM_AG_MOVER"] = request.param
+    yield request.param
+    os.environ.pop("AMEM_AG_MOVER", None)
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("m_local,N,K", [(128, 256, 256), (200, 520, 328), (512, 1024, 1024), (300, 264, 4096)])
-def test_all_gather_gemm(world, m_local, N, K, tile_height):
+def test_all_gather_gemm(world, m_local, N, K, tile_height, mover):
     """Both tile heights; shards whose row count is no multiple of the tile height or of the rows
     one ready flag covers (a flag covers 16 rows at K = 256, 13 at K = 328, one at K = 4096)."""
     from asystem_amem_b200.ops import all_gather_gemm
