@@ -293,7 +293,8 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
   g.p.rows_per_rank = rpr;
   g.p.a_local = a_shard;
   g.p.ag_unit_rows = gemm_ag_unit_rows(rpr, K);
-  g.p.ag_mover = (int)env_long("AMEM_AG_MOVER", 0);
+  if (long ur = env_long("AMEM_AG_UNIT_ROWS", 0); ur > g.p.ag_unit_rows) g.p.ag_unit_rows = (int)std::min<long>(ur, rpr);   // coarser flags (never finer than the minimum)
+  g.p.ag_mover = (int)env_long("AMEM_AG_MOVER", 1);
   // Every CTA computes (one extra warp of each moves data), so the tiling is planned like the plain
   // GEMM's: tile height, tile width and the split of the last wave along K.  The emulation runs all
   // ranks in one grid on one stream: they would share the split workspace, so it runs unsplit.
@@ -323,6 +324,7 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
     Segment* seg = nullptr;
     if ((s = c->fused_segment(0, (size_t)M * K * 2, &seg)) != kSuccess) return R(s);
     for (int r = 0; r < n; ++r) g.p.ag_buf[r] = (void*)seg->va[r];
+    g.p.ag_mc = (K % 8 == 0) ? (void*)seg->mc_va : nullptr;
     if ((s = make_tensor_map_bf16(&g.map_a, g.p.ag_buf[c->rank()], M, K, K, tile_rows)) != kSuccess) return R(s);
     if ((s = make_tensor_map_bf16(&g.map_a_local, a_shard, rpr, K, K, tile_rows)) != kSuccess) return R(s);
   }

@@ -224,6 +224,13 @@ Status Comm::fused_segment(int which, size_t bytes, Segment** out) {
   }
   AMEM_TRY(sym_alloc(bytes, kScratch, kTagSymm, &s));
   if (nranks_ > 1) AMEM_TRY(mesh_->barrier());
+  // The gathered-A buffer of the all-gather -> GEMM kernel also gets a multicast mapping where the
+  // communicator has one for its staging: a row then crosses this GPU's links once (one
+  // multimem.st, replicated by the switch) instead of once per peer.  Every rank decides the same
+  // way (setup_multicast agrees collectively); without it the kernel stores to each peer.
+  if (which == 0 && nranks_ > 2 && stage_.mc_va && env_long("AMEM_AG_MC", 1)) {
+    if (setup_multicast(&s, s.va[rank_]) != kSuccess) LOGI("all-gather buffer: no multicast mapping, using per-peer stores");
+  }
   *out = &s;
   return kSuccess;
 }

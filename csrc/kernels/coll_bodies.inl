@@ -532,7 +532,9 @@ AMEM_BODY void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
-  run_chunks(a, p, nch, 8,
+  // The root only pushes and the others only drain: give nearly all warps of a block to the job
+  // this rank has (the other group just passes the credits on).
+  run_chunks(a, p, nch, r == a.root ? 15 : 1,
     [&](uint32_t t, Lane ln) {
       if (r != a.root) return;
       size_t off = (size_t)t * cb;

@@ -65,6 +65,8 @@ struct __align__(8) SmemCtl {
   uint32_t tmem_base;
   int abort;
   int s_abort_coll;
+  int mover_go;     // all-gather: the cross-launch guard has passed, peers may be written
+  int next_unit;    // all-gather: next unit (in this CTA's sequence) a mover warp takes
 };
 
 struct Tile {
@@ -276,15 +278,22 @@ __device__ void ag_mover(const GemmParams& p, char* bufs, SmemCtl* ctl, int cta,
   bulk_wait_all();  // nothing of this CTA's shared memory is still being read when it exits
 }
 
-// The same job with plain loads and stores by the whole mover warp: nothing of it goes through
-// the SM's bulk-copy engine, which the operand loads of the main loop depend on.
-__device__ void ag_mover_lsu(const GemmParams& p, int cta, int nctas, uint32_t epoch, int lane) {
+// The same job with plain loads and stores by whole warps (several per CTA, so that enough bytes are
+// in flight to cover the link's latency): nothing of it goes through the SM's bulk-copy engine,
+// which the operand loads of the main loop depend on.
+__device__ void ag_mover_lsu(const GemmParams& p, SmemCtl* ctl, int cta, int nctas, uint32_t epoch, int lane) {
   const int n = p.coll.nranks, r = p.coll.rank;
   const size_t row_bytes = (size_t)p.K * 2;
   const size_t unit_stride = (size_t)p.ag_unit_rows * row_bytes;
   const int units = (p.rows_per_rank + p.ag_unit_rows - 1) / p.ag_unit_rows;
   const size_t shard_off = (size_t)r * p.rows_per_rank * row_bytes;
-  for (int u = cta; u < units; u += nctas) {
+  // the CTA's mover warps share its sequence of units (cta, cta + nctas, ...): each takes the next one
+  for (;;) {
+    int k = 0;
+    if (lane == 0) k = atomicAdd(&ctl->next_unit, 1);
+    k = __shfl_sync(0xffffffffu, k, 0);
+    const int u = cta + k * nctas;
+    if (u >= units) break;
     const size_t nvec = unit_bytes(p, u) / 16;
     const uint4* src = (const uint4*)((const char*)p.a_local + (size_t)u * unit_stride);
     const size_t dst_off = shard_off + (size_t)u * unit_stride;
@@ -295,12 +304,23 @@ __device__ void ag_mover_lsu(const GemmParams& p, int cta, int nctas, uint32_t e
         const size_t i = i0 + (size_t)j * 32 + lane;
         if (i < nvec) v[j] = __ldg(src + i);
       }
-      for (int q1 = p.copy_own ? 0 : 1; q1 < n; ++q1) {
-        uint4* dst = (uint4*)((char*)p.ag_buf[(r + q1) % n] + dst_off);
+      if (p.ag_mc) {
+        // one store per 16 bytes, replicated into every rank's gathered buffer by the switch
+        char* dst = (char*)p.ag_mc + dst_off;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const size_t i = i0 + (size_t)j * 32 + lane;
-          if (i < nvec) dst[i] = v[j];
+          if (i < nvec)
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + i * 16), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
+        }
+      } else {
+        for (int q1 = p.copy_own ? 0 : 1; q1 < n; ++q1) {
+          uint4* dst = (uint4*)((char*)p.ag_buf[(r + q1) % n] + dst_off);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const size_t i = i0 + (size_t)j * 32 + lane;
+            if (i < nvec) dst[i] = v[j];
+          }
         }
       }
     }
@@ -393,6 +413,8 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
       mbar_init(&ctl->tempty[b], 4 * MT);  // one arrival per epilogue warp
     }
     ctl->abort = 0;
+    ctl->mover_go = 0;
+    ctl->next_unit = 0;
     mbar_fence_init();
     tma_prefetch_desc(map_a);
     tma_prefetch_desc(map_b);
@@ -414,7 +436,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   // mode only the mover warp writes to peers: it alone exchanges the flags (mover_barrier below,
   // same flag words and epoch as block_barrier) and the compute warps start at once.
   const bool ag = p.mode == kGemmAllGather && fused;
-  constexpr int MOVER_WARP = 2 + 4 * MT;
+  constexpr int MOVER_WARP = 2 + 4 * MT;   // the first mover warp; the warps behind it are movers too
   if (fused && p.mode == kGemmReduceScatter) dev::block_barrier(proto);
   if (ag) proto.epoch += 1;
 
@@ -435,23 +457,37 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
   const int S = ((p.mode == kGemmPlain || p.mode == kGemmAllGather) && p.sk_slices > 1 && p.sk_ws && p.sk_ctr) ? p.sk_slices : 1;
   const int n_items = work_count(g, G, total_tiles, S);
 
-  if (warp == MOVER_WARP) {
-    // ------------------------------------------------------------ all-gather mover
+  if (warp >= MOVER_WARP) {
+    // ------------------------------------------------------------ all-gather movers
     if (ag) {
-      // the cross-launch guard, by this warp alone: lane t talks to rank t
       bool go = true;
-      if (lane < n && lane != r) {
-        __threadfence_system();
-        dev::st_release_sys(&p.coll.ctrl[lane]->flags[cta][r], proto.epoch);
-        if (!dev::wait_flag_ge(&proto.me->flags[cta][lane], proto.epoch, p.coll.timeout_ns)) {
-          dev::report_error(p.coll.status, kDevBarrierTimeout, r, lane, cta, proto.epoch);
-          *abort = 1;
-          go = false;
+      if (warp == MOVER_WARP) {
+        // the cross-launch guard, by this warp alone: lane t talks to rank t
+        if (lane < n && lane != r) {
+          __threadfence_system();
+          dev::st_release_sys(&p.coll.ctrl[lane]->flags[cta][r], proto.epoch);
+          if (!dev::wait_flag_ge(&proto.me->flags[cta][lane], proto.epoch, p.coll.timeout_ns)) {
+            dev::report_error(p.coll.status, kDevBarrierTimeout, r, lane, cta, proto.epoch);
+            *abort = 1;
+            go = false;
+          }
         }
+        go = __all_sync(0xffffffffu, go);
+        if (lane == 0) {
+          *(volatile int*)&ctl->mover_go = go ? 1 : -1;
+          __threadfence_block();
+        }
+      } else {
+        // the other mover warps start when the first one has passed the guard
+        const unsigned long long t0 = dev::globaltimer_ns();
+        int st = 0;
+        while ((st = *(volatile int*)&ctl->mover_go) == 0 && !*abort && dev::globaltimer_ns() - t0 < p.coll.timeout_ns) {
+        }
+        go = st == 1;
       }
-      go = __all_sync(0xffffffffu, go);
-      if (go && p.ag_mover == 1) ag_mover_lsu(p, cta, nctas, epoch, lane);
-      else if (go && lane == 0) ag_mover(p, epi_stage, ctl, cta, nctas, epoch);
+      const bool by_warps = p.ag_mover == 1 || p.ag_mc;
+      if (go && by_warps) ag_mover_lsu(p, ctl, cta, nctas, epoch, lane);
+      else if (go && warp == MOVER_WARP && lane == 0) ag_mover(p, epi_stage, ctl, cta, nctas, epoch);
     }
   } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (lane 0 issues;
@@ -820,7 +856,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
 }
 
 template <int MT>
-__global__ void __launch_bounds__(96 + 128 * MT, 1)  // TMA warp, MMA warp, 4 * MT epilogue warps, mover warp
+__global__ void __launch_bounds__(MT == 2 ? kGemmThreadsTall : kGemmThreads, 1)  // TMA warp, MMA warp, 4 * MT epilogue warps, mover warps
 gemm_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap map_a,
             const __grid_constant__ CUtensorMap map_a_local, const __grid_constant__ CUtensorMap map_b) {
   extern __shared__ char smem_raw[];
@@ -831,7 +867,7 @@ struct EmuGemmParams {
   GemmLaunch rank[kMaxRanks];
 };
 template <int MT>
-__global__ void __launch_bounds__(96 + 128 * MT, 1) gemm_kernel_emu(const __grid_constant__ EmuGemmParams all) {
+__global__ void __launch_bounds__(MT == 2 ? kGemmThreadsTall : kGemmThreads, 1) gemm_kernel_emu(const __grid_constant__ EmuGemmParams all) {
   extern __shared__ char smem_raw[];
   const GemmLaunch& g = all.rank[blockIdx.y];
   gemm_body<MT>(g.p, &g.map_a, &g.map_a_local, &g.map_b, blockIdx.x, gridDim.x, smem_raw);

@@ -12,8 +12,8 @@
 namespace amem {
 
 static const int kGemmBM = 128, kGemmBN = 256, kGemmBK = 64, kGemmStages = 4;
-static const int kGemmThreads = 224;       // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warp 6: all-gather mover
-static const int kGemmThreadsTall = 352;   // 256-row tiles: eight epilogue warps (2-9), mover warp 10
+static const int kGemmThreads = 320;       // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue, warps 6-9: all-gather movers
+static const int kGemmThreadsTall = 384;   // 256-row tiles: eight epilogue warps (2-9), mover warps 10-11
 static const int kMaxUnits = 256;          // reduce-scatter: row blocks (of 128 rows) per rank
 static const int kMaxAgUnits = 1024;       // all-gather: ready flags per source rank (a flag covers GemmParams::ag_unit_rows rows)
 static const int kAgPieceBytes = 8192;     // all-gather: bytes per bulk copy of the mover
@@ -49,7 +49,9 @@ struct GemmParams {
   int rows_per_rank;        // M / nranks (M when nranks == 1)
   int ag_unit_rows;         // all-gather: rows of a shard announced by one ready flag (see gemm_ag_unit_rows)
   int ag_mover;             // all-gather: how the mover warp copies: 0 = bulk async copies through shared memory
-                            // (one thread), 1 = plain 16-byte loads and stores by all 32 lanes
+                            // (one thread), 1 = plain 16-byte loads and stores by all 32 lanes; with ag_mc set,
+                            // the stores are multimem.st into the multicast mapping (one per 16 bytes for all peers)
+  void* ag_mc;              // all-gather: multicast mapping of the gathered buffers (null: none)
   int copy_own;             // all-gather: also place my own shard in the gathered buffer
   const void* a_local;      // all-gather: my shard, bf16 [rows_per_rank, K]
   void* ag_buf[kMaxRanks];  // all-gather: every rank's gathered-A buffer [M, K]; [rank] is mine
