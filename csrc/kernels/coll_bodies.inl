@@ -102,13 +102,14 @@ AMEM_BODY void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
+  const size_t fb = nch == 1 ? B : cb;   // what the blocks split: the whole message, or a full chunk (block_range_clip)
   run_chunks(a, p, nch, 8,
     [&](uint32_t t, Lane ln) {
       size_t off = (size_t)t * cb;
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fb, len, p.block, p.nblocks, &lo, &hi);
       char* mc = (a.algo == kAlgoNvls && a.mc_stage) ? a.mc_stage + qoff + (size_t)r * slot + lo : nullptr;
       if (mc_copy_ok(mc, send + off + lo, hi - lo)) {
         // NVLS all-gather: one multicast store lands my piece in every rank's staging slot
@@ -126,7 +127,7 @@ AMEM_BODY void body_allgather(const CollArgs& a, Proto& p, size_t chunk_elems) {
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fb, len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
         copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ln);
@@ -146,13 +147,14 @@ AMEM_BODY void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
+  const size_t fb = nch == 1 ? B : cb;   // what the blocks split: the whole message, or a full chunk (block_range_clip)
   run_chunks(a, p, nch, 8,
     [&](uint32_t t, Lane ln) {
       size_t off = (size_t)t * cb;
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fb, len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
         copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + (size_t)q * B + off + lo, hi - lo, ln);
@@ -164,7 +166,7 @@ AMEM_BODY void body_alltoall(const CollArgs& a, Proto& p, size_t chunk_elems) {
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fb, len, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
         copy_span(recv + (size_t)q * B + off + lo, a.stage[r] + qoff + (size_t)q * slot + lo, hi - lo, ln);
@@ -256,6 +258,7 @@ AMEM_BODY void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elem
   const char* send = (const char*)a.send;
   TO* recv = (TO*)a.recv;
   const uint32_t nch = (uint32_t)((R + ce - 1) / ce);
+  const size_t fe = nch == 1 ? R : ce;   // what the blocks split: the whole message, or a full chunk (block_range_clip)
   // the reduce side reads n slots per output: it gets more warps than the push side
   run_chunks(a, p, nch, 6,
     [&](uint32_t t, Lane ln) {
@@ -263,7 +266,7 @@ AMEM_BODY void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elem
       size_t len = R - off < ce ? R - off : ce;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len * es, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fe * es, len * es, p.block, p.nblocks, &lo, &hi);
       for (int k = 1; k < n; ++k) {
         int q = peer_at(r, n, k, p.block);
         copy_span(a.stage[q] + qoff + (size_t)r * slot + lo, send + ((size_t)q * R + off) * es + lo, hi - lo, ln);
@@ -274,7 +277,7 @@ AMEM_BODY void body_reducescatter(const CollArgs& a, Proto& p, size_t chunk_elem
       size_t len = R - off < ce ? R - off : ce;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len * es, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fe * es, len * es, p.block, p.nblocks, &lo, &hi);
       const TI* slots[kMaxRanks];
       for (int s2 = 0; s2 < n; ++s2)
         slots[s2] = (s2 == r) ? (const TI*)(send + ((size_t)r * R + off) * es + lo)
@@ -436,12 +439,15 @@ AMEM_BODY void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, siz
   char* recv = (char*)a.recv;
   auto xbase = [&](uint32_t t) { return hoff + (size_t)(t & 1u) * (Q / 2); };
   auto ybase = [&](uint32_t t) { return hoff + Q + (size_t)(t & 1u) * (Q / 2); };
+  // Slices and block ranges are those of a FULL chunk in every chunk (a short last chunk just fills
+  // fewer of them): block b then touches the same bytes of X and Y each time, which is what lets
+  // per-block credits order the reuse of a buffer two chunks later (see block_range_clip).
+  const size_t sl_full = ((ce + n - 1) / n + vi - 1) / vi * vi;
   auto slice = [&](uint32_t t, int owner, size_t* off, size_t* b0, size_t* b1) {
     *off = (size_t)t * ce;
     size_t len = N - *off < ce ? N - *off : ce;
-    size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
-    *b0 = (size_t)owner * sl;
-    *b1 = *b0 + sl;
+    *b0 = (size_t)owner * sl_full;
+    *b1 = *b0 + sl_full;
     if (*b0 > len) *b0 = len;
     if (*b1 > len) *b1 = len;
   };
@@ -450,14 +456,14 @@ AMEM_BODY void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, siz
       int q = peer_at(r, n, k, p.block);
       size_t off, b0, b1, lo, hi;
       slice(t, q, &off, &b0, &b1);
-      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(sl_full * es, (b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
       copy_span(a.stage[q] + xbase(t) + (size_t)r * slot + lo, send + (off + b0) * es + lo, hi - lo, ln);
     }
   };
   auto reduce = [&](uint32_t t, Lane ln) {
     size_t off, b0, b1, lo, hi;
     slice(t, r, &off, &b0, &b1);
-    block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+    block_range_clip(sl_full * es, (b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
     const TI* slots[kMaxRanks];
     for (int s2 = 0; s2 < n; ++s2)
       slots[s2] = (s2 == r) ? (const TI*)(send + (off + b0) * es + lo) : (const TI*)(a.stage[r] + xbase(t) + (size_t)s2 * slot + lo);
@@ -475,7 +481,7 @@ AMEM_BODY void body_allreduce_twoshot_pipelined(const CollArgs& a, Proto& p, siz
       int q = peer_at(r, n, k, p.block);
       size_t off, b0, b1, lo, hi;
       slice(t, q, &off, &b0, &b1);
-      block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(sl_full * es, (b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
       copy_span(recv + (off + b0) * es + lo, a.stage[r] + ybase(t) + (size_t)q * slot + lo, hi - lo, ln);
     }
   };
@@ -532,6 +538,7 @@ AMEM_BODY void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   const uint32_t nch = (uint32_t)((B + cb - 1) / cb);
+  const size_t fb = nch == 1 ? B : cb;   // what the blocks split: the whole message, or a full chunk (block_range_clip)
   // The root only pushes and the others only drain: give nearly all warps of a block to the job
   // this rank has (the other group just passes the credits on).
   run_chunks(a, p, nch, r == a.root ? 15 : 1,
@@ -541,7 +548,7 @@ AMEM_BODY void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fb, len, p.block, p.nblocks, &lo, &hi);
       char* mc = (n > 2 && a.mc_stage) ? a.mc_stage + qoff + lo : nullptr;
       if (mc_copy_ok(mc, send + off + lo, hi - lo)) {
         copy_span_mc(mc, send + off + lo, hi - lo, ln);
@@ -559,7 +566,7 @@ AMEM_BODY void body_broadcast(const CollArgs& a, Proto& p, size_t chunk_elems) {
       size_t len = B - off < cb ? B - off : cb;
       size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, t);
       size_t lo, hi;
-      block_range(len, p.block, p.nblocks, &lo, &hi);
+      block_range_clip(fb, len, p.block, p.nblocks, &lo, &hi);
       copy_span(recv + off + lo, a.stage[r] + qoff + lo, hi - lo, ln);
     });
 }
@@ -574,12 +581,13 @@ AMEM_BODY void body_reduce(const CollArgs& a, Proto& p, size_t chunk_elems) {
   size_t ce = chunk_elems;
   if (ce * es > slot) ce = slot / es;
   const char* send = (const char*)a.send;
+  const size_t fe = N <= ce ? N : ce;   // what the blocks split: the whole message, or a full chunk (block_range_clip)
   uint32_t c = 0;
   for (size_t off = 0; off < N; off += ce, ++c) {
     size_t len = N - off < ce ? N - off : ce;
     size_t qoff = quarter_offset(a.stage_bytes, a.p2p_slot_bytes, p.opseq, c);
     size_t lo, hi;
-    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    block_range_clip(fe * es, len * es, p.block, p.nblocks, &lo, &hi);
     if (r != a.root) copy_span(a.stage[a.root] + qoff + (size_t)r * slot + lo, send + off * es + lo, hi - lo, full_lane());
     block_barrier(p);
     if (r == a.root) {

@@ -187,6 +187,18 @@ __device__ __forceinline__ void block_range(size_t total_bytes, int block, int n
   *hi = h;
 }
 
+// The same split for a piece of `avail_bytes` of a chunked message whose full chunks have
+// `full_bytes`: the ranges are those of a FULL chunk, cut off at what this chunk really has.
+// Block b then touches the same staging bytes in every chunk, so the per-block barriers and
+// credits (which order block b of one rank only against block b of the others) also cover a
+// short last chunk; splitting `avail_bytes` itself would move the ranges and let block b of one
+// rank write what block b' of another is still reading from two chunks earlier.
+__device__ __forceinline__ void block_range_clip(size_t full_bytes, size_t avail_bytes, int block, int nblocks, size_t* lo, size_t* hi) {
+  block_range(full_bytes, block, nblocks, lo, hi);
+  if (*lo > avail_bytes) *lo = avail_bytes;
+  if (*hi > avail_bytes) *hi = avail_bytes;
+}
+
 // A lane is the slice of a block's threads that executes one loop: the whole block, or the
 // "push" / "drain" group of warps when a collective overlaps its two phases.
 struct Lane {

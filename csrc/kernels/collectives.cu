@@ -81,15 +81,17 @@ __device__ __forceinline__ void multimem_st(void* p, uint4 v) {
 // Three staging regions rotate; region N % 3 is restaged only after chunk N-3 was copied out,
 // which (program order of the copy group) is also after everybody's reduce of it.
 template <typename T, int U>
-__device__ __forceinline__ void nvls_reduce_slice(const CollArgs& a, Proto& p, char* region_mc, size_t len, Lane lr) {
+__device__ __forceinline__ void nvls_reduce_slice(const CollArgs& a, Proto& p, char* region_mc, size_t len, size_t full, Lane lr) {
   const int n = a.nranks, r = a.rank;
   const size_t es = sizeof(T), vi = 16 / es;
-  size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+  // slices and block ranges of a FULL chunk (`full` elements), cut off at `len`: block b touches the
+  // same bytes of a region in every chunk (see block_range_clip)
+  size_t sl = ((full + n - 1) / n + vi - 1) / vi * vi;
   size_t b0 = (size_t)r * sl, b1 = b0 + sl;
   if (b0 > len) b0 = len;
   if (b1 > len) b1 = len;
   size_t slo, shi;
-  block_range((b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
+  block_range_clip(sl * es, (b1 - b0) * es, p.block, p.nblocks, &slo, &shi);
   // the staging tail beyond `len` holds stale but mapped bytes: whole vectors are safe
   size_t nvec = (shi - slo + 15) / 16;
   char* base = region_mc + b0 * es + slo;
@@ -120,10 +122,10 @@ __device__ __forceinline__ void nvls_reduce_slice(const CollArgs& a, Proto& p, c
 // rank's slice.  Then block b of a reducer depends on block b of every rank and on nothing else,
 // which is what the per-block barriers and credits promise.
 template <typename T>
-__device__ __forceinline__ void nvls_copy_sliced(char* dst, const char* src, size_t len, const CollArgs& a, const Proto& p, Lane ln) {
+__device__ __forceinline__ void nvls_copy_sliced(char* dst, const char* src, size_t len, size_t full, const CollArgs& a, const Proto& p, Lane ln) {
   const int n = a.nranks;
   const size_t es = sizeof(T), vi = 16 / es;
-  const size_t sl = ((len + n - 1) / n + vi - 1) / vi * vi;
+  const size_t sl = ((full + n - 1) / n + vi - 1) / vi * vi;   // slice length of a full chunk, whatever this chunk's length
   int nfull = sl ? (int)(len / sl) : 0;
   if (nfull > n) nfull = n;
   size_t lo, hi;
@@ -149,7 +151,7 @@ __device__ __forceinline__ void nvls_copy_sliced(char* dst, const char* src, siz
     size_t b0 = (size_t)q * sl, b1 = b0 + sl;
     if (b0 > len) b0 = len;
     if (b1 > len) b1 = len;
-    block_range((b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
+    block_range_clip(sl * es, (b1 - b0) * es, p.block, p.nblocks, &lo, &hi);
     copy_span(dst + b0 * es + lo, src + b0 * es + lo, hi - lo, ln);
   }
 }
@@ -167,23 +169,24 @@ __device__ __forceinline__ void body_allreduce_nvls(const CollArgs& a, Proto& p,
   ce = ce / (vi * n) * (vi * n);
   if (ce == 0) ce = vi * n;
   const uint32_t nch = (uint32_t)((N + ce - 1) / ce);
+  const size_t fe = nch == 1 ? N : ce;   // slices and block ranges: of the whole message, or of a full chunk
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
   auto stage_in = [&](uint32_t t, Lane ln) {
     size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
-    nvls_copy_sliced<T>(a.stage[r] + hoff + (t % 3) * region, send + off * es, len, a, p, ln);
+    nvls_copy_sliced<T>(a.stage[r] + hoff + (t % 3) * region, send + off * es, len, fe, a, p, ln);
   };
   auto stage_out = [&](uint32_t t, Lane ln) {
     size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
-    nvls_copy_sliced<T>(recv + off * es, a.stage[r] + hoff + (t % 3) * region, len, a, p, ln);
+    nvls_copy_sliced<T>(recv + off * es, a.stage[r] + hoff + (t % 3) * region, len, fe, a, p, ln);
   };
   auto reduce = [&](uint32_t t, Lane ln) {
     size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
-    nvls_reduce_slice<T, 8>(a, p, a.mc_stage + hoff + (t % 3) * region, len, ln);
+    nvls_reduce_slice<T, 8>(a, p, a.mc_stage + hoff + (t % 3) * region, len, fe, ln);
   };
   auto reduce_deep = [&](uint32_t t, Lane ln) {  // few warps: twice the loads in flight each
     size_t off = (size_t)t * ce, len = N - off < ce ? N - off : ce;
-    nvls_reduce_slice<T, 16>(a, p, a.mc_stage + hoff + (t % 3) * region, len, ln);
+    nvls_reduce_slice<T, 16>(a, p, a.mc_stage + hoff + (t % 3) * region, len, fe, ln);
   };
   if (nch == 1) {
     stage_in(0, full_lane());
@@ -326,10 +329,11 @@ __device__ __forceinline__ void body_reduce_nvls(const CollArgs& a, Proto& p, si
   if (ce == 0) ce = vi;
   const char* send = (const char*)a.send;
   char* recv = (char*)a.recv;
+  const size_t fe = N <= ce ? N : ce;   // what the blocks split: the whole message, or a full chunk (block_range_clip)
   for (size_t off = 0; off < N; off += ce) {
     const size_t len = N - off < ce ? N - off : ce;
     size_t lo, hi;
-    block_range(len * es, p.block, p.nblocks, &lo, &hi);
+    block_range_clip(fe * es, len * es, p.block, p.nblocks, &lo, &hi);
     copy_span(a.stage[r] + hoff + lo, send + off * es + lo, hi - lo, full_lane());
     block_barrier(p);   // everybody's chunk is staged
     if (r == a.root) {

@@ -117,6 +117,11 @@ inline void block_range(size_t total_bytes, int block, int nblocks, size_t* lo, 
   *lo = l;
   *hi = h;
 }
+inline void block_range_clip(size_t full_bytes, size_t avail_bytes, int block, int nblocks, size_t* lo, size_t* hi) {
+  block_range(full_bytes, block, nblocks, lo, hi);
+  if (*lo > avail_bytes) *lo = avail_bytes;
+  if (*hi > avail_bytes) *hi = avail_bytes;
+}
 
 struct Lane {
   int tid, nt;

@@ -106,6 +106,37 @@ def main():
     torch.cuda.synchronize()
     report("sendrecv ring 16MiB", bool((rcv == float((rank - 1) % world)).all()))
 
+    # ---- messages of several chunks whose last chunk is short (device-generated integers: sums are exact)
+    nb = 18_000_004                                   # 68.7 MiB of fp32 per rank: several chunks, an odd tail
+    base = torch.arange(nb, device="cuda", dtype=torch.float32) % 1021
+    mine_big = base + rank
+    out_big = torch.empty(world * nb, device="cuda")
+    comm.all_gather(mine_big, out_big)
+    torch.cuda.synchronize()
+    report("allgather, 69 MiB per rank", all(torch.equal(out_big[j * nb:(j + 1) * nb], base + j) for j in range(world)))
+    send_big = torch.cat([base + rank + 3 * j for j in range(world)])
+    comm.reduce_scatter(send_big, out_big[:nb])
+    torch.cuda.synchronize()
+    report("reducescatter, 69 MiB per rank", torch.equal(out_big[:nb], world * base + sum(range(world)) + 3 * rank * world))
+    comm.all_to_all(send_big, out_big)
+    torch.cuda.synchronize()
+    report("alltoall, 69 MiB per peer", all(torch.equal(out_big[j * nb:(j + 1) * nb], base + j + 3 * rank) for j in range(world)))
+    big = mine_big.repeat(3)[: 3 * nb - 5].contiguous()     # 206 MiB
+    ref_big = (base * world + sum(range(world))).repeat(3)[: 3 * nb - 5]
+    for algo in ("twoshot", "nvls") if info["nvls"] else ("twoshot",):
+        for rep in range(3):
+            yb = big.clone()
+            comm.all_reduce(yb, algo=algo)
+            torch.cuda.synchronize()
+            report(f"allreduce 206 MiB fp32 {algo} #{rep}", torch.equal(yb, ref_big))
+    bb = big.clone() if rank == 1 % world else torch.zeros_like(big)
+    comm.broadcast(bb, root=1 % world)
+    torch.cuda.synchronize()
+    src_big = ((base + 1 % world).repeat(3))[: 3 * nb - 5]
+    report("broadcast 206 MiB", torch.equal(bb, src_big))
+    del out_big, send_big, big, ref_big, bb, src_big, mine_big, base
+    torch.cuda.empty_cache()
+
     # ---- pause / resume: memory returns, same results afterwards, no re-init
     y0 = x.clone()
     comm.all_reduce(y0)
