@@ -486,7 +486,7 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         go = st == 1;
       }
       const bool by_warps = p.ag_mover == 1 || p.ag_mc;
-      if (go && by_warps) ag_mover_lsu(p, ctl, cta, nctas, epoch, lane);
+      if (go && by_warps && warp - MOVER_WARP < p.ag_mover_warps) ag_mover_lsu(p, ctl, cta, nctas, epoch, lane);
       else if (go && warp == MOVER_WARP && lane == 0) ag_mover(p, epi_stage, ctl, cta, nctas, epoch);
     }
   } else if (warp == 0) {
