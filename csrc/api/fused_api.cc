@@ -296,6 +296,7 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
   if (long ur = env_long("AMEM_AG_UNIT_ROWS", 0); ur > g.p.ag_unit_rows) g.p.ag_unit_rows = (int)std::min<long>(ur, rpr);   // coarser flags (never finer than the minimum)
   g.p.ag_mover = (int)env_long("AMEM_AG_MOVER", 1);
   g.p.ag_mover_warps = (int)std::max<long>(1, env_long("AMEM_AG_MOVER_WARPS", 2));
+  g.p.ag_epi_help = (int)env_long("AMEM_AG_EPI_HELP", 0);
   // Every CTA computes (one extra warp of each moves data), so the tiling is planned like the plain
   // GEMM's: tile height, tile width and the split of the last wave along K.  The emulation runs all
   // ranks in one grid on one stream: they would share the split workspace, so it runs unsplit.

@@ -278,55 +278,68 @@ __device__ void ag_mover(const GemmParams& p, char* bufs, SmemCtl* ctl, int cta,
   bulk_wait_all();  // nothing of this CTA's shared memory is still being read when it exits
 }
 
-// The same job with plain loads and stores by whole warps (several per CTA, so that enough bytes are
-// in flight to cover the link's latency): nothing of it goes through the SM's bulk-copy engine,
-// which the operand loads of the main loop depend on.
-__device__ void ag_mover_lsu(const GemmParams& p, SmemCtl* ctl, int cta, int nctas, uint32_t epoch, int lane) {
+// One unit of the shard (p.ag_unit_rows rows) to every peer, by one warp; nothing is fenced or
+// announced yet.
+__device__ __forceinline__ void ag_copy_unit(const GemmParams& p, int u, int lane) {
   const int n = p.coll.nranks, r = p.coll.rank;
   const size_t row_bytes = (size_t)p.K * 2;
   const size_t unit_stride = (size_t)p.ag_unit_rows * row_bytes;
-  const int units = (p.rows_per_rank + p.ag_unit_rows - 1) / p.ag_unit_rows;
   const size_t shard_off = (size_t)r * p.rows_per_rank * row_bytes;
-  // the CTA's mover warps share its sequence of units (cta, cta + nctas, ...): each takes the next one
-  for (;;) {
-    int k = 0;
-    if (lane == 0) k = atomicAdd(&ctl->next_unit, 1);
-    k = __shfl_sync(0xffffffffu, k, 0);
-    const int u = cta + k * nctas;
-    if (u >= units) break;
-    const size_t nvec = unit_bytes(p, u) / 16;
-    const uint4* src = (const uint4*)((const char*)p.a_local + (size_t)u * unit_stride);
-    const size_t dst_off = shard_off + (size_t)u * unit_stride;
-    for (size_t i0 = 0; i0 < nvec; i0 += 256) {
-      uint4 v[8];
+  const size_t nvec = unit_bytes(p, u) / 16;
+  const uint4* src = (const uint4*)((const char*)p.a_local + (size_t)u * unit_stride);
+  const size_t dst_off = shard_off + (size_t)u * unit_stride;
+  for (size_t i0 = 0; i0 < nvec; i0 += 256) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const size_t i = i0 + (size_t)j * 32 + lane;
+      if (i < nvec) v[j] = __ldg(src + i);
+    }
+    if (p.ag_mc) {
+      // one store per 16 bytes, replicated into every rank's gathered buffer by the switch
+      char* dst = (char*)p.ag_mc + dst_off;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const size_t i = i0 + (size_t)j * 32 + lane;
-        if (i < nvec) v[j] = __ldg(src + i);
+        if (i < nvec)
+          asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + i * 16), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
       }
-      if (p.ag_mc) {
-        // one store per 16 bytes, replicated into every rank's gathered buffer by the switch
-        char* dst = (char*)p.ag_mc + dst_off;
+    } else {
+      for (int q1 = p.copy_own ? 0 : 1; q1 < n; ++q1) {
+        uint4* dst = (uint4*)((char*)p.ag_buf[(r + q1) % n] + dst_off);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const size_t i = i0 + (size_t)j * 32 + lane;
-          if (i < nvec)
-            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(dst + i * 16), "r"(v[j].x), "r"(v[j].y), "r"(v[j].z), "r"(v[j].w) : "memory");
-        }
-      } else {
-        for (int q1 = p.copy_own ? 0 : 1; q1 < n; ++q1) {
-          uint4* dst = (uint4*)((char*)p.ag_buf[(r + q1) % n] + dst_off);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const size_t i = i0 + (size_t)j * 32 + lane;
-            if (i < nvec) dst[i] = v[j];
-          }
+          if (i < nvec) dst[i] = v[j];
         }
       }
     }
-    __threadfence_system();  // every lane: its stores of this unit are visible before the flags
-    __syncwarp();
-    if (lane < n && (lane != 0 || p.copy_own)) dev::st_release_sys(&p.fflags[(r + lane) % n]->ag_ready[r][u], epoch);
+  }
+}
+// Announces unit u to every peer: each lane first makes its own stores visible system-wide.
+__device__ __forceinline__ void ag_flag_unit(const GemmParams& p, int u, uint32_t epoch, int lane) {
+  const int n = p.coll.nranks, r = p.coll.rank;
+  __threadfence_system();
+  __syncwarp();
+  if (lane < n && (lane != 0 || p.copy_own)) dev::st_release_sys(&p.fflags[(r + lane) % n]->ag_ready[r][u], epoch);
+}
+// The CTA's warps that move data share its sequence of units (cta, cta + nctas, ...): each takes
+// the next one.  Returns -1 when none is left.
+__device__ __forceinline__ int ag_take_unit(const GemmParams& p, SmemCtl* ctl, int cta, int nctas, int lane) {
+  const int units = (p.rows_per_rank + p.ag_unit_rows - 1) / p.ag_unit_rows;
+  int k = 0;
+  if (lane == 0) k = atomicAdd(&ctl->next_unit, 1);
+  k = __shfl_sync(0xffffffffu, k, 0);
+  const int u = cta + k * nctas;
+  return u < units ? u : -1;
+}
+// The same job as ag_mover with plain loads and stores by whole warps (several per CTA, so that
+// enough bytes are in flight to cover the link's latency): nothing of it goes through the SM's
+// bulk-copy engine, which the operand loads of the main loop depend on.
+__device__ void ag_mover_lsu(const GemmParams& p, SmemCtl* ctl, int cta, int nctas, uint32_t epoch, int lane) {
+  for (int u; (u = ag_take_unit(p, ctl, cta, nctas, lane)) >= 0;) {
+    ag_copy_unit(p, u, lane);
+    ag_flag_unit(p, u, epoch, lane);
   }
 }
 
@@ -617,11 +630,33 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
     constexpr int EPI_THREADS = 128 * MT;
     int it = 0;
     bool ok = true;
+    const bool epi_help = ag && p.ag_epi_help && (p.ag_mover == 1 || p.ag_mc);
+    int help_pending = -1;     // unit this warp copied but has not announced yet
+    bool help_done = false;    // the CTA's units are all taken
     for (; it < n_items && ok; ++it) {
       const Work wk = work_of(it, g, G, total_tiles, S, num_kb);
       Tile tl = tile_of(p, wk.t, tiles_m, tiles_n);
       const int buf = MT == 2 ? 0 : (it & 1);
       const uint32_t acc_phase = MT == 2 ? ((uint32_t)it & 1u) : ((uint32_t)(it >> 1) & 1u);
+      if (epi_help) {
+        // No accumulator to drain yet: move units of the shard meanwhile, one at a time, looking at
+        // the accumulator's barrier between units (a unit that was copied is announced first).
+        for (;;) {
+          const bool ready = __shfl_sync(0xffffffffu, mbar_try_wait(&ctl->tfull[buf], acc_phase) ? 1 : 0, 0) != 0;
+          if (help_pending >= 0) {
+            ag_flag_unit(p, help_pending, epoch, lane);
+            help_pending = -1;
+          }
+          if (ready || help_done || *(volatile int*)&ctl->mover_go != 1) break;
+          const int u = ag_take_unit(p, ctl, cta, nctas, lane);
+          if (u < 0) {
+            help_done = true;
+            break;
+          }
+          ag_copy_unit(p, u, lane);
+          help_pending = u;
+        }
+      }
       ok = mbar_wait(&ctl->tfull[buf], acc_phase, p.coll.timeout_ns, abort);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -825,6 +860,11 @@ __device__ void gemm_body(const GemmParams& p, const CUtensorMap* map_a, const C
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->tempty[buf]);
       }
+    }
+    if (epi_help) {
+      // out of tiles: announce what is still pending and keep moving until the CTA's units are gone
+      if (help_pending >= 0) ag_flag_unit(p, help_pending, epoch, lane);
+      if (!*abort && *(volatile int*)&ctl->mover_go == 1) ag_mover_lsu(p, ctl, cta, nctas, epoch, lane);
     }
   }
 

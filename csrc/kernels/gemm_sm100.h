@@ -53,6 +53,7 @@ struct GemmParams {
                             // the stores are multimem.st into the multicast mapping (one per 16 bytes for all peers)
   void* ag_mc;              // all-gather: multicast mapping of the gathered buffers (null: none)
   int ag_mover_warps;       // all-gather: mover warps per CTA that take part (1 .. 4 with 128-row tiles, 1 .. 2 with 256-row tiles)
+  int ag_epi_help;          // all-gather: epilogue warps move units of the shard while they wait for an accumulator
   int copy_own;             // all-gather: also place my own shard in the gathered buffer
   const void* a_local;      // all-gather: my shard, bf16 [rows_per_rank, K]
   void* ag_buf[kMaxRanks];  // all-gather: every rank's gathered-A buffer [M, K]; [rank] is mine

@@ -58,13 +58,15 @@ def test_gemm_split_k_tail(M, N, K, tile_height):
         assert torch.equal(out, outs[0])
 
 
-@pytest.fixture(params=["0", "1"], ids=["bulk_mover", "lsu_mover"])
+@pytest.fixture(params=[("0", "0"), ("1", "0"), ("1", "1")], ids=["bulk_mover", "warp_movers", "warp_movers_epilogue_helps"])
 def mover(request):
-    """The two ways the all-gather mover warp copies (read by the library at every call)."""
+    """How the all-gather movers copy, and whether the epilogue warps help while they wait (the
+    library reads both variables at every call)."""
     import os
-    os.environ["AMEM_AG_MOVER"] = request.param
+    os.environ["AMEM_AG_MOVER"], os.environ["AMEM_AG_EPI_HELP"] = request.param
     yield request.param
     os.environ.pop("AMEM_AG_MOVER", None)
+    os.environ.pop("AMEM_AG_EPI_HELP", None)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
