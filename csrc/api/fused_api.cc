@@ -12,6 +12,7 @@
 #include "../comm/emu.h"
 #include "../core/log.h"
 #include "../include/nccl.h"
+#include "../kernels/gemm_ag_cta_movers.h"
 #include "../kernels/gemm_sm100.h"
 #include "../kernels/moe.h"
 #include "../vmm/tracked.h"
@@ -270,6 +271,53 @@ ncclResult_t amemGroupedGemmBf16(const void* A, const void* B, void* C, const in
   return R(s);
 }
 
+}  // extern "C"
+
+namespace {
+// All-gather -> GEMM on the schedule with dedicated mover CTAs (gemm_ag_cta_movers.cu): CTAs
+// [0, comm_ctas) stream the local shard to the peers with bulk copies through their operand ring
+// and announce every 32 rows; the other CTAs compute, local shard first.
+Status ag_gemm_cta_movers(Comm* c, const void* a_shard, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
+  namespace v = agcta;
+  const int n = c->nranks(), rpr = M / n;
+  if ((rpr + v::kAgUnitRows - 1) / v::kAgUnitRows > v::kMaxUnits) return fail(kInvalidArgument, "more than %d rows per rank", v::kAgUnitRows * v::kMaxUnits);
+  v::GemmLaunch g;
+  memset(&g, 0, sizeof(g));
+  c->fill_args(&g.p.coll);
+  for (int r = 0; r < n; ++r) g.p.fflags[r] = (v::FusedFlags*)c->fused_flags(r);
+  g.p.M = M;
+  g.p.N = N;
+  g.p.K = K;
+  g.p.C = C;
+  g.p.ldc = N;
+  g.p.rows_per_rank = rpr;
+  g.p.a_local = a_shard;
+  g.p.mode = v::kGemmAllGather;
+  Segment* seg = nullptr;
+  AMEM_TRY(c->fused_segment(0, (size_t)M * K * 2, &seg));
+  for (int r = 0; r < n; ++r) g.p.ag_buf[r] = (void*)seg->va[r];
+  AMEM_TRY(v::make_tensor_map_bf16(&g.map_a, g.p.ag_buf[c->rank()], M, K, K, v::kGemmBM));
+  AMEM_TRY(v::make_tensor_map_bf16(&g.map_a_local, a_shard, rpr, K, K, v::kGemmBM));
+  if (c->emulated()) {
+    g.grid = emu_grid(n);
+    g.p.comm_ctas = 1;
+  } else {
+    g.grid = v::gemm_default_grid(c->device());
+    g.p.comm_ctas = (int)env_long("AMEM_AG_COMM_CTAS", 16);
+    if (g.p.comm_ctas < 1) g.p.comm_ctas = 1;
+    if (g.p.comm_ctas > g.grid / 2) g.p.comm_ctas = g.grid / 2;
+  }
+  g.p.bn = v::gemm_pick_bn(n * ((rpr + v::kGemmBM - 1) / v::kGemmBM), N, g.grid - g.p.comm_ctas);
+  AMEM_TRY(v::make_tensor_map_bf16(&g.map_b, B, N, K, K, g.p.bn));
+  if (c->emulated())
+    return c->emu()->rendezvous(c->rank(), 1100 + g.p.mode, &g, sizeof(g), stream,
+                                [n](const void* host_all, const void*, cudaStream_t s) { return v::launch_gemm_emu((const v::GemmLaunch*)host_all, n, s); });
+  return v::launch_gemm(g, stream);
+}
+}  // namespace
+
+extern "C" {
+
 // C[M, N] = allgather_rows(a_shard)[M, K] * B[N, K]^T.  Every rank passes its M/nranks rows;
 // B and C are per rank (column-parallel weight shard and its output).
 ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int M, int N, int K, ncclComm_t comm, cudaStream_t stream) {
@@ -282,6 +330,7 @@ ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int 
   if (M % n) return R(fail(kInvalidArgument, "M=%d is not divisible by %d ranks", M, n));
   int rpr = M / n;
   if ((s = c->prepare_stream(stream)) != kSuccess) return R(s);
+  if (n > 1 && !gemm_ag_uses_mover_warps(n)) return R(ag_gemm_cta_movers(c, a_shard, B, C, M, N, K, stream));
   GemmLaunch g;
   memset(&g, 0, sizeof(g));
   fill_fused(c, &g.p);

@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "../core/log.h"
+#include "../kernels/gemm_sm100.h"
 #include "../kernels/launch.h"
 #include "emu.h"
 #include "../vmm/tracked.h"
@@ -228,7 +229,7 @@ Status Comm::fused_segment(int which, size_t bytes, Segment** out) {
   // communicator has one for its staging: a row then crosses this GPU's links once (one
   // multimem.st, replicated by the switch) instead of once per peer.  Every rank decides the same
   // way (setup_multicast agrees collectively); without it the kernel stores to each peer.
-  if (which == 0 && nranks_ > 2 && stage_.mc_va && env_long("AMEM_AG_MC", 1)) {
+  if (which == 0 && nranks_ > 2 && stage_.mc_va && gemm_ag_uses_mover_warps(nranks_) && env_long("AMEM_AG_MC", 1)) {
     if (setup_multicast(&s, s.va[rank_]) != kSuccess) LOGI("all-gather buffer: no multicast mapping, using per-peer stores");
   }
   *out = &s;

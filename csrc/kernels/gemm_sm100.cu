@@ -951,6 +951,11 @@ Status make_tensor_map_bf16(CUtensorMap* out, const void* base, uint64_t rows, u
 
 size_t gemm_smem_bytes() { return (size_t)kGemmStages * gemmk::STAGE_BYTES + gemmk::SIDE_BUFS * gemmk::EPI_CHUNK_BYTES + sizeof(gemmk::SmemCtl) + 1024 + 64; }
 
+bool gemm_ag_uses_mover_warps(int nranks) {
+  const long d = env_long("AMEM_AG_DESIGN", 0);
+  return d == 1 ? true : d == 2 ? false : nranks <= 4;
+}
+
 int gemm_ag_unit_rows(int rows_per_rank, int K) {
   const int by_flags = (rows_per_rank + kMaxAgUnits - 1) / kMaxAgUnits;      // at most kMaxAgUnits flags per source
   const int by_piece = (kAgPieceBytes + K * 2 - 1) / (K * 2);                // a unit is at least one piece of the mover

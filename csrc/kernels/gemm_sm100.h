@@ -96,6 +96,11 @@ int gemm_pick_bn(int row_tiles, int N, int ctas, int k_blocks = 0, int* slices =
 bool gemm_tall_pays(int M, int N, int k_blocks, int ctas, int bn_flat, int slices_flat, int bn_tall, int slices_tall);
 // Slices of the tail split for a given tiling, 1 when splitting does not pay.
 int gemm_tail_slices(long tiles, int ctas, int k_blocks);
+// Which all-gather -> GEMM schedule a communicator of n ranks runs: mover warps inside every CTA
+// (this file; the faster one up to four ranks) or dedicated mover CTAs (gemm_ag_cta_movers.cu; the
+// faster one from five ranks up, where the transfer takes as long as the GEMM).
+// AMEM_AG_DESIGN: 0 = by rank count, 1 = mover warps, 2 = mover CTAs.
+bool gemm_ag_uses_mover_warps(int nranks);
 // Rows per ready flag of the all-gather mode: as few as the flag array and the mover's copy size allow,
 // so that rows become usable in the order they arrive.
 int gemm_ag_unit_rows(int rows_per_rank, int K);

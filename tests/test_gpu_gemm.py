@@ -58,20 +58,34 @@ def test_gemm_split_k_tail(M, N, K, tile_height):
         assert torch.equal(out, outs[0])
 
 
-@pytest.fixture(params=[("0", "0"), ("1", "0"), ("1", "1")], ids=["bulk_mover", "warp_movers", "warp_movers_epilogue_helps"])
-def mover(request):
-    """How the all-gather movers copy, and whether the epilogue warps help while they wait (the
-    library reads both variables at every call)."""
+_AG_VARIANTS = {   # AMEM_AG_DESIGN, AMEM_GEMM_TALL, AMEM_AG_MOVER, AMEM_AG_EPI_HELP
+    "mover_ctas": ("2", "0", "0", "0"),
+    "mover_warps_bulk_128": ("1", "0", "0", "0"),
+    "mover_warps_bulk_256": ("1", "1", "0", "0"),
+    "mover_warps_128": ("1", "0", "1", "0"),
+    "mover_warps_256": ("1", "1", "1", "0"),
+    "mover_warps_128_epilogue_helps": ("1", "0", "1", "1"),
+    "mover_warps_256_epilogue_helps": ("1", "1", "1", "1"),
+}
+
+
+@pytest.fixture(params=list(_AG_VARIANTS), ids=list(_AG_VARIANTS))
+def ag_variant(request):
+    """Both schedules of the all-gather -> GEMM kernel at every rank count (dedicated mover CTAs;
+    mover warps in every CTA with both tile heights, both ways of copying, with and without help
+    from the epilogue warps).  The library reads the variables at every call."""
     import os
-    os.environ["AMEM_AG_MOVER"], os.environ["AMEM_AG_EPI_HELP"] = request.param
+    names = ("AMEM_AG_DESIGN", "AMEM_GEMM_TALL", "AMEM_AG_MOVER", "AMEM_AG_EPI_HELP")
+    for name, val in zip(names, _AG_VARIANTS[request.param]):
+        os.environ[name] = val
     yield request.param
-    os.environ.pop("AMEM_AG_MOVER", None)
-    os.environ.pop("AMEM_AG_EPI_HELP", None)
+    for name in names:
+        os.environ.pop(name, None)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("m_local,N,K", [(128, 256, 256), (200, 520, 328), (512, 1024, 1024), (300, 264, 4096)])
-def test_all_gather_gemm(world, m_local, N, K, tile_height, mover):
+def test_all_gather_gemm(world, m_local, N, K, ag_variant):
     """Both tile heights; shards whose row count is no multiple of the tile height or of the rows
     one ready flag covers (a flag covers 16 rows at K = 256, 13 at K = 328, one at K = 4096)."""
     from asystem_amem_b200.ops import all_gather_gemm
