@@ -136,6 +136,7 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "amemMoeCombine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "amemGemmBf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "amemGemmPlan": [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],
+        "amemAllGatherGemmPlan": [c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],
         "amemGroupedGemmBf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "amemAllGatherGemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
         "amemGemmReduceScatter": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],

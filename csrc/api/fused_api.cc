@@ -162,6 +162,24 @@ ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* til
   return ncclSuccess;
 }
 
+// What amemAllGatherGemm does on a communicator of `nranks` ranks whose shards have `rows_per_rank`
+// rows of K bf16 (host arithmetic, no GPU needed).  *mover_warps: 1 = mover warps inside every CTA,
+// 0 = dedicated mover CTAs; *rows_per_flag: rows of a shard that one ready flag announces;
+// *flags_per_rank: ready flags one source rank uses.  Outputs may be null.
+ncclResult_t amemAllGatherGemmPlan(int nranks, int rows_per_rank, int K, int* mover_warps, int* rows_per_flag, int* flags_per_rank) {
+  if (nranks < 1 || nranks > kMaxRanks || rows_per_rank <= 0 || K <= 0 || K % 8)
+    return R(fail(kInvalidArgument, "amemAllGatherGemmPlan: nranks=%d rows_per_rank=%d K=%d", nranks, rows_per_rank, K));
+  const bool warps = nranks == 1 || gemm_ag_uses_mover_warps(nranks);
+  const int per_flag = warps ? gemm_ag_unit_rows(rows_per_rank, K) : agcta::kAgUnitRows;
+  const int flags = (rows_per_rank + per_flag - 1) / per_flag;
+  if (flags > (warps ? kMaxAgUnits : agcta::kMaxUnits))
+    return R(fail(kInvalidArgument, "amemAllGatherGemmPlan: %d rows per rank need %d ready flags", rows_per_rank, flags));
+  if (mover_warps) *mover_warps = warps ? 1 : 0;
+  if (rows_per_flag) *rows_per_flag = per_flag;
+  if (flags_per_rank) *flags_per_rank = flags;
+  return ncclSuccess;
+}
+
 ncclResult_t amemGemmBf16(const void* A, const void* B, void* C, int M, int N, int K, cudaStream_t stream) {
   Status s = check_shape(M, N, K);
   if (s != kSuccess) return R(s);

@@ -226,6 +226,9 @@ ncclResult_t amemDebugDirtyCanary(ncclComm_t comm); /* test hook: dirties the gu
 ncclResult_t amemGroupedGemmBf16(const void* A, const void* B, void* C, const int* group_off, int groups, int rows_cap, int rows_hint,
                                  int N, int K, int epilogue, cudaStream_t stream);
 ncclResult_t amemGemmPlan(int M, int N, int K, int sms, int* tile_rows, int* tile_cols, int* tail_slices);
+/* Schedule of amemAllGatherGemm for nranks ranks (1 = mover warps in every CTA, 0 = dedicated mover CTAs), rows of a
+   shard per ready flag and ready flags per source rank.  Host arithmetic, no GPU needed. */
+ncclResult_t amemAllGatherGemmPlan(int nranks, int rows_per_rank, int K, int* mover_warps, int* rows_per_flag, int* flags_per_rank);
 /* One kernel: C[M,N] = allgather_rows(a_shard)[M,K] * B[N,K]^T.  a_shard holds this rank's
  * M/nranks rows; the transfer of the other ranks' rows overlaps the tensor-core work. */
 ncclResult_t amemAllGatherGemm(const void* a_shard, const void* B, void* C, int M, int N, int K, ncclComm_t comm, cudaStream_t stream);

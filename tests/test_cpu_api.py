@@ -135,6 +135,36 @@ def test_gemm_planner_picks_tile_form_and_tail_split():
     assert lib.amemGemmPlan(128, 100, 64, 148, None, None, None) == 4   # N not a multiple of 8
 
 
+def test_all_gather_gemm_plan_picks_schedule_and_flag_granularity(monkeypatch):
+    """Mover warps inside every CTA up to four ranks, dedicated mover CTAs from five up (an
+    environment variable forces either); a ready flag covers as few rows as the flag array and the
+    movers' smallest copy allow, 32 rows on the mover-CTA schedule; shards too long for the flag
+    array are refused."""
+    import ctypes
+    from asystem_amem_b200.bindings import load_library
+    lib = load_library()
+    w, per, flags = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+
+    def plan(n, rows, K):
+        rc = lib.amemAllGatherGemmPlan(n, rows, K, ctypes.byref(w), ctypes.byref(per), ctypes.byref(flags))
+        return rc, w.value, per.value, flags.value
+
+    monkeypatch.delenv("AMEM_AG_DESIGN", raising=False)
+    assert plan(2, 4096, 8192) == (0, 1, 4, 1024)          # 1024 flags at most: 4 rows each
+    assert plan(4, 2048, 8192) == (0, 1, 2, 1024)
+    assert plan(4, 1024, 8192) == (0, 1, 1, 1024)          # one 16 KB row is more than the smallest copy
+    assert plan(4, 512, 256) == (0, 1, 16, 32)             # 512-byte rows: 16 of them make one 8 KB copy
+    assert plan(8, 1024, 8192) == (0, 0, 32, 32)           # mover CTAs: a flag per 32 rows
+    assert plan(5, 1000, 4096) == (0, 0, 32, 32)
+    assert plan(8, 32 * 256 + 1, 4096)[0] != 0             # more than 256 flags on the mover-CTA schedule
+    assert plan(4, 128, 100)[0] != 0                       # K not a multiple of 8
+    monkeypatch.setenv("AMEM_AG_DESIGN", "1")
+    assert plan(8, 1024, 8192)[:2] == (0, 1)
+    monkeypatch.setenv("AMEM_AG_DESIGN", "2")
+    assert plan(2, 1024, 8192)[:3] == (0, 0, 32)
+    assert lib.amemAllGatherGemmPlan(4, 1024, 8192, None, None, None) == 0
+
+
 def test_tuner_plan_is_deterministic_and_within_staging():
     """Variant picker: thresholds measured on 2 and 8 GPUs, chunk sizes that fit the staging
     layout, identical answers on repeated calls (every rank must pick the same plan)."""
