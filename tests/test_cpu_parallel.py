@@ -108,9 +108,9 @@ def test_pipeline_forward_schedule():
     assert res[2] == [((2 * (i + 1) + 0) * 2 + 1) * 2 + 2 for i in range(3)]
 
 
-def _pipeline_1f1b(rank, world, uid):
-    """Three stages, five micro-batches, one linear layer per stage: losses and every stage's
-    accumulated weight gradient must equal those of the same three layers run in one process."""
+def _pipeline_1f1b(rank, world, uid, n_mb=5):
+    """One linear layer per stage, `n_mb` micro-batches: losses and every stage's accumulated
+    weight gradient must equal those of the same layers run in one process."""
     import torch
     from asystem_amem_b200 import Communicator
     from asystem_amem_b200.parallel import PipelineStage
@@ -118,8 +118,8 @@ def _pipeline_1f1b(rank, world, uid):
     torch.manual_seed(0)
     layers = [torch.nn.Linear(8, 8) for _ in range(world)]        # same on every rank (same seed)
     g = torch.Generator().manual_seed(1)
-    mbs = [torch.randn(4, 8, generator=g) for _ in range(5)]
-    targets = [torch.randn(4, 8, generator=g) for _ in range(5)]
+    mbs = [torch.randn(4, 8, generator=g) for _ in range(n_mb)]
+    targets = [torch.randn(4, 8, generator=g) for _ in range(n_mb)]
     mine = layers[rank]
     stage = PipelineStage(comm, rank, world)
     losses = stage.run_1f1b(lambda x: torch.tanh(mine(x)), mbs, torch.empty(4, 8),
@@ -142,12 +142,14 @@ def _pipeline_1f1b(rank, world, uid):
     return err, None if losses is None else [float(v) for v in losses], ref_losses
 
 
-def test_pipeline_1f1b_matches_single_process_gradients():
-    res = run_ranks(_pipeline_1f1b, 3)
+@pytest.mark.parametrize("stages,n_mb", [(3, 5), (4, 2), (2, 1), (4, 9)])
+def test_pipeline_1f1b_matches_single_process_gradients(stages, n_mb):
+    """More micro-batches than stages (a steady 1F1B phase), fewer (warm-up and drain only), one."""
+    res = run_ranks(_pipeline_1f1b, stages, args=(n_mb,))
     for err, _losses, _ref in res:
         assert err < 1e-5, res
-    assert res[0][1] is None and res[1][1] is None
-    assert all(abs(a - b) < 1e-5 for a, b in zip(res[2][1], res[2][2])), res[2]
+    assert all(r[1] is None for r in res[:-1])
+    assert all(abs(a - b) < 1e-5 for a, b in zip(res[-1][1], res[-1][2])), res[-1]
 
 
 def test_1f1b_plan_completes_under_rendezvous_semantics():
