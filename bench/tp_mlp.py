@@ -109,6 +109,13 @@ def main():
     res["ag_speedup_vs_cublas_nccl"] = res["ag_gemm_cublas_nccl_ms"] / res["ag_gemm_fused_ms"]
     res["rs_speedup_vs_cublas_nccl"] = res["gemm_rs_cublas_nccl_ms"] / res["gemm_rs_fused_ms"]
     res["peaks"] = peaks.get("source")
+    # which schedule the all-gather -> GEMM kernel ran (host arithmetic of the library)
+    import ctypes
+    from asystem_amem_b200.bindings import load_library
+    sched, per_flag = ctypes.c_int(), ctypes.c_int()
+    if load_library().amemAllGatherGemmPlan(world, rows, D, ctypes.byref(sched), ctypes.byref(per_flag), None) == 0:
+        res["ag_schedule"] = "mover warps in every CTA" if sched.value else "dedicated mover CTAs"
+        res["ag_rows_per_ready_flag"] = per_flag.value
     # numerics of the fused kernels against the library path
     base_ag()
     ref_h = h.clone()
