@@ -193,6 +193,23 @@ def test_1f1b_plan_completes_under_rendezvous_semantics():
             assert all(pos[s] == len(plans[s]) for s in range(n)), (n, m, pos)
 
 
+def test_1f1b_plan_keeps_at_most_n_minus_s_micro_batches_alive():
+    """The point of 1F1B over GPipe: stage s never holds more than n - s forward results that
+    still wait for their backward (GPipe would hold all m)."""
+    from asystem_amem_b200.parallel.pp import plan_1f1b
+    for n in range(1, 7):
+        for m in range(1, 13):
+            for s in range(n):
+                alive = peak = 0
+                for st in plan_1f1b(s, n, m):
+                    if st[0] == "fwd":
+                        alive += 1
+                        peak = max(peak, alive)
+                    elif st[0] == "bwd":
+                        alive -= 1
+                assert alive == 0 and peak <= min(m, n - s), (n, m, s, peak)
+
+
 def _context_parallel(rank, world, uid, causal):
     import torch
     from asystem_amem_b200 import Communicator
