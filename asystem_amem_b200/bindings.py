@@ -137,6 +137,7 @@ def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
         "amemGemmBf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "amemGemmPlan": [c_int, c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],
         "amemAllGatherGemmPlan": [c_int, c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), ctypes.POINTER(c_int)],
+        "amemDeviceWaitProbe": [c_int, c_int, ctypes.POINTER(c_int), ctypes.POINTER(ctypes.c_float)],
         "amemGroupedGemmBf16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "amemAllGatherGemm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
         "amemGemmReduceScatter": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],

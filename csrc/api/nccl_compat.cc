@@ -487,6 +487,42 @@ ncclResult_t amemBackendTimings(char* buf, size_t len, int reset) {
   snprintf(buf, len, "%s", s.c_str());
   return ncclSuccess;
 }
+ncclResult_t amemDeviceWaitProbe(int timeout_ms, int flag_is_set, int* code, float* waited_ms) {
+  if (timeout_ms <= 0 || timeout_ms > 10000) return R(fail(kInvalidArgument, "amemDeviceWaitProbe: timeout %d ms (1 .. 10000)", timeout_ms));
+  uint32_t* flag = nullptr;
+  uint32_t* status = nullptr;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  Status st = kSuccess;
+  float ms = 0.f;
+  if (cudaMalloc((void**)&flag, sizeof(uint32_t)) != cudaSuccess || cudaHostAlloc((void**)&status, kStatusWords * sizeof(uint32_t), cudaHostAllocMapped) != cudaSuccess ||
+      cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) {
+    cudaGetLastError();
+    st = fail(kCudaError, "amemDeviceWaitProbe: could not allocate its two words and events");
+  }
+  if (st == kSuccess) {
+    memset(status, 0, kStatusWords * sizeof(uint32_t));
+    const uint32_t init = flag_is_set ? 1u : 0u;
+    if (cudaMemcpy(flag, &init, sizeof(init), cudaMemcpyHostToDevice) != cudaSuccess) st = fail(kCudaError, "amemDeviceWaitProbe: cudaMemcpy failed");
+  }
+  if (st == kSuccess) {
+    cudaEventRecord(e0, 0);
+    st = launch_wait_probe(flag, 1u, (unsigned long long)timeout_ms * 1000000ull, status, 0);
+    cudaEventRecord(e1, 0);
+    cudaError_t e = cudaEventSynchronize(e1);
+    if (st == kSuccess && e != cudaSuccess) st = fail(kCudaError, "amemDeviceWaitProbe: %s", cudaGetErrorString(e));
+    if (st == kSuccess) cudaEventElapsedTime(&ms, e0, e1);
+  }
+  if (st == kSuccess) {
+    if (code) *code = (int)status[0];
+    if (waited_ms) *waited_ms = ms;
+  }
+  if (e0) cudaEventDestroy(e0);
+  if (e1) cudaEventDestroy(e1);
+  if (status) cudaFreeHost(status);
+  if (flag) cudaFree(flag);
+  return R(st);
+}
+
 int amemBackendIsDevice(void) {
   VmmBackend* be = default_backend();
   return be && be->is_device() ? 1 : 0;

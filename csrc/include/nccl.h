@@ -259,6 +259,11 @@ ncclResult_t amemCommInfo(ncclComm_t comm, int* emulated, int* nvls, size_t* sta
 ncclResult_t amemInject(const char* what, int nth, int param);
 /* Bytes of physical memory and number of mappings this process holds through the backend. */
 ncclResult_t amemBackendUsage(size_t* physical_bytes, size_t* mappings, const char** backend_name);
+/* Runs one device thread that waits, as the collective kernels wait for their peers, for a word that
+ * is set beforehand (flag_is_set != 0) or never (0), for at most timeout_ms.  *code receives the
+ * device error code written to host-visible status words (0 = the flag came, 1 = the wait ran out),
+ * *waited_ms the kernel's duration.  The kernel always returns; the CUDA context stays usable. */
+ncclResult_t amemDeviceWaitProbe(int timeout_ms, int flag_is_set, int* code, float* waited_ms);
 /* 1 when the memory backend is CUDA device memory, 0 for the host-memory mock. */
 int amemBackendIsDevice(void);
 /* JSON with the time spent in every kind of VMM driver call (create, map, set_access, ...). */

@@ -526,4 +526,21 @@ Status launch_collective_emu(const CollArgs* dev_all, const CollArgs& a, int nra
   return st;
 }
 
+
+// ---- bounded-wait probe: what a kernel does when the flag it waits for never comes
+namespace dev {
+__global__ void wait_probe_kernel(const uint32_t* flag, uint32_t want, unsigned long long timeout_ns, uint32_t* status) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    if (!wait_flag_ge(flag, want, timeout_ns)) report_error(status, kDevBarrierTimeout, 0, 0, 0, want);
+  }
+}
+}  // namespace dev
+
+Status launch_wait_probe(const uint32_t* flag, uint32_t want, unsigned long long timeout_ns, uint32_t* status, cudaStream_t stream) {
+  dev::wait_probe_kernel<<<1, 32, 0, stream>>>(flag, want, timeout_ns, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(kCudaError, "wait probe launch failed: %s", cudaGetErrorString(e));
+  return kSuccess;
+}
+
 }  // namespace amem

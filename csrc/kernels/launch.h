@@ -12,6 +12,10 @@ Status launch_collective(const CollArgs& a, const LaunchPlan& plan, cudaStream_t
 // Launches every rank of an emulated (single-GPU) communicator as one cooperative grid.
 // `dev_all` points to `nranks` CollArgs in device-readable memory; `a` is any rank's copy
 // (used for type dispatch only).
+// One thread waits, the way every collective kernel waits for a peer, until *flag >= want or
+// timeout_ns have passed; a wait that runs out is recorded in `status` (host-visible words) like a
+// collective's and the kernel returns normally.
+Status launch_wait_probe(const uint32_t* flag, uint32_t want, unsigned long long timeout_ns, uint32_t* status, cudaStream_t stream);
 Status launch_collective_emu(const CollArgs* dev_all, const CollArgs& a, int nranks, const LaunchPlan& plan, cudaStream_t stream);
 int sendrecv_blocks(const CollArgs& a);
 

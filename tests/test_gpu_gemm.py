@@ -59,7 +59,6 @@ def test_gemm_split_k_tail(M, N, K, tile_height):
 
 
 _AG_VARIANTS = {   # AMEM_AG_DESIGN, AMEM_GEMM_TALL, AMEM_AG_MOVER, AMEM_AG_EPI_HELP
-    "mover_ctas": ("2", "0", "0", "0"),
     "mover_warps_bulk_128": ("1", "0", "0", "0"),
     "mover_warps_bulk_256": ("1", "1", "0", "0"),
     "mover_warps_128": ("1", "0", "1", "0"),
@@ -71,9 +70,10 @@ _AG_VARIANTS = {   # AMEM_AG_DESIGN, AMEM_GEMM_TALL, AMEM_AG_MOVER, AMEM_AG_EPI_
 
 @pytest.fixture(params=list(_AG_VARIANTS), ids=list(_AG_VARIANTS))
 def ag_variant(request):
-    """Both schedules of the all-gather -> GEMM kernel at every rank count (dedicated mover CTAs;
-    mover warps in every CTA with both tile heights, both ways of copying, with and without help
-    from the epilogue warps).  The library reads the variables at every call."""
+    """The mover-warp schedule of the all-gather -> GEMM kernel at every rank count: both tile
+    heights, both ways of copying, with and without help from the epilogue warps (the schedule
+    with dedicated mover CTAs has a test file of its own).  The library reads the variables at
+    every call."""
     import os
     names = ("AMEM_AG_DESIGN", "AMEM_GEMM_TALL", "AMEM_AG_MOVER", "AMEM_AG_EPI_HELP")
     for name, val in zip(names, _AG_VARIANTS[request.param]):
